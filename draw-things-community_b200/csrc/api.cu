@@ -1,0 +1,265 @@
+// C ABI of the attention library (include/dtattn.h): argument validation, kernel selection, workspace
+// sizing, the host-tensor entry point and the gathered-layout permute.  No kernel math lives here.
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "sm100_ptx.cuh"
+
+namespace dt {
+
+// ---- error bookkeeping -------------------------------------------------------------------------------
+
+static thread_local int g_last_cuda_error = 0;
+
+int record_cuda_error(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return DT_CUDA;
+}
+
+// ---- per-device status word --------------------------------------------------------------------------
+
+static std::mutex g_status_mu;
+static unsigned int* g_status_words[64] = {nullptr};
+
+unsigned int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status_words[dev]) {
+    unsigned int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
+    g_status_words[dev] = p;
+  }
+  return g_status_words[dev];
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------------
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+bool make_bshd_tensor_map(CUtensorMap* map, const dt_tensor4& t, int B, int S, int H, int D, int dtype,
+                          int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return false;
+  if (dtype != DT_F16 && dtype != DT_BF16) return false;
+  if (reinterpret_cast<uintptr_t>(t.ptr) % 16) return false;
+  const cuuint64_t es = 2;
+  // A dimension of extent 1 may carry any stride in the view; give TMA a legal one.
+  auto stride_bytes = [&](int64_t s, int extent, cuuint64_t fallback) -> cuuint64_t {
+    return extent == 1 ? fallback : (cuuint64_t)s * es;
+  };
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t sh = stride_bytes(t.stride_h, H, (cuuint64_t)D * es);
+  cuuint64_t ss = stride_bytes(t.stride_s, S, sh * (cuuint64_t)H);
+  cuuint64_t sb = stride_bytes(t.stride_b, B, ss * (cuuint64_t)S);
+  cuuint64_t strides[3] = {sh, ss, sb};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 || strides[i] == 0 || strides[i] >= (1ull << 40)) return false;
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// ---- validation and dispatch -------------------------------------------------------------------------
+
+static int validate(const dt_sdpa_params* p) {
+  if (!p) return DT_BAD_ARG;
+  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->D <= 0) return DT_BAD_ARG;
+  if (p->Hq % p->Hkv) return DT_BAD_ARG;
+  if (p->dtype != DT_F16 && p->dtype != DT_BF16 && p->dtype != DT_F32) return DT_BAD_ARG;
+  if (!p->q.ptr || !p->k.ptr || !p->v.ptr || !p->o.ptr) return DT_BAD_ARG;
+  if (!(p->scale == p->scale)) return DT_BAD_ARG;  // NaN
+  const size_t es = dtype_size(p->dtype);
+  const dt_tensor4* ts[4] = {&p->q, &p->k, &p->v, &p->o};
+  for (auto t : ts)
+    if (reinterpret_cast<uintptr_t>(t->ptr) % es) return DT_BAD_ARG;
+  if (p->D > 256) return DT_UNSUPPORTED;
+  return DT_OK;
+}
+
+enum Kernel { kGeneric = 0, kDecode = 1, kPrefill = 2 };
+
+static Kernel choose(const dt_sdpa_params& p) {
+  if (p.flags & DT_FLAG_FORCE_GENERIC) return kGeneric;
+  if (decode_supported(p) && p.Sk >= 256) return kDecode;
+  if (prefill_supported(p)) return kPrefill;
+  if (decode_supported(p)) return kDecode;
+  return kGeneric;
+}
+
+}  // namespace dt
+
+using namespace dt;
+
+extern "C" {
+
+const char* dt_status_string(int status) {
+  switch (status) {
+    case DT_OK: return "ok";
+    case DT_BAD_ARG: return "bad argument";
+    case DT_UNSUPPORTED: return "unsupported shape, dtype or layout";
+    case DT_WORKSPACE: return "workspace missing or too small";
+    case DT_CUDA: return "CUDA call failed";
+    case DT_NCCL: return "NCCL unavailable or failed";
+    case DT_TIMEOUT: return "bounded wait ran out";
+    case DT_NO_DEVICE: return "no usable sm_100 device";
+  }
+  return "unknown status";
+}
+
+int dt_last_cuda_error(void) { return g_last_cuda_error; }
+
+int dt_abi_version(void) { return 1; }
+
+int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name) {
+  int st = validate(p);
+  if (st != DT_OK) return st;
+  if (!name) return DT_BAD_ARG;
+  static const char* names[3] = {"generic", "decode_splitkv", "prefill_tcgen05"};
+  *name = names[choose(*p)];
+  return DT_OK;
+}
+
+int dt_sdpa_workspace_size(const dt_sdpa_params* p, size_t* bytes) {
+  int st = validate(p);
+  if (st != DT_OK) return st;
+  if (!bytes) return DT_BAD_ARG;
+  *bytes = choose(*p) == kDecode ? decode_workspace_bytes(*p) : 0;
+  return DT_OK;
+}
+
+int dt_sdpa_workspace_init(void* workspace, size_t bytes, void* cuda_stream) {
+  if (!workspace || bytes == 0) return DT_OK;
+  DT_CUDA_TRY(cudaMemsetAsync(workspace, 0, bytes, (cudaStream_t)cuda_stream));
+  return DT_OK;
+}
+
+int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  int st = validate(p);
+  if (st != DT_OK) return st;
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  switch (choose(*p)) {
+    case kDecode: return launch_decode(*p, workspace, workspace_bytes, stream);
+    case kPrefill: return launch_prefill(*p, stream);
+    default: return launch_generic(*p, stream);
+  }
+}
+
+int dt_device_status(void* cuda_stream, int* code) {
+  if (!code) return DT_BAD_ARG;
+  unsigned int* w = device_status_word();
+  if (!w) return DT_CUDA;
+  unsigned int h = 0;
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  DT_CUDA_TRY(cudaMemcpyAsync(&h, w, sizeof(h), cudaMemcpyDeviceToHost, s));
+  DT_CUDA_TRY(cudaStreamSynchronize(s));
+  *code = (int)h;
+  if (h) {
+    DT_CUDA_TRY(cudaMemsetAsync(w, 0, sizeof(h), s));
+    DT_CUDA_TRY(cudaStreamSynchronize(s));
+    return DT_TIMEOUT;
+  }
+  return DT_OK;
+}
+
+// ---- host-tensor entry point -------------------------------------------------------------------------
+
+namespace {
+struct HostScratch {
+  void* dev = nullptr;
+  size_t dev_bytes = 0;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  cudaStream_t stream = nullptr;
+};
+thread_local HostScratch g_hs;
+
+// Extent in elements of the smallest contiguous span that holds a [B,S,H,D] view.
+size_t view_span(const dt_tensor4& t, int B, int S, int H, int D) {
+  return (size_t)((B - 1) * t.stride_b + (S - 1) * t.stride_s + (H - 1) * t.stride_h + D);
+}
+}  // namespace
+
+int dt_host_release(void) {
+  if (g_hs.dev) cudaFree(g_hs.dev);
+  if (g_hs.ws) cudaFree(g_hs.ws);
+  if (g_hs.stream) cudaStreamDestroy(g_hs.stream);
+  g_hs = HostScratch();
+  return DT_OK;
+}
+
+int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
+  int st = validate(ph);
+  if (st != DT_OK) return st;
+  if (ph->mask) return DT_UNSUPPORTED;  // masks are served by the device-tensor entry point only
+  dt_sdpa_params p = *ph;
+  const size_t es = dtype_size(p.dtype);
+  const size_t nq = view_span(p.q, p.B, p.Sq, p.Hq, p.D) * es, nk = view_span(p.k, p.B, p.Sk, p.Hkv, p.D) * es;
+  const size_t nv = view_span(p.v, p.B, p.Sk, p.Hkv, p.D) * es, no = view_span(p.o, p.B, p.Sq, p.Hq, p.D) * es;
+  auto al = [](size_t x) { return (x + 255) / 256 * 256; };
+  const size_t nl = p.lse ? al((size_t)p.B * p.Hq * p.Sq * 4) : 0;
+  const size_t total = al(nq) + al(nk) + al(nv) + al(no) + nl;
+  if (!g_hs.stream) DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.stream, cudaStreamNonBlocking));
+  if (g_hs.dev_bytes < total) {
+    if (g_hs.dev) cudaFree(g_hs.dev);
+    g_hs.dev = nullptr;
+    g_hs.dev_bytes = 0;
+    DT_CUDA_TRY(cudaMalloc(&g_hs.dev, total));
+    g_hs.dev_bytes = total;
+  }
+  uint8_t* d = reinterpret_cast<uint8_t*>(g_hs.dev);
+  p.q.ptr = d; d += al(nq);
+  p.k.ptr = d; d += al(nk);
+  p.v.ptr = d; d += al(nv);
+  p.o.ptr = d; d += al(no);
+  if (p.lse) p.lse = reinterpret_cast<float*>(d);
+  size_t wsb = 0;
+  st = dt_sdpa_workspace_size(&p, &wsb);
+  if (st != DT_OK) return st;
+  if (wsb > g_hs.ws_bytes) {
+    if (g_hs.ws) cudaFree(g_hs.ws);
+    g_hs.ws = nullptr;
+    g_hs.ws_bytes = 0;
+    DT_CUDA_TRY(cudaMalloc(&g_hs.ws, wsb));
+    g_hs.ws_bytes = wsb;
+    DT_CUDA_TRY(cudaMemsetAsync(g_hs.ws, 0, wsb, g_hs.stream));
+  }
+  cudaStream_t s = g_hs.stream;
+  DT_CUDA_TRY(cudaMemcpyAsync(p.q.ptr, ph->q.ptr, nq, cudaMemcpyHostToDevice, s));
+  DT_CUDA_TRY(cudaMemcpyAsync(p.k.ptr, ph->k.ptr, nk, cudaMemcpyHostToDevice, s));
+  DT_CUDA_TRY(cudaMemcpyAsync(p.v.ptr, ph->v.ptr, nv, cudaMemcpyHostToDevice, s));
+  // A strided output view has gaps the kernel never writes: carry the host's bytes through them.
+  if (no != (size_t)p.B * p.Sq * p.Hq * p.D * es) DT_CUDA_TRY(cudaMemcpyAsync(p.o.ptr, ph->o.ptr, no, cudaMemcpyHostToDevice, s));
+  st = dt_sdpa_forward(&p, g_hs.ws, g_hs.ws_bytes, s);
+  if (st != DT_OK) return st;
+  DT_CUDA_TRY(cudaMemcpyAsync(ph->o.ptr, p.o.ptr, no, cudaMemcpyDeviceToHost, s));
+  if (p.lse) DT_CUDA_TRY(cudaMemcpyAsync(ph->lse, p.lse, (size_t)p.B * p.Hq * p.Sq * 4, cudaMemcpyDeviceToHost, s));
+  DT_CUDA_TRY(cudaStreamSynchronize(s));
+  return DT_OK;
+}
+
+int dt_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D, int dtype,
+                        void* cuda_stream) {
+  if (!src || !dst.ptr || world <= 0 || B <= 0 || Sq <= 0 || Hl <= 0 || D <= 0) return DT_BAD_ARG;
+  return launch_permute_gathered(src, dst, world, B, Sq, Hl, D, dtype, (cudaStream_t)cuda_stream);
+}
+
+}  // extern "C"

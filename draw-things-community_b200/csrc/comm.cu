@@ -1,0 +1,253 @@
+// Head-sharded attention across the GPUs of one box: each rank runs the local head slice, the output
+// slices are exchanged with ncclAllGather over NVLink/NVSwitch on a side stream, and a permute kernel
+// lays them out as [B, Sq, H, D].  The query rows are cut into chunks so the gather of chunk c overlaps
+// the attention of chunk c+1.  NCCL is loaded with dlopen at first use: the core library has no
+// link-time NCCL dependency, and a process that already loaded an NCCL (PyTorch's) shares it.
+//
+// The reference has no counterpart: it is single-GPU per process (ccv is built with have_nccl = False,
+// WORKSPACE.linux:127).  No TMA multicast and no peer-memory TMA load is used anywhere on this path.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <string.h>
+
+#include <chrono>
+#include <thread>
+
+#include "common.cuh"
+
+namespace dt {
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  bool ok = false;
+};
+
+NcclApi& nccl() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api;
+  tried = true;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (api.handle) break;
+  }
+  if (!api.handle) return api;
+#define LOAD(field, sym) *reinterpret_cast<void**>(&api.field) = dlsym(api.handle, sym)
+  LOAD(GetUniqueId, "ncclGetUniqueId");
+  LOAD(CommInitRankConfig, "ncclCommInitRankConfig");
+  LOAD(CommGetAsyncError, "ncclCommGetAsyncError");
+  LOAD(CommAbort, "ncclCommAbort");
+  LOAD(CommDestroy, "ncclCommDestroy");
+  LOAD(AllGather, "ncclAllGather");
+#undef LOAD
+  api.ok = api.GetUniqueId && api.CommInitRankConfig && api.CommGetAsyncError && api.CommAbort && api.CommDestroy &&
+           api.AllGather;
+  return api;
+}
+
+constexpr int kMaxChunks = 64;
+
+struct Comm {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+  int timeout_ms = 30000;
+  cudaStream_t side = nullptr;
+  cudaEvent_t chunk_done[kMaxChunks];
+  cudaEvent_t all_done = nullptr;
+};
+
+// Poll the communicator until the pending operation left the in-progress state or the limit ran out.
+int wait_nccl(Comm* c, ncclResult_t r, int timeout_ms) {
+  NcclApi& api = nccl();
+  if (r == ncclSuccess) return DT_OK;
+  if (r != ncclInProgress) return DT_NCCL;
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    ncclResult_t st = ncclSuccess;
+    if (api.CommGetAsyncError(c->comm, &st) != ncclSuccess) return DT_NCCL;
+    if (st == ncclSuccess) return DT_OK;
+    if (st != ncclInProgress) return DT_NCCL;
+    const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+    if (ms > timeout_ms) return DT_TIMEOUT;
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+// src [world][B][Sq][Hl][D] -> dst view [B, Sq, world*Hl, D]; 16-byte vectors.
+__global__ void permute_gathered_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst_base, int world, int B,
+                                        int Sq, int Hl, int vec_per_head, int64_t d_sb, int64_t d_ss, int64_t d_sh,
+                                        int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t t = i;
+    const int vv = (int)(t % vec_per_head); t /= vec_per_head;
+    const int h = (int)(t % Hl); t /= Hl;
+    const int s = (int)(t % Sq); t /= Sq;
+    const int b = (int)(t % B); t /= B;
+    const int w = (int)t;
+    // strides are in 16-byte vectors here
+    dst_base[b * d_sb + s * d_ss + (int64_t)(w * Hl + h) * d_sh + vv] = src[i];
+  }
+}
+
+}  // namespace
+
+int launch_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D, int dtype,
+                            cudaStream_t stream) {
+  const size_t es = dtype_size(dtype);
+  const size_t head_bytes = (size_t)D * es;
+  if (head_bytes % 16) return DT_UNSUPPORTED;
+  const int vec = (int)(16 / es);
+  if (dst.stride_b % vec || dst.stride_s % vec || dst.stride_h % vec) return DT_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst.ptr) % 16) return DT_UNSUPPORTED;
+  const int vph = (int)(head_bytes / 16);
+  const int64_t total = (int64_t)world * B * Sq * Hl * vph;
+  const int threads = 256;
+  int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  permute_gathered_kernel<<<(int)blocks, threads, 0, stream>>>(
+      reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst.ptr), world, B, Sq, Hl, vph,
+      dst.stride_b / vec, dst.stride_s / vec, dst.stride_h / vec, total);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace dt
+
+using namespace dt;
+
+extern "C" {
+
+int dt_comm_unique_id(void* id_out_128) {
+  if (!id_out_128) return DT_BAD_ARG;
+  NcclApi& api = nccl();
+  if (!api.ok) return DT_NCCL;
+  ncclUniqueId id;
+  if (api.GetUniqueId(&id) != ncclSuccess) return DT_NCCL;
+  static_assert(sizeof(ncclUniqueId) == DT_NCCL_UNIQUE_ID_BYTES, "unique id size");
+  memcpy(id_out_128, &id, sizeof(id));
+  return DT_OK;
+}
+
+int dt_comm_init(void** comm_out, int rank, int world, const void* unique_id_128, int timeout_ms) {
+  if (!comm_out || !unique_id_128 || world <= 0 || rank < 0 || rank >= world) return DT_BAD_ARG;
+  *comm_out = nullptr;
+  NcclApi& api = nccl();
+  if (!api.ok) return DT_NCCL;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return DT_NO_DEVICE;
+  Comm* c = new Comm();
+  c->rank = rank;
+  c->world = world;
+  c->timeout_ms = timeout_ms > 0 ? timeout_ms : 30000;
+  ncclUniqueId id;
+  memcpy(&id, unique_id_128, sizeof(id));
+  ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+  cfg.blocking = 0;  // so that a rank that never joins ends in DT_TIMEOUT instead of a hang
+  ncclResult_t r = api.CommInitRankConfig(&c->comm, world, id, rank, &cfg);
+  int st = (r == ncclSuccess || r == ncclInProgress) ? wait_nccl(c, ncclInProgress, c->timeout_ms) : DT_NCCL;
+  if (st != DT_OK) {
+    if (c->comm) api.CommAbort(c->comm);
+    delete c;
+    return st;
+  }
+  if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess) { delete c; return DT_CUDA; }
+  for (int i = 0; i < kMaxChunks; ++i) cudaEventCreateWithFlags(&c->chunk_done[i], cudaEventDisableTiming);
+  cudaEventCreateWithFlags(&c->all_done, cudaEventDisableTiming);
+  *comm_out = c;
+  return DT_OK;
+}
+
+int dt_comm_destroy(void* comm) {
+  if (!comm) return DT_OK;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  NcclApi& api = nccl();
+  if (c->side) cudaStreamSynchronize(c->side);
+  if (c->comm && api.ok) api.CommDestroy(c->comm);
+  for (int i = 0; i < kMaxChunks; ++i) cudaEventDestroy(c->chunk_done[i]);
+  if (c->all_done) cudaEventDestroy(c->all_done);
+  if (c->side) cudaStreamDestroy(c->side);
+  delete c;
+  return DT_OK;
+}
+
+static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
+
+int dt_sdpa_headsharded_workspace_size(const dt_sdpa_params* local, int world, int chunks, size_t* bytes) {
+  if (!local || !bytes || world <= 0 || chunks <= 0 || chunks > kMaxChunks) return DT_BAD_ARG;
+  size_t inner = 0;
+  int st = dt_sdpa_workspace_size(local, &inner);
+  if (st != DT_OK) return st;
+  const size_t slice = (size_t)local->B * local->Sq * local->Hq * local->D * dtype_size(local->dtype);
+  // every chunk gets its own staging and gather region, so no region is reused while in flight
+  *bytes = al256(inner) + al256(slice) + al256(slice * world) + 256 * (size_t)chunks * 2;
+  return DT_OK;
+}
+
+int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tensor4 o_full, int chunks,
+                                void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!comm || !local || !o_full.ptr) return DT_BAD_ARG;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  NcclApi& api = nccl();
+  if (!api.ok) return DT_NCCL;
+  if (chunks <= 0 || chunks > kMaxChunks) return DT_BAD_ARG;
+  if (local->is_causal && chunks != 1) return DT_UNSUPPORTED;  // a row chunk would shift the causal diagonal
+  if (local->mask || local->lse) return DT_UNSUPPORTED;
+  if (chunks > local->Sq) chunks = local->Sq;
+  size_t need = 0, inner = 0;
+  int st = dt_sdpa_headsharded_workspace_size(local, c->world, chunks, &need);
+  if (st != DT_OK) return st;
+  if (!workspace || workspace_bytes < need) return DT_WORKSPACE;
+  dt_sdpa_workspace_size(local, &inner);
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const size_t es = dtype_size(local->dtype);
+  const int B = local->B, Hl = local->Hq, D = local->D;
+  uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
+  void* inner_ws = w;
+  uint8_t* stage = w + al256(inner);
+  const size_t slice = (size_t)B * local->Sq * Hl * D * es;
+  uint8_t* gath = stage + al256(slice);
+
+  // rows per chunk, rounded to the 256-row pair of query tiles the tensor-core kernel works in
+  int rows_per = (local->Sq + chunks - 1) / chunks;
+  if (chunks > 1) rows_per = (rows_per + 255) / 256 * 256;
+  size_t stage_off = 0, gath_off = 0;
+  int ci = 0;
+  for (int r0 = 0; r0 < local->Sq; r0 += rows_per, ++ci) {
+    const int rows = local->Sq - r0 < rows_per ? local->Sq - r0 : rows_per;
+    dt_sdpa_params p = *local;
+    p.Sq = rows;
+    p.q.ptr = reinterpret_cast<uint8_t*>(local->q.ptr) + (size_t)r0 * local->q.stride_s * es;
+    p.o.ptr = stage + stage_off;
+    p.o.stride_h = D;
+    p.o.stride_s = (int64_t)Hl * D;
+    p.o.stride_b = (int64_t)rows * Hl * D;
+    st = dt_sdpa_forward(&p, inner_ws, inner, s);
+    if (st != DT_OK) return st;
+    DT_CUDA_TRY(cudaEventRecord(c->chunk_done[ci], s));
+    DT_CUDA_TRY(cudaStreamWaitEvent(c->side, c->chunk_done[ci], 0));
+    const size_t cbytes = (size_t)B * rows * Hl * D * es;
+    ncclResult_t r = api.AllGather(stage + stage_off, gath + gath_off, cbytes, ncclChar, c->comm, c->side);
+    st = wait_nccl(c, r, c->timeout_ms);
+    if (st != DT_OK) return st;
+    dt_tensor4 dst = o_full;
+    dst.ptr = reinterpret_cast<uint8_t*>(o_full.ptr) + (size_t)r0 * o_full.stride_s * es;
+    st = launch_permute_gathered(gath + gath_off, dst, c->world, B, rows, Hl, D, local->dtype, c->side);
+    if (st != DT_OK) return st;
+    stage_off += cbytes;
+    gath_off += cbytes * c->world;
+  }
+  DT_CUDA_TRY(cudaEventRecord(c->all_done, c->side));
+  DT_CUDA_TRY(cudaStreamWaitEvent(s, c->all_done, 0));
+  return DT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,76 @@
+// Shared declarations of the attention library: kernel launch prototypes and small device helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dtattn.h"
+
+namespace dt {
+
+// Per-device status word written by kernels whose bounded waits ran out (0 = healthy).
+// Codes: 1 = TMA/full barrier wait, 2 = empty-slot wait, 3 = S-ready wait, 4 = P-ready wait,
+//        5 = final-O wait.  The word keeps the first code stored.
+unsigned int* device_status_word();  // device pointer for the current device (allocated once)
+
+// Remember a failing cudaError_t for dt_last_cuda_error().
+int record_cuda_error(cudaError_t e);
+
+#define DT_CUDA_TRY(expr)                                   \
+  do {                                                      \
+    cudaError_t _e = (expr);                                \
+    if (_e != cudaSuccess) return dt::record_cuda_error(_e); \
+  } while (0)
+
+inline size_t dtype_size(int dtype) { return dtype == DT_F32 ? 4 : 2; }
+
+// ---- kernel entry points (each in its own .cu) --------------------------------------------------
+
+// CUDA-core flash kernel: any D <= 256, any dtype, mask, causal, GQA.  Fallback and second opinion.
+int launch_generic(const dt_sdpa_params& p, cudaStream_t stream);
+
+// Split-KV decode: Sq * (Hq/Hkv) <= 16 query rows per KV head, fp16/bf16, D in {64,128}.
+bool decode_supported(const dt_sdpa_params& p);
+size_t decode_workspace_bytes(const dt_sdpa_params& p);
+int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream);
+
+// TMA + tcgen05 flash attention: fp16/bf16, D in {64,128}, no mask.
+bool prefill_supported(const dt_sdpa_params& p);
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream);
+
+// [world][rows][Hl][D] -> [B,Sq,world*Hl,D]
+int launch_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D,
+                            int dtype, cudaStream_t stream);
+
+// ---- device helpers -----------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ float to_float(T x);
+template <>
+__device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace dt

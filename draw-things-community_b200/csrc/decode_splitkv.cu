@@ -1,0 +1,473 @@
+// Split-KV grouped-query decode attention (the KV-cache step of
+// Libraries/SwiftLLM/Sources/Models/Qwen3_5.swift:183-196: a few new query tokens over T cached rows).
+//
+// The path is bound by streaming the K and V cache once from HBM.  Layout in HBM is the reference's
+// cache layout [B, T, Hkv, D] (Qwen3_5TextGeneration.swift:1639-1655), so one KV head's rows are 2*D-byte
+// segments `stride_s` elements apart.
+//
+//   grid  = (splits, Hkv, B); one CTA streams a contiguous range of 16-key units of ONE KV head and
+//           serves all M = Sq * (Hq/Hkv) <= 16 query rows that read it, so K/V are read exactly once.
+//   CTA   = 4 consumer warps + 1 producer warp.  The producer issues TMA tile loads (boxes of
+//           16 keys x 64 dims, 128-byte swizzle, no multicast) into a ring of stages; each consumer warp
+//           owns one 16-key unit per stage: S^T = Q K^T and O += P V with mma.sync m16n8k16 (fp32
+//           accumulate) fed by ldmatrix from the swizzled tiles, online softmax in registers with
+//           warp-shuffle reductions.
+//   merge = the 4 warps' (m, l, O) are merged through shared memory; with more than one split the CTA
+//           writes an fp32 partial to the workspace and takes a ticket (atomicAdd); the CTA that draws
+//           the last ticket of its (batch, KV head) combines all partials.  Nothing waits on another
+//           CTA, so nothing can hang.
+#include <stdlib.h>
+
+#include "sm100_ptx.cuh"
+
+namespace dt {
+namespace {
+
+constexpr int kUnitKeys = 16;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kBoxBytes = kUnitKeys * 128;  // one TMA box: 16 keys x 64 dims x 2 B
+constexpr int kMaxRows = 16;
+
+template <int D>
+struct Cfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kWarpTileBytes = 2 * kHalves * kBoxBytes;  // K boxes then V boxes
+  static constexpr int kStageBytes = kConsumerWarps * kWarpTileBytes;
+  static constexpr int kStages = D == 128 ? 3 : 4;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct DecodeArgs {
+  const void* q;
+  void* o;
+  float* lse;
+  int64_t q_sb, q_ss, q_sh, o_sb, o_ss, o_sh;
+  unsigned int* counters;  // [B*Hkv]
+  float* part_ml;          // [B*Hkv][nsplit][M][2]
+  float* part_o;           // [B*Hkv][nsplit][M][D]
+  unsigned int* status;
+  int Sq, Sk, Hq, Hkv, G, M;
+  int nsplit, units_per_split, total_units;
+  float scale_log2;
+  int is_causal;
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
+  if (bf16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+  __half2 t = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const DecodeArgs a) {
+  using C = Cfg<D>;
+  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;
+  uint8_t* ring_ptr = smem_raw + (ring - raw);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring_ptr + C::kRingBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  __shared__ int s_abort;
+  __shared__ int s_is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int unit_begin = split * a.units_per_split;
+  const int unit_end = min(a.total_units, unit_begin + a.units_per_split);
+  const int n_units = max(0, unit_end - unit_begin);
+  const int n_stages = (n_units + kConsumerWarps - 1) / kConsumerWarps;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    s_is_last = 0;
+    for (int i = 0; i < C::kStages; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], kConsumerWarps);
+    }
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  // per-lane running state of rows lane/4 (lo) and lane/4 + 8 (hi)
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_k);
+      ptx::prefetch_tensormap(&map_v);
+      for (int st = 0; st < n_stages; ++st) {
+        const int slot = st % C::kStages;
+        if (st >= C::kStages) {
+          if (!ptx::mbar_wait(&empty_bar[slot], ((st / C::kStages) - 1) & 1, &s_abort)) {
+            atomicCAS(a.status, 0u, 2u);
+            s_abort = 1;
+            break;
+          }
+        }
+        const int u0 = unit_begin + st * kConsumerWarps;
+        const int nu = min(kConsumerWarps, unit_end - u0);
+        ptx::mbar_arrive_expect_tx(&full_bar[slot], (uint32_t)(nu * C::kWarpTileBytes));
+        for (int w = 0; w < nu; ++w) {
+          uint8_t* dst = ring_ptr + slot * C::kStageBytes + w * C::kWarpTileBytes;
+          const int key0 = (u0 + w) * kUnitKeys;
+#pragma unroll
+          for (int hf = 0; hf < C::kHalves; ++hf) {
+            ptx::tma_load_4d(dst + hf * kBoxBytes, &map_k, &full_bar[slot], hf * 64, kvh, key0, b);
+            ptx::tma_load_4d(dst + (C::kHalves + hf) * kBoxBytes, &map_v, &full_bar[slot], hf * 64, kvh, key0, b);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const int cq = (lane & 3) * 2;
+    // Q fragments (A operand, rows = (query token, group head), k = head dim)
+    uint32_t qa[D / 16][4];
+    {
+      const T* q = reinterpret_cast<const T*>(a.q);
+      const T* p_lo = nullptr;
+      const T* p_hi = nullptr;
+      if (r_lo < a.M) p_lo = q + b * a.q_sb + (int64_t)(r_lo / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_lo % a.G) * a.q_sh;
+      if (r_hi < a.M) p_hi = q + b * a.q_sb + (int64_t)(r_hi / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_hi % a.G) * a.q_sh;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qa[ks][0] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq) : 0u;
+        qa[ks][1] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq) : 0u;
+        qa[ks][2] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq + 8) : 0u;
+        qa[ks][3] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq + 8) : 0u;
+      }
+    }
+    // last visible key per row (inclusive)
+    const int off = a.Sk - a.Sq;
+    const int vis_lo = a.is_causal ? min(a.Sk - 1, r_lo / a.G + off) : a.Sk - 1;
+    const int vis_hi = a.is_causal ? min(a.Sk - 1, r_hi / a.G + off) : a.Sk - 1;
+
+    for (int st = 0; st < n_stages; ++st) {
+      const int slot = st % C::kStages;
+      if (!ptx::mbar_wait(&full_bar[slot], (st / C::kStages) & 1, &s_abort)) {
+        atomicCAS(a.status, 0u, 1u);
+        s_abort = 1;
+        break;
+      }
+      const int unit = unit_begin + st * kConsumerWarps + warp;
+      if (unit < unit_end) {
+        const uint32_t kbase = ring + slot * C::kStageBytes + warp * C::kWarpTileBytes;
+        const uint32_t vbase = kbase + C::kHalves * kBoxBytes;
+        const int key0 = unit * kUnitKeys;
+
+        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+          const int key = ((lane >> 4) << 3) + (lane & 7);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const int chunk = ks * 2 + ((lane >> 3) & 1);
+            const uint32_t addr = kbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+            uint32_t b00, b01, b10, b11;
+            ptx::ldmatrix_x4(b00, b01, b10, b11, addr);
+            ptx::mma_m16n8k16<kBf16>(sacc[0], qa[ks], b00, b01);
+            ptx::mma_m16n8k16<kBf16>(sacc[1], qa[ks], b10, b11);
+          }
+        }
+        // scale, mask, online softmax
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = key0 + nt * 8 + cq + e;
+            float s0 = sacc[nt][e] * a.scale_log2;
+            float s1 = sacc[nt][2 + e] * a.scale_log2;
+            if (j > vis_lo) s0 = -INFINITY;
+            if (j > vis_hi) s1 = -INFINITY;
+            sacc[nt][e] = s0;
+            sacc[nt][2 + e] = s1;
+            mx_lo = fmaxf(mx_lo, s0);
+            mx_hi = fmaxf(mx_hi, s1);
+          }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+        const float ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float al_lo = fast_exp2(m_lo - ms_lo), al_hi = fast_exp2(m_hi - ms_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float p0 = fast_exp2(sacc[nt][e] - ms_lo);
+            const float p1 = fast_exp2(sacc[nt][2 + e] - ms_hi);
+            sacc[nt][e] = p0;
+            sacc[nt][2 + e] = p1;
+            ps_lo += p0;
+            ps_hi += p1;
+          }
+        }
+        l_lo = l_lo * al_lo + ps_lo;
+        l_hi = l_hi * al_hi + ps_hi;
+        uint32_t pa[4];
+        pa[0] = pack2(sacc[0][0], sacc[0][1], kBf16);
+        pa[1] = pack2(sacc[0][2], sacc[0][3], kBf16);
+        pa[2] = pack2(sacc[1][0], sacc[1][1], kBf16);
+        pa[3] = pack2(sacc[1][2], sacc[1][3], kBf16);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          oacc[i][0] *= al_lo;
+          oacc[i][1] *= al_lo;
+          oacc[i][2] *= al_hi;
+          oacc[i][3] *= al_hi;
+        }
+        {
+          const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+          for (int dp = 0; dp < D / 16; ++dp) {
+            const int chunk = dp * 2 + (lane >> 4);
+            const uint32_t addr = vbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+            uint32_t v00, v01, v10, v11;
+            ptx::ldmatrix_x4_trans(v00, v01, v10, v11, addr);
+            ptx::mma_m16n8k16<kBf16>(oacc[2 * dp], pa, v00, v01);
+            ptx::mma_m16n8k16<kBf16>(oacc[2 * dp + 1], pa, v10, v11);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  }
+
+  // ---------------- merge the consumer warps through shared memory (ring is idle now) ----------------
+  __syncthreads();
+  float* obuf = reinterpret_cast<float*>(ring_ptr);                    // [4][16][D]
+  float* mbuf = obuf + kConsumerWarps * kMaxRows * D;                  // [4][16]
+  float* lbuf = mbuf + kConsumerWarps * kMaxRows;                      // [4][16]
+  if (warp < kConsumerWarps) {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8, cq = (lane & 3) * 2;
+    float* ob = obuf + warp * kMaxRows * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      ob[r_lo * D + i * 8 + cq] = oacc[i][0];
+      ob[r_lo * D + i * 8 + cq + 1] = oacc[i][1];
+      ob[r_hi * D + i * 8 + cq] = oacc[i][2];
+      ob[r_hi * D + i * 8 + cq + 1] = oacc[i][3];
+    }
+    if ((lane & 3) == 0) {
+      mbuf[warp * kMaxRows + r_lo] = m_lo;
+      mbuf[warp * kMaxRows + r_hi] = m_hi;
+      lbuf[warp * kMaxRows + r_lo] = l_lo;
+      lbuf[warp * kMaxRows + r_hi] = l_hi;
+    }
+  }
+  __syncthreads();
+
+  const int pair = b * a.Hkv + kvh;
+  T* o = reinterpret_cast<T*>(a.o);
+  for (int idx = threadIdx.x; idx < a.M * D; idx += kThreads) {
+    const int r = idx / D, d = idx - r * D;
+    float mstar = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) mstar = fmaxf(mstar, mbuf[w * kMaxRows + r]);
+    float lt = 0.f, ot = 0.f;
+    if (mstar != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float wgt = fast_exp2(mbuf[w * kMaxRows + r] - mstar);
+        lt += wgt * lbuf[w * kMaxRows + r];
+        ot += wgt * obuf[(w * kMaxRows + r) * D + d];
+      }
+    }
+    if (a.nsplit == 1) {
+      const int sq = r / a.G, h = kvh * a.G + r % a.G;
+      o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
+      if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+    } else {
+      const int64_t slot = (int64_t)pair * a.nsplit + split;
+      a.part_o[slot * a.M * D + idx] = ot;
+      if (d == 0) {
+        a.part_ml[(slot * a.M + r) * 2] = mstar;
+        a.part_ml[(slot * a.M + r) * 2 + 1] = lt;
+      }
+    }
+  }
+  if (a.nsplit == 1) return;
+
+  // ---------------- ticket: the last CTA of this (batch, KV head) combines ----------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(&a.counters[pair], 1u);
+    s_is_last = (ticket == (unsigned int)(a.nsplit - 1));
+  }
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < a.M * D; idx += kThreads) {
+    const int r = idx / D, d = idx - r * D;
+    const int64_t base = (int64_t)pair * a.nsplit;
+    float mstar = -INFINITY;
+    for (int s = 0; s < a.nsplit; ++s) mstar = fmaxf(mstar, __ldcg(&a.part_ml[((base + s) * a.M + r) * 2]));
+    float lt = 0.f, ot = 0.f;
+    if (mstar != -INFINITY) {
+      for (int s = 0; s < a.nsplit; ++s) {
+        const float wgt = fast_exp2(__ldcg(&a.part_ml[((base + s) * a.M + r) * 2]) - mstar);
+        lt += wgt * __ldcg(&a.part_ml[((base + s) * a.M + r) * 2 + 1]);
+        ot += wgt * __ldcg(&a.part_o[(base + s) * a.M * D + idx]);
+      }
+    }
+    const int sq = r / a.G, h = kvh * a.G + r % a.G;
+    o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
+    if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+  }
+  if (threadIdx.x == 0) a.counters[pair] = 0u;  // leave the workspace ready for the next call
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+struct Plan {
+  int nsplit, units_per_split, total_units;
+};
+
+// Pick the split count that minimises the modelled time: CTAs run `occ` per SM; each costs its units
+// plus a fixed start-up; a last partial round costs as much as its fullest SM.
+Plan make_plan(const dt_sdpa_params& p) {
+  Plan pl;
+  pl.total_units = (p.Sk + kUnitKeys - 1) / kUnitKeys;
+  const int pairs = p.B * p.Hkv;
+  const int sms = sm_count();
+  const int occ = 2;
+  const char* env = getenv("DTATTN_DECODE_SPLITS");
+  int forced = env ? atoi(env) : 0;
+  double best = 1e30;
+  int best_ups = pl.total_units;
+  const int max_split = pl.total_units < 128 ? pl.total_units : 128;
+  for (int ns = 1; ns <= max_split; ++ns) {
+    const int ups = (pl.total_units + ns - 1) / ns;
+    const int ns_eff = (pl.total_units + ups - 1) / ups;
+    if (forced > 0) {
+      if (ns == forced || ns == max_split) { best_ups = ups; break; }
+      continue;
+    }
+    const long long ctas = (long long)pairs * ns_eff;
+    const long long full = ctas / ((long long)sms * occ), rem = ctas % ((long long)sms * occ);
+    const double rounds = (double)full * occ + (double)((rem + sms - 1) / sms);
+    const double cost = rounds * (ups + 3.0) + 0.02 * ns_eff;
+    if (cost < best - 1e-9) {
+      best = cost;
+      best_ups = ups;
+    }
+  }
+  pl.units_per_split = best_ups;
+  pl.nsplit = (pl.total_units + best_ups - 1) / best_ups;
+  return pl;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+template <typename T, int D>
+int launch_t(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
+  using C = Cfg<D>;
+  const Plan pl = make_plan(p);
+  const int G = p.Hq / p.Hkv, M = p.Sq * G;
+  const size_t pairs = (size_t)p.B * p.Hkv;
+  DecodeArgs a{};
+  if (pl.nsplit > 1) {
+    const size_t need = decode_workspace_bytes(p);
+    if (!workspace || bytes < need) return DT_WORKSPACE;
+    uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
+    a.counters = reinterpret_cast<unsigned int*>(w);
+    size_t off = align_up(pairs * sizeof(unsigned int), 256);
+    a.part_ml = reinterpret_cast<float*>(w + off);
+    off += align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256);
+    a.part_o = reinterpret_cast<float*>(w + off);
+  }
+  CUtensorMap mk, mv;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
+  a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
+  a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
+  a.status = device_status_word();
+  if (!a.status) return DT_CUDA;
+  a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
+  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
+  a.scale_log2 = p.scale * kLog2e;
+  a.is_causal = p.is_causal;
+  auto kern = decode_splitkv_kernel<T, D>;
+  static bool attr_set = false;  // per (T, D) instantiation
+  if (!attr_set) {
+    DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    attr_set = true;
+  }
+  dim3 grid(pl.nsplit, p.Hkv, p.B);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mk, mv, a);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace
+
+bool decode_supported(const dt_sdpa_params& p) {
+  if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
+  if (p.D != 64 && p.D != 128) return false;
+  if (p.mask) return false;
+  if (p.Hq % p.Hkv) return false;
+  const int M = p.Sq * (p.Hq / p.Hkv);
+  if (M > kMaxRows) return false;
+  if (p.Hkv > 65535 || p.B > 65535) return false;
+  // TMA and 32-bit fragment loads: 16-byte aligned bases, strides multiples of 8 elements
+  auto ok = [](const dt_tensor4& t) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && t.stride_b % 8 == 0 && t.stride_s % 8 == 0 &&
+           t.stride_h % 8 == 0;
+  };
+  return ok(p.q) && ok(p.k) && ok(p.v);
+}
+
+size_t decode_workspace_bytes(const dt_sdpa_params& p) {
+  const Plan pl = make_plan(p);
+  if (pl.nsplit <= 1) return 0;
+  const size_t pairs = (size_t)p.B * p.Hkv;
+  const size_t M = (size_t)p.Sq * (p.Hq / p.Hkv);
+  return align_up(pairs * sizeof(unsigned int), 256) + align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256) +
+         align_up(pairs * pl.nsplit * M * p.D * sizeof(float), 256);
+}
+
+int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
+  if (p.dtype == DT_F16) {
+    return p.D == 128 ? launch_t<__half, 128>(p, workspace, bytes, stream) : launch_t<__half, 64>(p, workspace, bytes, stream);
+  }
+  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, workspace, bytes, stream)
+                    : launch_t<__nv_bfloat16, 64>(p, workspace, bytes, stream);
+}
+
+}  // namespace dt

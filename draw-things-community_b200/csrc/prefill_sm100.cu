@@ -1,0 +1,453 @@
+// Flash-attention forward for sm_100a: TMA-staged Q/K/V tiles, tcgen05.mma with TMEM accumulators,
+// warp-specialised online softmax.  Serves the diffusion shapes of the reference
+// (Libraries/SwiftDiffusion/Sources/Models/Flux1.swift:224-232 joint attention, Wan.swift:95-131 video
+// self-attention, UNetXL.swift:67-185 cross-attention): fp16/bf16 I/O, fp32 accumulation, head dim 64 or
+// 128, grouped KV heads, optional bottom-right causal mask, BSHD strided views.
+//
+// One CTA = one (batch, head, pair of 128-row query tiles).  12 warps:
+//   warp 0      TMA producer: Q tiles once, then K(j), V(j) blocks of 128 keys through a ring of slots
+//   warp 1      MMA issuer (one thread): S_t = Q_t K(j)^T  (operands in shared memory) and
+//               O_t += P_t V(j) (P read from TMEM, V from shared memory), interleaved over the two tiles so
+//               that the tensor pipe works on one tile while the other tile's softmax runs
+//   warp 2      TMEM allocation / release
+//   warps 4-7   softmax of tile 0: one thread per query row; reads its S row from TMEM, keeps the running
+//               max / sum, rescales O in TMEM only when the max grew by more than 2^8 (the final 1/l
+//               normalisation makes the result independent of that choice), writes P as 16-bit back to
+//               TMEM over the S columns, and at the end normalises O and stores it
+//   warps 8-11  the same for tile 1
+// TMEM (512 columns x 128 lanes, fp32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+// Every mbarrier wait is bounded; a wait that runs out stores a code into the device status word and the
+// CTA unwinds (TMEM is released on that path too).
+#include <stdlib.h>
+
+#include <type_traits>
+
+#include "sm100_ptx.cuh"
+
+namespace dt {
+namespace {
+
+constexpr int kBM = 128;       // query rows per tile
+constexpr int kBN = 128;       // keys per block
+constexpr int kThreads = 384;
+constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 x 16-bit] = 16 KB, one TMA box
+constexpr float kRescaleThreshold = 8.f;
+// 128 * kRegsLow + 256 * kRegsHigh must not exceed what the CTA was launched with (384 threads * 168)
+constexpr int kRegsLow = 56, kRegsHigh = 224;
+
+template <int D>
+struct Cfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kTileBytes = kHalves * kHalfBytes;  // one Q tile / one K block / one V block
+  static constexpr int kSlots = D == 128 ? 5 : 8;
+  static constexpr int kQBytes = 2 * kTileBytes;
+  static constexpr int kRingBytes = kSlots * kTileBytes;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kSmemBytes = kQBytes + kRingBytes + kBarBytes + 1024;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+};
+
+struct PrefillArgs {
+  void* o;
+  float* lse;
+  float* dbg;  // optional [2][128][128] fp32 dump of the first S block of CTA (0,0,0)
+  int64_t o_sb, o_ss, o_sh;
+  unsigned int* status;
+  int Sq, Sk, Hq, Hkv;
+  float scale_log2;
+  int is_causal;
+  int options;  // bit 0: issue P*V as D/64 MMAs of N = 64 instead of one of N = D
+};
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t kv_full[8];
+  uint64_t kv_empty[8];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if constexpr (std::is_same<T, __half>::value) {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
+  using C = Cfg<D>;
+  constexpr int kBf16 = std::is_same<T, __half>::value ? 0 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t q_smem = base;
+  const uint32_t ring_smem = base + C::kQBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int kvh = h / (a.Hq / a.Hkv);
+  const int q0 = blockIdx.x * (2 * kBM);
+  const bool two = q0 + kBM < a.Sq;  // is the second query tile non-empty
+  const int off = a.Sk - a.Sq;       // causal: key j visible to query i iff j <= i + off
+  // number of key blocks this CTA visits
+  int nkv = (a.Sk + kBN - 1) / kBN;
+  if (a.is_causal) {
+    const int last_row = min(a.Sq, q0 + 2 * kBM) - 1;
+    const long long lim = (long long)last_row + off + 1;  // keys [0, lim) can be visible
+    const int need = (int)((max(0LL, min((long long)a.Sk, lim)) + kBN - 1) / kBN);
+    nkv = max(1, min(nkv, need));
+  }
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bars->q_full, 1);
+    for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(&bars->s_full[t], 1);
+      ptx::mbar_init(&bars->p_full[t], 128);
+    }
+    for (int i = 0; i < C::kSlots; ++i) {
+      ptx::mbar_init(&bars->kv_full[i], 1);
+      ptx::mbar_init(&bars->kv_empty[i], 1);
+    }
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(&bars->tmem_base, C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  // Register budget: the data-movement warpgroup gives registers back, the softmax warpgroups take them.
+  // (Each setmaxnreg must dominate the code it governs, hence the nesting.)
+  if (warp < 4) {
+  ptx::setmaxnreg_dec<kRegsLow>();
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_q);
+      ptx::prefetch_tensormap(&map_k);
+      ptx::prefetch_tensormap(&map_v);
+      ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)((two ? 2 : 1) * C::kTileBytes));
+      for (int t = 0; t < (two ? 2 : 1); ++t)
+#pragma unroll
+        for (int hf = 0; hf < C::kHalves; ++hf)
+          ptx::tma_load_4d(base_ptr + t * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full, hf * 64, h,
+                           q0 + t * kBM, b);
+      bool ok = true;
+      for (int it = 0; it < 2 * nkv && ok; ++it) {
+        const int slot = it % C::kSlots, use = it / C::kSlots;
+        if (use > 0 && !ptx::mbar_wait(&bars->kv_empty[slot], (use - 1) & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 2u);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        const int j = it >> 1;
+        const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
+        ptx::mbar_arrive_expect_tx(&bars->kv_full[slot], (uint32_t)C::kTileBytes);
+#pragma unroll
+        for (int hf = 0; hf < C::kHalves; ++hf)
+          ptx::tma_load_4d(base_ptr + C::kQBytes + slot * C::kTileBytes + hf * kHalfBytes, map, &bars->kv_full[slot],
+                           hf * 64, kvh, j * kBN, b);
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kBM, kBN, 0, 0);
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kBM, D, 0, 1);
+      constexpr uint32_t idesc_pv64 = ptx::make_idesc_f16(kBf16, kBM, 64, 0, 1);
+      const uint32_t col_s[2] = {tmem + C::kColS0, tmem + C::kColS1};
+      const uint32_t col_o[2] = {tmem + C::kColO0, tmem + C::kColO1};
+      const int ntile = two ? 2 : 1;
+      bool ok = true;
+
+      auto slot_addr = [&](int it) { return ring_smem + (it % C::kSlots) * C::kTileBytes; };
+      auto wait_full = [&](int it) {
+        if (!ptx::mbar_wait(&bars->kv_full[it % C::kSlots], (it / C::kSlots) & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 1u);
+          *abort_flag = 1;
+          return false;
+        }
+        return true;
+      };
+      // Descriptors differ only in the 14-bit start-address field, so stepping through a tile is one add.
+      const uint64_t desc_k_major = ptx::make_smem_desc_sw128(0, 16, 1024);            // Q, K
+      const uint64_t desc_mn_major = ptx::make_smem_desc_sw128(0, kHalfBytes, 1024);   // V
+      auto addr_field = [](uint32_t smem_addr) { return (uint64_t)((smem_addr & 0x3FFFFu) >> 4); };
+      // S_t = Q_t K^T : both operands K-major, 128-byte swizzle, D/16 steps of k = 16
+      auto issue_qk = [&](int t, uint32_t k_addr) {
+        const uint64_t ad0 = desc_k_major | addr_field(q_smem + t * C::kTileBytes);
+        const uint64_t bd0 = desc_k_major | addr_field(k_addr);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t o = (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+          ptx::mma_ss(col_s[t], ad0 + o, bd0 + o, idesc_qk, ks > 0 ? 1u : 0u);
+        }
+      };
+      // O_t (+)= P_t V : P from TMEM (two 16-bit keys per 32-bit column), V is [key][d] = MN-major
+      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate, int ksteps) {
+        const uint64_t bd0 = desc_mn_major | addr_field(v_addr);
+#pragma unroll 1
+        for (int kk = 0; kk < ksteps; ++kk) {
+          const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
+          const uint64_t bd = bd0 + (uint64_t)(kk * (2048 >> 4));
+          if (a.options & 1) {
+#pragma unroll
+            for (int hf = 0; hf < C::kHalves; ++hf)
+              ptx::mma_ts(col_o[t] + hf * 64, col_s[t] + kk * 8, bd + (uint64_t)(hf * (kHalfBytes >> 4)), idesc_pv64, acc);
+          } else {
+            ptx::mma_ts(col_o[t], col_s[t] + kk * 8, bd, idesc_pv, acc);
+          }
+        }
+      };
+
+      if (!ptx::mbar_wait(&bars->q_full, 0, abort_flag)) {
+        atomicCAS(a.status, 0u, 1u);
+        *abort_flag = 1;
+        ok = false;
+      }
+      if (ok && wait_full(0)) {
+        ptx::tc_fence_after();
+        for (int t = 0; t < ntile; ++t) {
+          issue_qk(t, slot_addr(0));
+          ptx::tc_commit(&bars->s_full[t]);
+        }
+        ptx::tc_commit(&bars->kv_empty[0]);
+      } else {
+        ok = false;
+      }
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int it_v = 2 * j + 1, it_kn = 2 * j + 2;
+        const bool more = j + 1 < nkv;
+        const int valid = min(kBN, a.Sk - j * kBN);
+        const int ksteps = (valid + 15) >> 4;
+        if (!wait_full(it_v)) { ok = false; break; }
+        if (more && !wait_full(it_kn)) { ok = false; break; }
+        for (int t = 0; t < ntile; ++t) {
+          if (!ptx::mbar_wait(&bars->p_full[t], j & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 4u);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          issue_pv(t, slot_addr(it_v), j > 0, ksteps);
+          if (t == ntile - 1) ptx::tc_commit(&bars->kv_empty[it_v % C::kSlots]);
+          if (more) issue_qk(t, slot_addr(it_kn));
+          ptx::tc_commit(&bars->s_full[t]);  // next S ready, or (last block) O complete
+          if (more && t == ntile - 1) ptx::tc_commit(&bars->kv_empty[it_kn % C::kSlots]);
+        }
+      }
+    }
+  }
+  } else {
+    ptx::setmaxnreg_inc<kRegsHigh>();
+    // =========================== softmax / correction / epilogue ===========================
+    const int t = (warp - 4) >> 2;  // tile
+    if (t == 0 || two) {
+      const int row_in_tile = ((warp & 3) << 5) + lane;
+      const int row = q0 + t * kBM + row_in_tile;
+      const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
+      const uint32_t t_s = tmem + (t ? C::kColS1 : C::kColS0) + lane_addr;
+      const uint32_t t_o = tmem + (t ? C::kColO1 : C::kColO0) + lane_addr;
+      const long long vis = a.is_causal ? (long long)row + off : (long long)a.Sk;  // last visible key
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+
+      for (int j = 0; j < nkv; ++j) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], j & 1, abort_flag))) {
+          atomicCAS(a.status, 0u, 3u);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        uint32_t s[4][32];
+        ptx::tmem_ld32(t_s + 0, s[0]);
+        ptx::tmem_ld32(t_s + 32, s[1]);
+        ptx::tmem_ld32(t_s + 64, s[2]);
+        ptx::tmem_ld32(t_s + 96, s[3]);
+        ptx::tc_wait_ld();
+
+        if (a.dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          float* dst = a.dbg + ((size_t)t * kBM + row_in_tile) * kBN;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dst[c * 32 + i] = __uint_as_float(s[c][i]);
+        }
+
+        const int key0 = j * kBN;
+        const bool need_mask = (key0 + kBN > a.Sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis);
+        if (need_mask) {
+          const long long lim = min((long long)a.Sk - 1, vis);  // keys <= lim visible
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if ((long long)(key0 + c * 32 + i) > lim) s[c][i] = 0xff800000u;  // -inf
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+        mx *= a.scale_log2;  // scale > 0 is a precondition of this kernel
+        const float m_cand = fmaxf(m_used, mx);
+        // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
+        const bool grow = (m_cand - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_cand != -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = grow ? m_cand : m_used;
+          const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
+          l *= alpha;
+          m_used = m_new;
+          if (j > 0) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t ov[32];
+              ptx::tmem_ld32(t_o + c * 32, ov);
+              ptx::tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              ptx::tmem_st32(t_o + c * 32, ov);
+            }
+          }
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i]), a.scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 1]), a.scale_log2, neg_m));
+            l += p0 + p1;
+            pk[i] = pack_pair<T>(p0, p1);
+          }
+          ptx::tmem_st16(t_s + c * 16, pk);
+        }
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&bars->p_full[t]);
+      }
+
+      // ---- epilogue: O / l -> global ----
+      if (ok && __all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], nkv & 1, abort_flag))) {
+        ptx::tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* orow = reinterpret_cast<T*>(a.o) + b * a.o_sb + (int64_t)row * a.o_ss + (int64_t)h * a.o_sh;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          ptx::tmem_ld32(t_o + c * 32, ov);
+          ptx::tc_wait_ld();
+          if (row < a.Sq) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack_pair<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
+              pk.y = pack_pair<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
+              pk.z = pack_pair<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
+              pk.w = pack_pair<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pk;
+            }
+          }
+        }
+        if (a.lse && row < a.Sq)
+          a.lse[((int64_t)b * a.Hq + h) * a.Sq + row] = l > 0.f ? m_used * kLn2 + logf(l) : -INFINITY;
+      } else if (ok) {
+        atomicCAS(a.status, 0u, 5u);
+        *abort_flag = 1;
+      }
+    }
+  }
+
+  // =========================== teardown ===========================
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+int g_options = 0;
+float* g_dbg = nullptr;
+
+template <typename T, int D>
+int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
+  using C = Cfg<D>;
+  CUtensorMap mq, mk, mv;
+  if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, D, p.dtype, kBM)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
+  PrefillArgs a{};
+  a.o = p.o.ptr;
+  a.lse = p.lse;
+  a.dbg = g_dbg;
+  a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
+  a.status = device_status_word();
+  if (!a.status) return DT_CUDA;
+  a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv;
+  a.scale_log2 = p.scale * kLog2e;
+  a.is_causal = p.is_causal;
+  a.options = g_options;
+  auto kern = prefill_tcgen05_kernel<T, D>;
+  DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  dim3 grid((p.Sq + 2 * kBM - 1) / (2 * kBM), p.Hq, p.B);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, a);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace
+
+bool prefill_supported(const dt_sdpa_params& p) {
+  if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
+  if (p.D != 64 && p.D != 128) return false;
+  if (p.mask) return false;
+  if (!(p.scale > 0.f)) return false;
+  if (p.Hq % p.Hkv) return false;
+  if (p.Hq > 65535 || p.B > 65535) return false;
+  if (p.is_causal && p.Sq > p.Sk) return false;  // rows without any visible key: left to the generic kernel
+  auto ok = [](const dt_tensor4& t) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && t.stride_b % 8 == 0 && t.stride_s % 8 == 0 &&
+           t.stride_h % 8 == 0;
+  };
+  return ok(p.q) && ok(p.k) && ok(p.v) && ok(p.o);
+}
+
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream) {
+  if (p.dtype == DT_F16)
+    return p.D == 128 ? launch_t<__half, 128>(p, stream) : launch_t<__half, 64>(p, stream);
+  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, stream) : launch_t<__nv_bfloat16, 64>(p, stream);
+}
+
+}  // namespace dt
+
+// Test hooks (not part of the public header): kernel variant bits and the S-dump buffer.
+extern "C" int dt_internal_set_prefill_options(int options) {
+  dt::g_options = options;
+  return 0;
+}
+extern "C" int dt_internal_set_prefill_dump(float* device_buffer) {
+  dt::g_dbg = device_buffer;
+  return 0;
+}

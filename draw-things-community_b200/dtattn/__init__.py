@@ -1,0 +1,287 @@
+"""ctypes binding of libdtattn.so and a Python mirror of the reference's operator surface.
+
+The reference builds attention as a graph node::
+
+    ScaledDotProductAttention(scale: 1.0 / Float(k).squareRoot(), isCausal: true, flags: [.Float16])(
+        queries, keys, values)                       # Libraries/SwiftLLM/Sources/Models/Qwen3_5.swift:193-196
+
+and this module offers the same call shape on torch tensors (used as plain device/host buffers)::
+
+    ScaledDotProductAttention(scale=k ** -0.5, is_causal=True, flags=[GEMMFlag.Float16])(queries, keys, values)
+
+Everything goes through the C ABI in include/dtattn.h.  There is no fallback: if the shared library is
+missing, or the tensors are CUDA tensors and the kernels cannot run, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "..", "lib", "libdtattn.so")
+
+DT_OK, DT_BAD_ARG, DT_UNSUPPORTED, DT_WORKSPACE, DT_CUDA, DT_NCCL, DT_TIMEOUT, DT_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6, -7
+DT_F16, DT_BF16, DT_F32 = 0, 1, 2
+DT_FLAG_FP16_ACCUM_HINT, DT_FLAG_FORCE_GENERIC = 1, 2
+_DTYPES = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
+
+
+class Tensor4(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("stride_b", ctypes.c_int64), ("stride_s", ctypes.c_int64),
+                ("stride_h", ctypes.c_int64)]
+
+
+class SdpaParams(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("Sq", ctypes.c_int32), ("Sk", ctypes.c_int32), ("Hq", ctypes.c_int32),
+                ("Hkv", ctypes.c_int32), ("D", ctypes.c_int32), ("dtype", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("is_causal", ctypes.c_int32), ("flags", ctypes.c_uint32),
+                ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4),
+                ("mask", ctypes.c_void_p), ("mask_stride_b", ctypes.c_int64), ("mask_stride_h", ctypes.c_int64),
+                ("mask_stride_q", ctypes.c_int64), ("lse", ctypes.c_void_p)]
+
+
+class DtError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        super().__init__(f"{what}: {status_string(status)} ({status})")
+
+
+_lib = None
+
+# every symbol include/dtattn.h declares: (name, restype, argtypes)
+_P = ctypes.POINTER
+SYMBOLS = [
+    ("dt_status_string", ctypes.c_char_p, [ctypes.c_int]),
+    ("dt_last_cuda_error", ctypes.c_int, []),
+    ("dt_abi_version", ctypes.c_int, []),
+    ("dt_sdpa_workspace_size", ctypes.c_int, [_P(SdpaParams), _P(ctypes.c_size_t)]),
+    ("dt_sdpa_workspace_init", ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    ("dt_sdpa_forward", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    ("dt_sdpa_kernel_name", ctypes.c_int, [_P(SdpaParams), _P(ctypes.c_char_p)]),
+    ("dt_sdpa_forward_host", ctypes.c_int, [_P(SdpaParams)]),
+    ("dt_host_release", ctypes.c_int, []),
+    ("dt_device_status", ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int)]),
+    ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
+    ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
+    ("dt_comm_destroy", ctypes.c_int, [ctypes.c_void_p]),
+    ("dt_sdpa_headsharded_workspace_size", ctypes.c_int, [_P(SdpaParams), ctypes.c_int, ctypes.c_int, _P(ctypes.c_size_t)]),
+    ("dt_sdpa_forward_headsharded", ctypes.c_int,
+     [ctypes.c_void_p, _P(SdpaParams), Tensor4, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    ("dt_permute_gathered", ctypes.c_int,
+     [ctypes.c_void_p, Tensor4, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+      ctypes.c_void_p]),
+]
+
+
+def lib():
+    """The loaded library.  Raises (never falls back) when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} not found: build it with `python draw-things-community_b200/build.py`")
+        _lib = ctypes.CDLL(os.path.abspath(LIB_PATH))
+        for name, res, args in SYMBOLS:
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+def status_string(status):
+    return lib().dt_status_string(int(status)).decode()
+
+
+def _check(status, what):
+    if status != DT_OK:
+        raise DtError(status, what)
+
+
+def _view4(t: torch.Tensor) -> Tensor4:
+    assert t.dim() == 4 and (t.stride(3) == 1 or t.shape[3] == 1), "expect a [B,S,H,D] view with contiguous D"
+    return Tensor4(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def make_params(q, k, v, o, scale, is_causal=False, mask=None, lse=None, flags=0) -> SdpaParams:
+    B, Sq, Hq, D = q.shape
+    _, Sk, Hkv, _ = k.shape
+    p = SdpaParams()
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D = B, Sq, Sk, Hq, Hkv, D
+    p.dtype = _DTYPES[q.dtype]
+    p.scale = float(scale)
+    p.is_causal = int(bool(is_causal))
+    p.flags = int(flags)
+    p.q, p.k, p.v, p.o = _view4(q), _view4(k), _view4(v), _view4(o)
+    if mask is not None:
+        assert mask.dtype == q.dtype and mask.dim() == 4 and mask.shape[2] == Sq and mask.shape[3] == Sk
+        assert mask.stride(3) == 1 or Sk == 1
+        p.mask = mask.data_ptr()
+        p.mask_stride_b = mask.stride(0) if mask.shape[0] > 1 else 0
+        p.mask_stride_h = mask.stride(1) if mask.shape[1] > 1 else 0
+        p.mask_stride_q = mask.stride(2)
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, Hq, Sq)
+        p.lse = lse.data_ptr()
+    return p
+
+
+def kernel_name(p: SdpaParams) -> str:
+    name = ctypes.c_char_p()
+    _check(lib().dt_sdpa_kernel_name(ctypes.byref(p), ctypes.byref(name)), "dt_sdpa_kernel_name")
+    return name.value.decode()
+
+
+def workspace_size(p: SdpaParams) -> int:
+    n = ctypes.c_size_t(0)
+    _check(lib().dt_sdpa_workspace_size(ctypes.byref(p), ctypes.byref(n)), "dt_sdpa_workspace_size")
+    return n.value
+
+
+def device_status(stream=None) -> int:
+    """Read and clear the device status word (0 = healthy)."""
+    code = ctypes.c_int(0)
+    s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+    st = lib().dt_device_status(ctypes.c_void_p(s), ctypes.byref(code))
+    if st not in (DT_OK, DT_TIMEOUT):
+        raise DtError(st, "dt_device_status")
+    return code.value
+
+
+class Workspace:
+    """Caller-owned scratch for dt_sdpa_forward, grown on demand and zero-initialised when (re)allocated."""
+
+    def __init__(self, device):
+        self.device = device
+        self.buf = None
+
+    def ensure(self, nbytes, stream):
+        if nbytes == 0:
+            return None, 0
+        if self.buf is None or self.buf.numel() < nbytes:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            _check(lib().dt_sdpa_workspace_init(ctypes.c_void_p(self.buf.data_ptr()), self.buf.numel(),
+                                                ctypes.c_void_p(stream)), "dt_sdpa_workspace_init")
+        return self.buf.data_ptr(), self.buf.numel()
+
+
+def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None, flags=0, workspace=None,
+                 stream=None):
+    """O = softmax(scale * Q K^T [+mask] [causal]) V through the C ABI.
+
+    CUDA tensors -> dt_sdpa_forward on the current (or given) stream; CPU tensors -> dt_sdpa_forward_host,
+    which stages through device memory (the end-to-end path).
+    """
+    B, Sq, Hq, D = q.shape
+    if out is None:
+        out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
+    p = make_params(q, k, v, out, scale, is_causal, mask, lse, flags)
+    if q.is_cuda:
+        s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+        ws = workspace if workspace is not None else _default_workspace(q.device)
+        ptr, nbytes = ws.ensure(workspace_size(p), s)
+        _check(lib().dt_sdpa_forward(ctypes.byref(p), ctypes.c_void_p(ptr) if ptr else None, nbytes,
+                                     ctypes.c_void_p(s)), "dt_sdpa_forward")
+    else:
+        _check(lib().dt_sdpa_forward_host(ctypes.byref(p)), "dt_sdpa_forward_host")
+    return out
+
+
+_workspaces = {}
+
+
+def _default_workspace(device):
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _workspaces:
+        _workspaces[key] = Workspace(device)
+    return _workspaces[key]
+
+
+# --------------------------------------------------------------------------------------------------
+# Mirror of the reference operator
+# --------------------------------------------------------------------------------------------------
+
+class GEMMFlag(enum.Flag):
+    """Functional.GEMMFlag as passed by the reference's call sites (UNet.swift:124, Flux1.swift:229-231)."""
+    NONE = 0
+    Float16 = 1   # half-precision accumulation allowed; this library always accumulates in fp32
+    Float32 = 2
+    Int8 = 4      # quantised-attention hint; only selected on Metal in the reference (DeviceCapability.swift:132-146)
+
+
+class ScaledDotProductAttention:
+    """NNC.ScaledDotProductAttention(scale:isCausal:hasAttentionMask:flags:multiHeadOutputProjectionFused:name:).
+
+    Argument meaning follows the reference call sites:
+      scale                 multiplies Q.K^T (1 for FlashAttentionLevel.scale1, 1/sqrt(k) for .scaleMerged)
+      is_causal             bottom-right aligned causal mask (Qwen3_5.swift:193-196)
+      has_attention_mask    a 4th input [B|1, H|1, Sq, Sk] is added to the scores (CLIPTextModel.swift:46-51)
+      flags                 GEMMFlag set; accepted for signature parity
+      multi_head_output_projection_fused
+                            the reference fuses the output Dense into the op (UNet.swift:122-130); not built
+                            here -> the constructor raises, as the reference would on an unsupported back end
+    Like the reference, misuse is a hard error (the reference traps with precondition/fatalError).
+    """
+
+    def __init__(self, scale, is_causal=False, has_attention_mask=False, flags=(), multi_head_output_projection_fused=False,
+                 name=""):
+        if multi_head_output_projection_fused:
+            raise NotImplementedError("multiHeadOutputProjectionFused is outside this library's scope")
+        self.scale = float(scale)
+        self.is_causal = bool(is_causal)
+        self.has_attention_mask = bool(has_attention_mask)
+        self.name = name
+        f = GEMMFlag.NONE
+        for x in (flags if isinstance(flags, (list, tuple, set)) else [flags]):
+            f |= x
+        self.flags = f
+        if GEMMFlag.Int8 in f:
+            raise NotImplementedError("quantised attention ([.Int8, .Float16]) is never selected off Metal")
+
+    def __call__(self, queries, keys, values, mask=None, *, out=None, lse=None):
+        if self.has_attention_mask != (mask is not None):
+            raise ValueError("hasAttentionMask and the number of inputs disagree")
+        abi_flags = DT_FLAG_FP16_ACCUM_HINT if GEMMFlag.Float16 in self.flags else 0
+        return sdpa_forward(queries, keys, values, self.scale, self.is_causal, mask, out=out, lse=lse, flags=abi_flags)
+
+
+# --------------------------------------------------------------------------------------------------
+# Head-sharded multi-GPU
+# --------------------------------------------------------------------------------------------------
+
+class HeadShardedComm:
+    """One communicator per process (one process per GPU).  `store_bcast(bytes|None) -> bytes` ships rank 0's
+    128-byte id to every rank (torch.distributed's broadcast_object_list does)."""
+
+    def __init__(self, rank, world, store_bcast, timeout_ms=60000):
+        self.rank, self.world = rank, world
+        ident = None
+        if rank == 0:
+            buf = ctypes.create_string_buffer(128)
+            _check(lib().dt_comm_unique_id(buf), "dt_comm_unique_id")
+            ident = buf.raw
+        ident = store_bcast(ident)
+        self.handle = ctypes.c_void_p()
+        _check(lib().dt_comm_init(ctypes.byref(self.handle), rank, world, ident, timeout_ms), "dt_comm_init")
+        self.ws = None
+
+    def forward(self, q_local, k_local, v_local, scale, o_full, chunks=1, is_causal=False, stream=None):
+        """q_local [B,Sq,H/world,D] etc. -> o_full [B,Sq,H,D] on every rank."""
+        dummy_o = q_local  # `o` of the local params is ignored by the head-sharded entry point
+        p = make_params(q_local, k_local, v_local, dummy_o, scale, is_causal)
+        n = ctypes.c_size_t(0)
+        _check(lib().dt_sdpa_headsharded_workspace_size(ctypes.byref(p), self.world, chunks, ctypes.byref(n)),
+               "dt_sdpa_headsharded_workspace_size")
+        s = stream if stream is not None else torch.cuda.current_stream(q_local.device).cuda_stream
+        if self.ws is None or self.ws.numel() < n.value:
+            self.ws = torch.zeros(n.value, dtype=torch.uint8, device=q_local.device)
+        _check(lib().dt_sdpa_forward_headsharded(self.handle, ctypes.byref(p), _view4(o_full), chunks,
+                                                 ctypes.c_void_p(self.ws.data_ptr()), self.ws.numel(),
+                                                 ctypes.c_void_p(s)), "dt_sdpa_forward_headsharded")
+        return o_full
+
+    def close(self):
+        if self.handle:
+            lib().dt_comm_destroy(self.handle)
+            self.handle = ctypes.c_void_p()

@@ -1,0 +1,145 @@
+/*
+ * dtattn.h -- C ABI of the B200 (sm_100a) scaled-dot-product-attention forward.
+ *
+ * This is the boundary a binding of the Draw Things operator
+ *     NNC.ScaledDotProductAttention(scale:isCausal:hasAttentionMask:flags:...)
+ * calls into.  The reference reaches its own arithmetic through s4nnc -> ccv (neither is vendored in
+ * the reference tree), so each entry point below cites the reference call site whose behaviour it
+ * replaces rather than a C prototype.
+ *
+ * Conventions
+ *   - plain C types only; no exceptions; every function returns a dt_status (0 = OK, <0 = error).
+ *   - all tensors are caller-owned DEVICE memory (except dt_sdpa_forward_host, which takes host
+ *     memory); the library never takes ownership and never allocates inside dt_sdpa_forward.
+ *   - tensors are 4-D views [B, S, H, D] ("BSHD", the layout every reference call site passes, e.g.
+ *     Libraries/SwiftDiffusion/Sources/Models/UNet.swift:139-155) described by element strides; the
+ *     innermost (D) stride is 1.  Strided views (row-offset views, batch strides larger than S*H*D)
+ *     are honoured without a copy (Flux1.swift:236-243, UNet.swift:334-344).
+ *   - work is enqueued on the given CUDA stream; no call synchronises the stream.
+ *   - re-entrant across host threads and streams as long as each concurrent call has its own
+ *     workspace.
+ */
+#ifndef DTATTN_H_
+#define DTATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  DT_OK = 0,
+  DT_BAD_ARG = -1,      /* null pointer, non-positive extent, Hq % Hkv != 0, misaligned base ...        */
+  DT_UNSUPPORTED = -2,  /* valid request that no kernel of this build covers                            */
+  DT_WORKSPACE = -3,    /* workspace missing or smaller than dt_sdpa_workspace_size reports             */
+  DT_CUDA = -4,         /* a CUDA runtime/driver call failed (dt_last_cuda_error gives the code)        */
+  DT_NCCL = -5,         /* NCCL missing or a collective failed                                          */
+  DT_TIMEOUT = -6,      /* a bounded wait ran out (device status word or communicator set-up)           */
+  DT_NO_DEVICE = -7     /* no sm_100 device / library built without the kernel                          */
+} dt_status;
+
+typedef enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2 } dt_dtype;
+
+/* A [B, S, H, D] view: element strides, D contiguous. */
+typedef struct {
+  void* ptr;
+  int64_t stride_b, stride_s, stride_h;
+} dt_tensor4;
+
+/* dt_sdpa_params.flags */
+#define DT_FLAG_FP16_ACCUM_HINT 1u /* reference flags:[.Float16] (UNet.swift:124); accepted, ignored: accumulation is always fp32 */
+#define DT_FLAG_FORCE_GENERIC 2u   /* route to the CUDA-core kernel (second GPU opinion in tests)        */
+
+typedef struct {
+  int32_t B, Sq, Sk, Hq, Hkv, D; /* Hq % Hkv == 0; query head h reads KV head h / (Hq/Hkv)
+                                    (Libraries/SwiftDiffusion/Sources/Models/Llama.swift:74-96)          */
+  int32_t dtype;                 /* dt_dtype of q, k, v, o and mask                                      */
+  float scale;                   /* multiplies Q.K^T: 1 for FlashAttentionLevel.scale1, 1/sqrt(D) for
+                                    .scaleMerged (Flux1.swift:224-232)                                   */
+  int32_t is_causal;             /* bottom-right aligned: key j is visible to query i iff
+                                    j <= i + (Sk - Sq) (Qwen3_5.swift:193-196: Sq new tokens over a
+                                    cache prefix of Sk rows)                                             */
+  uint32_t flags;
+  dt_tensor4 q, k, v, o;
+  /* optional additive mask, same dtype as q, logical shape [B or 1, Hq or 1, Sq, Sk]; a broadcast
+     axis has stride 0 (CLIPTextModel.swift:46-51).  NULL = none.                                        */
+  const void* mask;
+  int64_t mask_stride_b, mask_stride_h, mask_stride_q;
+  /* optional fp32 log-sum-exp output [B, Hq, Sq] (natural log of sum_j exp(scale*s_ij)), NULL = none   */
+  float* lse;
+} dt_sdpa_params;
+
+/* Library / device ------------------------------------------------------------------------------ */
+
+/* Human-readable name of a status code. */
+const char* dt_status_string(int status);
+/* cudaError_t value recorded by the last failing CUDA call on this host thread (0 if none). */
+int dt_last_cuda_error(void);
+/* Version of this ABI (bumped on incompatible change). */
+int dt_abi_version(void);
+
+/* Forward ----------------------------------------------------------------------------------------
+ * Replaces the graph node the reference builds with
+ *   ScaledDotProductAttention(scale:, isCausal:, hasAttentionMask:, flags:)(queries, keys, values[, mask])
+ * at UNet.swift:139-155 (SD1.5 self-attention), UNetXL.swift:67-185 (SDXL cross-attention),
+ * Flux1.swift:224-232 (MMDiT joint attention), Wan.swift:95-131 (video DiT) and
+ * SwiftLLM/Sources/Models/Qwen3_5.swift:193-196 (GQA decode over the KV cache).
+ */
+
+/* Bytes of scratch dt_sdpa_forward needs for these params (0 is a valid answer). */
+int dt_sdpa_workspace_size(const dt_sdpa_params* p, size_t* bytes);
+/* Zero the workspace's ticket counters.  Call once after allocating a workspace (and again after any
+   call that returned an error); dt_sdpa_forward leaves them zero on success. */
+int dt_sdpa_workspace_init(void* workspace, size_t bytes, void* cuda_stream);
+/* O = softmax(scale * Q K^T [+ mask] [causal]) V on `cuda_stream` of the current device. */
+int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_bytes, void* cuda_stream);
+/* Which kernel dt_sdpa_forward would pick: writes a short static name ("prefill_tcgen05",
+   "decode_splitkv", "generic") to *name. */
+int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name);
+
+/* Same operator with HOST tensors: copies q, k, v (and mask) to device scratch it owns, runs
+ * dt_sdpa_forward, copies o (and lse) back and synchronises.  This is the call a host program makes
+ * when its tensors live in host memory; it is the end-to-end path the benchmark times.  The scratch
+ * is cached per host thread and released by dt_host_release().
+ */
+int dt_sdpa_forward_host(const dt_sdpa_params* p_host);
+int dt_host_release(void);
+
+/* Device status word ------------------------------------------------------------------------------
+ * Kernels never spin without a bound: a wait that runs out stores a non-zero code into a per-device
+ * status word and the kernel returns.  dt_device_status reads and clears it (synchronises `stream`).
+ */
+int dt_device_status(void* cuda_stream, int* code);
+
+/* Head-sharded multi-GPU ---------------------------------------------------------------------------
+ * No counterpart in the reference (it is single-GPU per process: Apps/gRPCServerCLI/
+ * gRPCServerCLI.swift:291-292, ccv built with have_nccl = False at WORKSPACE.linux:127).  Rank r of
+ * `world` owns query heads [r*Hq/world, (r+1)*Hq/world) and the KV heads they read.
+ */
+#define DT_NCCL_UNIQUE_ID_BYTES 128
+/* Fill 128 bytes with an NCCL unique id (rank 0 calls this, then ships the bytes to every rank). */
+int dt_comm_unique_id(void* id_out_128);
+/* Create a communicator on the current device.  Returns DT_TIMEOUT when the other ranks do not join
+   within timeout_ms. */
+int dt_comm_init(void** comm, int rank, int world, const void* unique_id_128, int timeout_ms);
+int dt_comm_destroy(void* comm);
+/* Run the local head slice (`local`: Hq and Hkv are the per-rank counts, o is ignored) and gather the
+ * full output into o_full ([B, Sq, Hq*world, D], contiguous rows) on every rank.  `chunks` >= 1 splits
+ * the query rows into that many pieces so the gather of one piece overlaps the attention of the next.
+ * `workspace_bytes` must be at least dt_sdpa_headsharded_workspace_size.
+ */
+int dt_sdpa_headsharded_workspace_size(const dt_sdpa_params* local, int world, int chunks, size_t* bytes);
+int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tensor4 o_full, int chunks,
+                                void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Layout helper used by the head-sharded path: src [world][B*Sq][Hl][D] (rank-major gather order)
+ * -> dst view [B, Sq, world*Hl, D].  Exposed because a caller that gathers by other means needs it. */
+int dt_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D,
+                        int dtype, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DTATTN_H_ */

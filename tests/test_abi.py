@@ -1,0 +1,114 @@
+"""CPU checks of the C-ABI boundary: the library loads, exports every symbol the header declares, and
+rejects bad requests with the documented status codes (no kernel runs here)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "dtattn.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dt_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(dtattn):
+    names = declared_functions()
+    assert len(names) >= 15
+    lib = dtattn.lib()
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/dtattn.h but not exported"
+    assert set(names) == {s[0] for s in dtattn.SYMBOLS}, "binding table and header disagree"
+
+
+def test_struct_layout_matches_header(dtattn):
+    # 10 x 4-byte scalars, 4 x (ptr + 3 int64), mask ptr + 3 int64, lse ptr
+    assert ctypes.sizeof(dtattn.Tensor4) == 32
+    assert ctypes.sizeof(dtattn.SdpaParams) == 40 + 4 * 32 + 8 + 24 + 8
+    assert dtattn.lib().dt_abi_version() == 1
+
+
+def test_status_strings(dtattn):
+    assert dtattn.status_string(0) == "ok"
+    for code in range(-7, 0):
+        assert dtattn.status_string(code) not in ("ok", "unknown status")
+    assert dtattn.status_string(-99) == "unknown status"
+
+
+def _params(dtattn, **over):
+    B, Sq, Sk, Hq, Hkv, D = 1, 8, 8, 4, 2, 64
+    q = torch.zeros(B, Sq, Hq, D, dtype=torch.float16)
+    k = torch.zeros(B, Sk, Hkv, D, dtype=torch.float16)
+    v = torch.zeros(B, Sk, Hkv, D, dtype=torch.float16)
+    o = torch.zeros(B, Sq, Hq, D, dtype=torch.float16)
+    p = dtattn.make_params(q, k, v, o, 0.125)
+    for key, val in over.items():
+        setattr(p, key, val)
+    return p, (q, k, v, o)
+
+
+def test_bad_arguments_are_rejected(dtattn):
+    lib = dtattn.lib()
+    n = ctypes.c_size_t()
+    assert lib.dt_sdpa_workspace_size(None, ctypes.byref(n)) == dtattn.DT_BAD_ARG
+    for over in (dict(Hkv=3), dict(B=0), dict(Sq=-1), dict(D=0), dict(dtype=7), dict(scale=float("nan"))):
+        p, keep = _params(dtattn, **over)
+        assert lib.dt_sdpa_workspace_size(ctypes.byref(p), ctypes.byref(n)) == dtattn.DT_BAD_ARG, over
+        assert lib.dt_sdpa_forward(ctypes.byref(p), None, 0, None) == dtattn.DT_BAD_ARG, over
+    p, keep = _params(dtattn, D=512)
+    assert lib.dt_sdpa_workspace_size(ctypes.byref(p), ctypes.byref(n)) == dtattn.DT_UNSUPPORTED
+    p, keep = _params(dtattn)
+    p.q.ptr = None
+    assert lib.dt_sdpa_forward(ctypes.byref(p), None, 0, None) == dtattn.DT_BAD_ARG
+    assert lib.dt_device_status(None, None) == dtattn.DT_BAD_ARG
+    assert lib.dt_comm_init(None, 0, 1, None, 10) == dtattn.DT_BAD_ARG
+    assert lib.dt_comm_unique_id(None) == dtattn.DT_BAD_ARG
+
+
+def test_kernel_selection(dtattn):
+    """Which kernel serves which reference call site (decided on the host, no GPU needed)."""
+    def pick(B, Sq, Sk, Hq, Hkv, D, dtype, causal=False, flags=0):
+        q = torch.zeros(1, dtype=dtype).expand(B, Sq, Hq, D)  # shapes only; never dereferenced
+        q = torch.empty_strided((B, Sq, Hq, D), (Sq * Hq * D, Hq * D, D, 1), dtype=dtype, device="meta")
+        k = torch.empty_strided((B, Sk, Hkv, D), (Sk * Hkv * D, Hkv * D, D, 1), dtype=dtype, device="meta")
+        p = dtattn.SdpaParams()
+        p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D = B, Sq, Sk, Hq, Hkv, D
+        p.dtype = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
+        p.scale, p.is_causal, p.flags = D ** -0.5, int(causal), flags
+        for name, t in (("q", q), ("k", k), ("v", k), ("o", q)):
+            setattr(p, name, dtattn.Tensor4(0x10000, t.stride(0), t.stride(1), t.stride(2)))
+        return dtattn.kernel_name(p)
+
+    assert pick(2, 4096, 4096, 8, 8, 40, torch.float32) == "generic"              # SD1.5 self-attention
+    assert pick(2, 4096, 77, 20, 20, 64, torch.float16) == "prefill_tcgen05"       # SDXL cross-attention
+    assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16) == "prefill_tcgen05"   # Flux joint attention
+    assert pick(1, 75600, 75600, 5, 5, 128, torch.bfloat16) == "prefill_tcgen05"   # Wan, one rank's heads
+    assert pick(16, 1, 8192, 32, 8, 128, torch.float16, True) == "decode_splitkv"  # GQA decode
+    assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16, flags=2) == "generic"
+
+
+def test_operator_mirror_validates_like_the_reference(dtattn):
+    op = dtattn.ScaledDotProductAttention(scale=0.125, is_causal=True, flags=[dtattn.GEMMFlag.Float16])
+    assert op.scale == 0.125 and op.is_causal
+    with pytest.raises(NotImplementedError):
+        dtattn.ScaledDotProductAttention(scale=1.0, multi_head_output_projection_fused=True)
+    with pytest.raises(NotImplementedError):
+        dtattn.ScaledDotProductAttention(scale=1.0, flags=[dtattn.GEMMFlag.Int8, dtattn.GEMMFlag.Float16])
+    q = torch.zeros(1, 4, 2, 64, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        dtattn.ScaledDotProductAttention(scale=1.0, has_attention_mask=True)(q, q, q)
+
+
+def test_no_cpu_fallback(dtattn):
+    """Host tensors go through the device; without a GPU the call must fail loudly, not compute on the CPU."""
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    q = torch.zeros(1, 4, 2, 64, dtype=torch.float16)
+    with pytest.raises(dtattn.DtError) as e:
+        dtattn.ScaledDotProductAttention(scale=1.0)(q, q, q)
+    assert e.value.status in (dtattn.DT_CUDA, dtattn.DT_NO_DEVICE, dtattn.DT_UNSUPPORTED)
