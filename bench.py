@@ -1,0 +1,473 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One step = one scaled-dot-product-attention forward over one batch of synthetic input.
+  N = 1  (default workload flux_joint): Flux-style joint attention, 24 heads x 4608 tokens x d128, bf16 --
+         the shape the headline metric is quoted on.  The same run also times the other single-GPU
+         shapes (GQA decode B=1/16 as GB/s of HBM, SDXL cross-attention) and reports them under "also".
+  N > 1  (default workload wan_self): the 75,600-token video shape, head-sharded over N GPUs with the
+         all-gather of the output included in every step ("scaling": "strong").
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of the reference's CPU path
+(the reference's own back end is not buildable: its arithmetic lives in un-vendored dependencies).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "draw-things-community_b200"))
+
+METRIC = "sdpa_fwd_tflops"
+UNIT = "TFLOP/s"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# Shapes of the benchmark configurations (B, Sq, Sk, Hq, Hkv, D, dtype, causal)
+WORKLOADS = {
+    "flux_joint": dict(B=1, Sq=4608, Sk=4608, Hq=24, Hkv=24, D=128, dtype="bf16", causal=False),
+    "wan_self": dict(B=1, Sq=75600, Sk=75600, Hq=40, Hkv=40, D=128, dtype="bf16", causal=False),
+    "sdxl_cross": dict(B=2, Sq=4096, Sk=77, Hq=20, Hkv=20, D=64, dtype="f16", causal=False),
+    "decode_b1": dict(B=1, Sq=1, Sk=8192, Hq=32, Hkv=8, D=128, dtype="f16", causal=True),
+    "decode_b16": dict(B=16, Sq=1, Sk=8192, Hq=32, Hkv=8, D=128, dtype="f16", causal=True),
+}
+TDT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+def flops_of(w, heads=None):
+    h = w["Hq"] if heads is None else heads
+    return 4 * w["B"] * h * w["Sq"] * w["Sk"] * w["D"]
+
+
+def bytes_of(w):
+    es = 2
+    return es * w["B"] * (2 * w["Sq"] * w["Hq"] * w["D"] + 2 * w["Sk"] * w["Hkv"] * w["D"])
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_sets(w, n_sets, device, heads=None, seed=0):
+    """n_sets independent (q, k, v, o) device buffer sets of synthetic N(0,1) data."""
+    g = torch.Generator(device=device).manual_seed(1234 + seed)
+    dt = TDT[w["dtype"]]
+    hq = w["Hq"] if heads is None else heads
+    hkv = w["Hkv"] if heads is None else max(1, heads * w["Hkv"] // w["Hq"])
+    sets = []
+    for _ in range(n_sets):
+        q = torch.randn((w["B"], w["Sq"], hq, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+        k = torch.randn((w["B"], w["Sk"], hkv, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+        v = torch.randn((w["B"], w["Sk"], hkv, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+        o = torch.empty_like(q)
+        sets.append((q, k, v, o))
+    return sets
+
+
+def time_device(fn, steps, warmup):
+    """CUDA-event time of `steps` calls of fn(i) on the current stream, after `warmup` calls."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)  # ms
+
+
+def time_graph(fns, reps, warmup_reps=3):
+    """Capture one call of each fn into a CUDA graph and replay it: for launches of a few microseconds,
+    where per-launch host work would otherwise be what is timed."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for f in fns:
+                f()
+        for _ in range(warmup_reps):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(reps):
+            g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * len(fns))  # ms per launch
+
+
+def side_measurements(dtattn, device, peaks):
+    """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention."""
+    out = {}
+    for name in ("decode_b16", "decode_b1", "sdxl_cross"):
+        w = WORKLOADS[name]
+        nbytes = bytes_of(w)
+        n_sets = max(2, -(-3 * L2_BYTES // nbytes))  # rotate through > 3x L2 worth of distinct inputs
+        n_sets = min(n_sets, 16)
+        sets = make_sets(w, n_sets, device, seed=7)
+        scale = w["D"] ** -0.5
+        fns = [(lambda s=s: dtattn.sdpa_forward(s[0], s[1], s[2], scale, w["causal"], out=s[3])) for s in sets]
+        ms_stream = time_device(lambda i: fns[i % n_sets](), 20 * n_sets, 2 * n_sets) / (20 * n_sets)
+        try:
+            ms_graph = time_graph(fns, reps=20)
+        except Exception as e:  # graph capture is a convenience for the tiny shapes, not a requirement
+            ms_graph = None
+            out[name + "_graph_error"] = str(e)[:120]
+        best = min(x for x in (ms_stream, ms_graph) if x is not None)
+        out[name] = {"us_per_call_stream": round(ms_stream * 1e3, 2),
+                     "us_per_call_graph": round(ms_graph * 1e3, 2) if ms_graph else None,
+                     "algorithmic_bytes": nbytes, "gbs": round(nbytes / (best * 1e-3) / 1e9, 1),
+                     "frac_hbm": round(nbytes / (best * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                     "tflops": round(flops_of(w) / (best * 1e-3) / 1e12, 2), "rotating_sets": n_sets}
+        del sets, fns
+        torch.cuda.empty_cache()
+    return out
+
+
+def cpu_baseline(w, max_seconds=25.0):
+    """The CPU restatement (oracle/sdpa_oracle.c) timed on this machine's host cores on the same shape.
+    Query rows are sampled evenly when the whole shape would take longer than the budget."""
+    from oracle import c_oracle
+    cores = c_oracle.host_cores()
+    dt = torch.float32
+    g = torch.Generator().manual_seed(5)
+    rows = w["Sq"]
+    # calibrate on a small slice, then size the sample for ~10-25 s
+    k = torch.randn((w["B"], w["Sk"], w["Hkv"], w["D"]), generator=g, dtype=dt)
+    v = torch.randn((w["B"], w["Sk"], w["Hkv"], w["D"]), generator=g, dtype=dt)
+    probe_rows = max(1, min(rows, 16))
+    qp = torch.randn((w["B"], probe_rows, w["Hq"], w["D"]), generator=g, dtype=dt)
+    t0 = time.perf_counter()
+    c_oracle.sdpa_c(qp, k, v, w["D"] ** -0.5, False)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    sample_rows = int(min(rows, max(probe_rows, (0.6 * max_seconds) / max(per_row, 1e-9))))
+    q = torch.randn((w["B"], sample_rows, w["Hq"], w["D"]), generator=g, dtype=dt)
+    t0 = time.perf_counter()
+    c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
+    dt_s = time.perf_counter() - t0
+    fl = 4 * w["B"] * w["Hq"] * sample_rows * w["Sk"] * w["D"]
+    return {"value": round(fl / dt_s / 1e12, 5), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{sample_rows} of {rows} query rows x all {w['Hq']} heads x all {w['Sk']} keys, fp32, "
+                      f"{dt_s:.1f} s; non-causal so every sampled row costs the same"}
+
+
+def run_reference(args):
+    """--impl reference: the CPU path on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload or ("flux_joint" if args.gpus == 1 else "wan_self")
+    w = WORKLOADS[name]
+    from oracle import c_oracle
+    cores = c_oracle.host_cores()
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn((w["B"], w["Sk"], w["Hkv"], w["D"]), generator=g)
+    v = torch.randn((w["B"], w["Sk"], w["Hkv"], w["D"]), generator=g)
+    # size one step to ~3 s of CPU work
+    probe = torch.randn((w["B"], 8, w["Hq"], w["D"]), generator=g)
+    t0 = time.perf_counter()
+    c_oracle.sdpa_c(probe, k, v, w["D"] ** -0.5, w["causal"] and False)
+    per_row = (time.perf_counter() - t0) / 8
+    rows = int(max(8, min(w["Sq"], 3.0 / max(per_row, 1e-9))))
+    q = torch.randn((w["B"], rows, w["Hq"], w["D"]), generator=g)
+    for _ in range(min(args.warmup, 1)):
+        c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
+    dt_s = (time.perf_counter() - t0) / steps
+    fl = 4 * w["B"] * w["Hq"] * rows * w["Sk"] * w["D"]
+    val = fl / dt_s / 1e12
+    sample = f"{rows} of {w['Sq']} query rows x all heads x all keys per step, fp32, {steps} steps"
+    line = {"impl": "reference", "metric": METRIC, "value": round(val, 5), "unit": UNIT, "n_gpus": args.gpus,
+            "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": round(dt_s * 1e3, 2),
+            "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, **{k2: w[k2] for k2 in ("B", "Sq", "Sk", "Hq", "Hkv", "D")}},
+            "cpu_baseline": {"value": round(val, 5), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(val, 5), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the reference's CPU attention path (oracle/sdpa_oracle.c); the reference's "
+                    "own back end (s4nnc/ccv) is not in its tree and cannot be built here"}
+    print(json.dumps(line))
+
+
+def run_single(args, dtattn, device, peaks):
+    name = args.workload or "flux_joint"
+    w = WORKLOADS[name]
+    scale = w["D"] ** -0.5
+    nbytes = bytes_of(w)
+    n_sets = min(16, max(2, -(-2 * L2_BYTES // nbytes) + 1))
+    sets = make_sets(w, n_sets, device)
+
+    def step(i):
+        s = sets[i % n_sets]
+        dtattn.sdpa_forward(s[0], s[1], s[2], scale, w["causal"], out=s[3])
+
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        ms = time_device(step, args.steps, args.warmup)
+        if ms < 1500 and not args.profile:  # keep the clock sampler fed for short runs
+            extra_steps = int(min(2000, 1500 / max(ms / args.steps, 1e-3)))
+            time_device(step, extra_steps, 0)
+    status = dtattn.device_status()
+    ms_step = ms / args.steps
+    fl = flops_of(w)
+    tflops = fl / (ms_step * 1e-3) / 1e12
+
+    # end to end: host tensors in pinned memory through dt_sdpa_forward_host (H2D + kernel + D2H per step)
+    hq, hk, hv, _ = [t.cpu().pin_memory() for t in sets[0]]
+    ho = torch.empty_like(hq).pin_memory()
+    e2e_steps = 1 if args.profile else max(3, min(args.steps, 10))
+    for _ in range(0 if args.profile else 2):
+        dtattn.sdpa_forward(hq, hk, hv, scale, w["causal"], out=ho)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dtattn.sdpa_forward(hq, hk, hv, scale, w["causal"], out=ho)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    es = 2
+    h2d = es * (hq.numel() + hk.numel() + hv.numel())
+    d2h = es * ho.numel()
+
+    also = side_measurements(dtattn, device, peaks) if not (args.no_side or args.profile) else {}
+    base = cpu_baseline(w) if not (args.no_cpu or args.profile) else None
+    peak = peaks["bf16_tflops"]
+    is_tensor = name in ("flux_joint", "wan_self")
+    if is_tensor:
+        roof = {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
+                "frac": round(tflops / peak, 4), "traffic": None, "peak_source": peaks["source"] + " (burst bf16 GEMM)",
+                "frac_of_sustained_peak": round(tflops / peaks["bf16_tflops_sustained"], 4) if peaks["bf16_tflops_sustained"] else None,
+                "kernel": "prefill_tcgen05_kernel", "launches_timed": args.steps}
+    else:
+        gbs = nbytes / (ms_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peaks["source"],
+                "launches_timed": args.steps}
+    line = {"metric": METRIC, "value": round(tflops, 3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": name, **{k2: w[k2] for k2 in ("B", "Sq", "Sk", "Hq", "Hkv", "D")},
+                       "l2": f"rotating {n_sets} input sets of {nbytes >> 20} MiB (> 126 MiB L2 in total)"},
+            "clocks": clk.summary(), "roofline": roof, "cpu_baseline": base,
+            "e2e": {"value": round(fl / e2e_s / 1e12, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e_s * 1e3, 3), "api": "dt_sdpa_forward_host (pinned host tensors)"},
+            "gpu_launches": args.steps, "device_status": status, "also": also}
+    print(json.dumps(line))
+
+
+def run_sharded(args, dtattn, device, peaks):
+    import torch.distributed as dist
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("nccl", device_id=device)
+    name = args.workload or "wan_self"
+    w = WORKLOADS[name]
+    assert w["Hq"] % world == 0, "heads must divide over the ranks"
+    hl = w["Hq"] // world
+    scale = w["D"] ** -0.5
+
+    def bcast(b):
+        obj = [b]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+
+    comm = dtattn.HeadShardedComm(rank, world, bcast)
+    nbytes_local = bytes_of(w) // world
+    n_sets = 2 if nbytes_local > L2_BYTES else min(8, -(-2 * L2_BYTES // nbytes_local) + 1)
+    sets = make_sets(w, n_sets, device, heads=hl, seed=rank)
+    o_full = [torch.empty((w["B"], w["Sq"], w["Hq"], w["D"]), dtype=TDT[w["dtype"]], device=device) for _ in range(2)]
+    chunks = args.chunks
+
+    def step(i):
+        s = sets[i % n_sets]
+        comm.forward(s[0], s[1], s[2], scale, o_full[i % 2], chunks=chunks)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    status = dtattn.device_status()
+    fl = flops_of(w)
+    tflops = fl / (ms_step * 1e-3) / 1e12
+
+    # end to end: local q/k/v from pinned host memory, full gathered output back to pinned host memory
+    hq, hk, hv, _ = [x.cpu().pin_memory() for x in sets[0]]
+    ho = torch.empty(o_full[0].shape, dtype=o_full[0].dtype).pin_memory()
+    dq, dk, dv = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1]), torch.empty_like(sets[0][2])
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        comm.forward(dq, dk, dv, scale, o_full[0], chunks=chunks)
+        ho.copy_(o_full[0], non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    dist.barrier()
+    n_e2e = 3
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    dist.barrier()
+    e2e_s = (time.perf_counter() - t0) / n_e2e
+    te = torch.tensor([e2e_s], device=device)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    n_chunks_run = chunks
+    launches = args.steps * 2 * n_chunks_run  # attention + permute kernel per chunk (NCCL's own kernels not counted)
+
+    # same workload on ONE GPU in the same run (rank 0 only), so the strong-scaling ratio has its own T1
+    t1 = None
+    if rank == 0 and not args.no_t1:
+        full = make_sets(w, 1, device, seed=99)[0]
+        f = lambda i: dtattn.sdpa_forward(full[0], full[1], full[2], scale, w["causal"], out=full[3])
+        t1 = time_device(f, 2, 1) / 2
+        del full
+    dist.barrier()
+    if rank == 0:
+        peak = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
+        line = {"metric": METRIC, "value": round(tflops, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+                "config": {"workload": name, **{k2: w[k2] for k2 in ("B", "Sq", "Sk", "Hq", "Hkv", "D")},
+                           "parallelism": f"heads sharded {hl} per GPU + all-gather of O in {chunks} row chunks",
+                           "l2": f"rotating {n_sets} input sets per rank; each set larger than L2" if nbytes_local > L2_BYTES
+                                 else f"rotating {n_sets} input sets per rank"},
+                "clocks": clk.summary(),
+                "roofline": {"bound": "tensor", "achieved": round(tflops / world, 2), "peak": peak, "unit": "TFLOP/s",
+                             "frac": round(tflops / world / peak, 4), "traffic": None,
+                             "peak_source": peaks["source"] + " (sustained bf16 GEMM; per GPU, step includes the all-gather)"},
+                "cpu_baseline": None,
+                "e2e": {"value": round(fl / e2e_s / 1e12, 3), "unit": UNIT,
+                        "h2d_bytes_per_step": 2 * (hq.numel() + hk.numel() + hv.numel()),
+                        "d2h_bytes_per_step": 2 * ho.numel(), "ms_per_step": round(e2e_s * 1e3, 3)},
+                "gpu_launches": launches, "device_status": status,
+                "t1_same_workload_ms": round(t1, 3) if t1 else None,
+                "strong_scaling_efficiency_same_run": round(t1 / (world * ms_step), 4) if t1 else None}
+        print(json.dumps(line))
+    comm.close()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="dtattn", choices=["dtattn", "reference"])
+    ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
+    ap.add_argument("--chunks", type=int, default=4)
+    ap.add_argument("--no-side", action="store_true", help="skip the decode / SDXL side measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-t1", action="store_true", help="skip the single-GPU run of the sharded workload")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    import dtattn
+    dtattn.lib()
+    peaks = load_peaks()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        run_sharded(args, dtattn, device, peaks)
+    else:
+        run_single(args, dtattn, device, peaks)
+
+
+if __name__ == "__main__":
+    main()

@@ -29,11 +29,16 @@ def oracle(q, k, v, scale, causal=False, mask=None):
 
 
 def check(out, ref, dtype, what="", strict=False):
+    """strict: the plain figures (benchmark shapes).  Otherwise the rounding of a 16-bit result is added:
+    P is rounded to the I/O type before P*V (as the reference's explicit graph does, UNet.swift:257-259) and
+    O is rounded once more on output, so a result of magnitude |O| carries up to ~2 ulp of it."""
     out = out.float().cpu()
     assert torch.isfinite(out).all(), f"{what}: non-finite output"
     mx, mean = so.error_stats(out, ref)
-    bound = so.TOL_MAX_ABS + (0.0 if strict else ROUND[dtype] * float(ref.abs().max()))
-    assert mx <= bound and mean <= so.TOL_MEAN_ABS, f"{what}: max-abs {mx:.3e} (bound {bound:.3e}) mean-abs {mean:.3e}"
+    bound_max = so.TOL_MAX_ABS + (0.0 if strict else 2 * ROUND[dtype] * float(ref.abs().max()))
+    bound_mean = so.TOL_MEAN_ABS + (0.0 if strict else ROUND[dtype] * float(ref.abs().mean()))
+    assert mx <= bound_max and mean <= bound_mean, \
+        f"{what}: max-abs {mx:.3e} (bound {bound_max:.3e}) mean-abs {mean:.3e} (bound {bound_mean:.3e})"
     return mx, mean
 
 
