@@ -322,22 +322,65 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < a.M * D; idx += kThreads) {
-    const int r = idx / D, d = idx - r * D;
+  // Combine.  All loads of a phase are independent so they overlap: first every (split, row) pair's
+  // (m, l) lands in shared memory, then each thread owns one float4 of one output row and streams the
+  // splits' partial O in batches of eight loads.
+  {
     const int64_t base = (int64_t)pair * a.nsplit;
-    float mstar = -INFINITY;
-    for (int s = 0; s < a.nsplit; ++s) mstar = fmaxf(mstar, __ldcg(&a.part_ml[((base + s) * a.M + r) * 2]));
-    float lt = 0.f, ot = 0.f;
-    if (mstar != -INFINITY) {
-      for (int s = 0; s < a.nsplit; ++s) {
-        const float wgt = fast_exp2(__ldcg(&a.part_ml[((base + s) * a.M + r) * 2]) - mstar);
-        lt += wgt * __ldcg(&a.part_ml[((base + s) * a.M + r) * 2 + 1]);
-        ot += wgt * __ldcg(&a.part_o[(base + s) * a.M * D + idx]);
-      }
+    float* wbuf = reinterpret_cast<float*>(ring_ptr);   // [nsplit][M] weights
+    float* lsm = wbuf + a.nsplit * a.M;                  // [nsplit][M] l
+    float* rowinfo = lsm + a.nsplit * a.M;               // [M][2]: m*, L
+    const int nm = a.nsplit * a.M;
+    for (int idx = threadIdx.x; idx < nm; idx += kThreads) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(&a.part_ml[(base * a.M + idx) * 2]));
+      wbuf[idx] = ml.x;
+      lsm[idx] = ml.y;
     }
-    const int sq = r / a.G, h = kvh * a.G + r % a.G;
-    o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
-    if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+    __syncthreads();
+    if (threadIdx.x < a.M) {
+      const int r = threadIdx.x;
+      float mstar = -INFINITY;
+      for (int sp = 0; sp < a.nsplit; ++sp) mstar = fmaxf(mstar, wbuf[sp * a.M + r]);
+      float lt = 0.f;
+      for (int sp = 0; sp < a.nsplit; ++sp) {
+        const float wgt = mstar == -INFINITY ? 0.f : fast_exp2(wbuf[sp * a.M + r] - mstar);
+        wbuf[sp * a.M + r] = wgt;
+        lt += wgt * lsm[sp * a.M + r];
+      }
+      rowinfo[2 * r] = mstar;
+      rowinfo[2 * r + 1] = lt;
+    }
+    __syncthreads();
+    constexpr int kVec = D / 4;
+    for (int item = threadIdx.x; item < a.M * kVec; item += kThreads) {
+      const int r = item / kVec, d4 = item - r * kVec;
+      const float4* src = reinterpret_cast<const float4*>(a.part_o) + (base * a.M + r) * kVec + d4;
+      const int64_t split_stride = (int64_t)a.M * kVec;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s0 = 0; s0 < a.nsplit; s0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          v[u] = (s0 + u < a.nsplit) ? __ldcg(src + (s0 + u) * split_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float wgt = (s0 + u < a.nsplit) ? wbuf[(s0 + u) * a.M + r] : 0.f;
+          acc.x = fmaf(wgt, v[u].x, acc.x);
+          acc.y = fmaf(wgt, v[u].y, acc.y);
+          acc.z = fmaf(wgt, v[u].z, acc.z);
+          acc.w = fmaf(wgt, v[u].w, acc.w);
+        }
+      }
+      const float mstar = rowinfo[2 * r], lt = rowinfo[2 * r + 1];
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      const int sq = r / a.G, h = kvh * a.G + r % a.G;
+      T* dst = o + b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d4 * 4;
+      dst[0] = from_float<T>(acc.x * inv);
+      dst[1] = from_float<T>(acc.y * inv);
+      dst[2] = from_float<T>(acc.z * inv);
+      dst[3] = from_float<T>(acc.w * inv);
+      if (a.lse && d4 == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+    }
   }
   if (threadIdx.x == 0) a.counters[pair] = 0u;  // leave the workspace ready for the next call
 }

@@ -304,11 +304,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < 32; ++i)
               if ((long long)(key0 + c * 32 + i) > lim) s[c][i] = 0xff800000u;  // -inf
         }
-        float mx = -INFINITY;
+        // row max: four independent chains of 3-input max (one per 32-column chunk)
+        float mxc[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) {
+          mxc[c] = ptx::max3(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]), __uint_as_float(s[c][2]));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+          for (int i = 3; i < 31; i += 2) mxc[c] = ptx::max3(mxc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+          mxc[c] = fmaxf(mxc[c], __uint_as_float(s[c][31]));
+        }
+        float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
         mx *= a.scale_log2;  // scale > 0 is a precondition of this kernel
         const float m_cand = fmaxf(m_used, mx);
         // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
@@ -330,18 +335,33 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
           }
         }
+        // p = exp2(s * scale_log2 - m): packed fp32x2 multiply-add, one MUFU per element, packed row sums in
+        // four independent accumulators, packed conversion to the 16-bit P the second MMA reads from TMEM
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
+        const uint64_t scale2 = ptx::pack_f32x2(a.scale_log2, a.scale_log2);
+        uint64_t lsum[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
+          lsum[c] = 0ull;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i]), a.scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * i + 1]), a.scale_log2, neg_m));
-            l += p0 + p1;
-            pk[i] = pack_pair<T>(p0, p1);
+            const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
+                                               scale2, neg_m2);
+            float x0, x1;
+            ptx::unpack_f32x2(x2, x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            lsum[c] = ptx::add_f32x2(lsum[c], ptx::pack_f32x2(p0, p1));
+            pk[i] = kBf16 ? ptx::cvt_pack_bf16(p0, p1) : ptx::cvt_pack_f16(p0, p1);
           }
           ptx::tmem_st16(t_s + c * 16, pk);
+        }
+        {
+          float a0, a1, b0, b1;
+          ptx::unpack_f32x2(ptx::add_f32x2(lsum[0], lsum[1]), a0, a1);
+          ptx::unpack_f32x2(ptx::add_f32x2(lsum[2], lsum[3]), b0, b1);
+          l += (a0 + a1) + (b0 + b1);
         }
         ptx::tc_wait_st();
         ptx::tc_fence_before();

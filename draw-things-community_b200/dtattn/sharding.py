@@ -1,0 +1,39 @@
+"""Host-side bookkeeping of the head-sharded mode: which heads a rank owns and how the gathered output is
+laid out.  No compute lives here; the exchange and the permute run in libdtattn.so
+(dt_sdpa_forward_headsharded, dt_permute_gathered)."""
+from __future__ import annotations
+
+
+def head_range(rank: int, world: int, Hq: int, Hkv: int):
+    """(q_begin, q_end, kv_begin, kv_end): rank r owns query heads [r*Hq/world, (r+1)*Hq/world) and the KV
+    heads they read.  Query heads [i*G, (i+1)*G) read KV head i (Llama.swift:74-86), so a rank's query range
+    must cover whole groups."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("bad rank/world")
+    if Hq % world:
+        raise ValueError(f"{Hq} query heads do not divide over {world} ranks")
+    G = Hq // Hkv
+    per = Hq // world
+    if per % G and G % per:
+        raise ValueError("a rank's heads must be whole KV groups or share one KV head")
+    q0, q1 = rank * per, (rank + 1) * per
+    kv0 = q0 // G
+    kv1 = max(kv0 + 1, -(-q1 // G))
+    return q0, q1, kv0, kv1
+
+
+def gathered_to_bshd(gathered, world: int):
+    """The layout contract of dt_permute_gathered as a torch expression:
+    [world, B, S, Hl, D] (rank-major all-gather order) -> [B, S, world*Hl, D]."""
+    w, B, S, Hl, D = gathered.shape
+    assert w == world
+    return gathered.permute(1, 2, 0, 3, 4).reshape(B, S, world * Hl, D)
+
+
+def chunk_rows(Sq: int, chunks: int, tile: int = 256):
+    """Row ranges dt_sdpa_forward_headsharded cuts the queries into (multiples of the 256-row CTA tile)."""
+    if chunks <= 1:
+        return [(0, Sq)]
+    per = -(-Sq // chunks)
+    per = -(-per // tile) * tile
+    return [(r0, min(Sq, r0 + per)) for r0 in range(0, Sq, per)]

@@ -1,0 +1,113 @@
+// C++ mirror of the reference's operator surface, header-only, above the C ABI (include/dtattn.h).
+//
+// The reference builds attention as a graph node of its Swift NNC module:
+//   ScaledDotProductAttention(scale:, isCausal:, hasAttentionMask:, flags:, multiHeadOutputProjectionFused:, name:)
+//   op(queries, keys, values[, mask])
+// (Libraries/SwiftDiffusion/Sources/Models/UNet.swift:139-155, Flux1.swift:224-232, Wan.swift:95-131,
+//  Libraries/SwiftLLM/Sources/Models/Qwen3_5.swift:193-196).  No Swift toolchain exists in this build
+// environment, so the host side is written in C++ with the same names and argument meaning; the Swift
+// facade a maintainer would add is in host/ScaledDotProductAttention.swift.
+//
+// Error behaviour: the reference traps (precondition / fatalError) on misuse.  Here misuse throws
+// dt::Error carrying the dt_status; nothing falls back to another implementation.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/dtattn.h"
+
+namespace dt {
+
+struct Error : std::runtime_error {
+  int status;
+  Error(int st, const std::string& what) : std::runtime_error(what + ": " + dt_status_string(st)), status(st) {}
+};
+
+// Functional.GEMMFlag as passed at the call sites ([.Float16], [], [.Float32], [.Int8, .Float16]).
+enum GEMMFlag : unsigned { kNone = 0, kFloat16 = 1, kFloat32 = 2, kInt8 = 4 };
+
+// A [B, S, H, D] tensor view in device memory (element strides, D contiguous): what Model.IO carries
+// for this operator.
+struct TensorView {
+  void* ptr = nullptr;
+  int B = 0, S = 0, H = 0, D = 0;
+  int64_t stride_b = 0, stride_s = 0, stride_h = 0;
+  dt_dtype dtype = DT_F16;
+  static TensorView contiguous(void* p, int B, int S, int H, int D, dt_dtype t) {
+    TensorView v;
+    v.ptr = p; v.B = B; v.S = S; v.H = H; v.D = D; v.dtype = t;
+    v.stride_h = D; v.stride_s = (int64_t)H * D; v.stride_b = (int64_t)S * H * D;
+    return v;
+  }
+  // rows [offset, offset + count) of the sequence axis, the reshaped(offset:strides:) views of
+  // Flux1.swift:236-243
+  TensorView rows(int offset, int count) const {
+    TensorView v = *this;
+    const size_t es = dtype == DT_F32 ? 4 : 2;
+    v.ptr = static_cast<char*>(ptr) + (size_t)offset * stride_s * es;
+    v.S = count;
+    return v;
+  }
+  dt_tensor4 abi() const { return dt_tensor4{ptr, stride_b, stride_s, stride_h}; }
+};
+
+class ScaledDotProductAttention {
+ public:
+  ScaledDotProductAttention(float scale, bool isCausal = false, bool hasAttentionMask = false,
+                            unsigned flags = kNone, bool multiHeadOutputProjectionFused = false,
+                            std::string name = "")
+      : scale_(scale), causal_(isCausal), has_mask_(hasAttentionMask), flags_(flags), name_(std::move(name)) {
+    if (multiHeadOutputProjectionFused)
+      throw Error(DT_UNSUPPORTED, "multiHeadOutputProjectionFused (UNet.swift:122-130) is outside this library");
+    if (flags & kInt8) throw Error(DT_UNSUPPORTED, "quantised attention is only selected on Metal in the reference");
+  }
+
+  // Bytes of scratch operator() needs for these shapes (the graph compiles once per shape in the
+  // reference, UNetProtocol.swift:2954-2965; query this at the same point).
+  size_t workspaceSize(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& o) const {
+    dt_sdpa_params p = params(q, k, v, o, nullptr);
+    size_t n = 0;
+    int st = dt_sdpa_workspace_size(&p, &n);
+    if (st != DT_OK) throw Error(st, "dt_sdpa_workspace_size");
+    return n;
+  }
+
+  // op(queries, keys, values[, mask]) -> out, enqueued on `stream`.
+  void operator()(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out,
+                  void* workspace, size_t workspace_bytes, void* stream, const TensorView* mask = nullptr) const {
+    if (has_mask_ != (mask != nullptr)) throw Error(DT_BAD_ARG, "hasAttentionMask and the inputs disagree");
+    dt_sdpa_params p = params(q, k, v, out, mask);
+    int st = dt_sdpa_forward(&p, workspace, workspace_bytes, stream);
+    if (st != DT_OK) throw Error(st, "dt_sdpa_forward(" + name_ + ")");
+  }
+
+ private:
+  dt_sdpa_params params(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& o,
+                        const TensorView* mask) const {
+    if (q.dtype != k.dtype || q.dtype != v.dtype || q.dtype != o.dtype) throw Error(DT_BAD_ARG, "dtype mismatch");
+    if (q.B != k.B || k.S != v.S || k.H != v.H || q.D != k.D || q.D != v.D) throw Error(DT_BAD_ARG, "shape mismatch");
+    dt_sdpa_params p{};
+    p.B = q.B; p.Sq = q.S; p.Sk = k.S; p.Hq = q.H; p.Hkv = k.H; p.D = q.D;
+    p.dtype = q.dtype;
+    p.scale = scale_;
+    p.is_causal = causal_ ? 1 : 0;
+    p.flags = (flags_ & kFloat16) ? DT_FLAG_FP16_ACCUM_HINT : 0;
+    p.q = q.abi(); p.k = k.abi(); p.v = v.abi(); p.o = o.abi();
+    if (mask) {  // [B|1, H|1, Sq, Sk] carried as a TensorView with B, S=H(mask heads), H=Sq, D=Sk
+      p.mask = mask->ptr;
+      p.mask_stride_b = mask->B > 1 ? mask->stride_b : 0;
+      p.mask_stride_h = mask->S > 1 ? mask->stride_s : 0;
+      p.mask_stride_q = mask->stride_h;
+    }
+    return p;
+  }
+  float scale_;
+  bool causal_, has_mask_;
+  unsigned flags_;
+  std::string name_;
+};
+
+}  // namespace dt
