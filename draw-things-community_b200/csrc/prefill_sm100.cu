@@ -32,8 +32,10 @@ constexpr int kBN = 128;       // keys per block
 constexpr int kThreads = 384;
 constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 x 16-bit] = 16 KB, one TMA box
 constexpr float kRescaleThreshold = 8.f;
+// every kPolyPeriod-th pair of exponentials is evaluated with the polynomial instead of MUFU.EX2
+constexpr int kPolyPeriod = 2;
 // 128 * kRegsLow + 256 * kRegsHigh must not exceed what the CTA was launched with (384 threads * 168)
-constexpr int kRegsLow = 56, kRegsHigh = 224;
+constexpr int kRegsLow = 80, kRegsHigh = 208;
 
 template <int D>
 struct Cfg {
@@ -57,7 +59,7 @@ struct PrefillArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int is_causal;
-  int options;  // bit 0: issue P*V as D/64 MMAs of N = 64 instead of one of N = D
+  int options;  // bit 1: record a clock64 timeline of CTA (0,0,0) into dbg (bring-up probe)
 };
 
 struct Barriers {
@@ -79,6 +81,38 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
   }
+}
+
+// S = Q K^T for one 128-row tile: both operands K-major with 128-byte swizzle, D/16 steps of k = 16.
+// Descriptor start addresses advance by 32 B per step inside a 64-element half and by 16 KB to the next half.
+template <int D>
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const uint64_t o = (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+    ptx::mma_ss(s_tmem, q_desc + o, k_desc + o, idesc, ks > 0 ? 1u : 0u);
+  }
+}
+
+// O (+)= P V for one tile: P from TMEM (two 16-bit keys per 32-bit column, 8 columns per step), V is
+// [key][d] = MN-major; one step consumes 16 keys = 2 KB of each 64-wide half.
+__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc,
+                                         uint32_t accumulate, int ksteps) {
+  if (ksteps == kBN / 16) {
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk)
+      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, kk > 0 ? 1u : accumulate);
+  } else {
+#pragma unroll 1
+    for (int kk = 0; kk < ksteps; ++kk)
+      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, kk > 0 ? 1u : accumulate);
+  }
+}
+
+// Timeline probe (options bit 1): clock64 stamps of CTA (0,0,0) into the debug buffer.
+__device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
+  if ((a.options & 2) && a.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+    reinterpret_cast<long long*>(a.dbg)[slot] = clock64();
 }
 
 template <typename T, int D>
@@ -172,88 +206,82 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kBM, kBN, 0, 0);
       constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kBM, D, 0, 1);
-      constexpr uint32_t idesc_pv64 = ptx::make_idesc_f16(kBf16, kBM, 64, 0, 1);
-      const uint32_t col_s[2] = {tmem + C::kColS0, tmem + C::kColS1};
-      const uint32_t col_o[2] = {tmem + C::kColO0, tmem + C::kColO1};
       const int ntile = two ? 2 : 1;
       bool ok = true;
-
-      auto slot_addr = [&](int it) { return ring_smem + (it % C::kSlots) * C::kTileBytes; };
-      auto wait_full = [&](int it) {
-        if (!ptx::mbar_wait(&bars->kv_full[it % C::kSlots], (it / C::kSlots) & 1, abort_flag)) {
-          atomicCAS(a.status, 0u, 1u);
-          *abort_flag = 1;
-          return false;
-        }
-        return true;
-      };
       // Descriptors differ only in the 14-bit start-address field, so stepping through a tile is one add.
       const uint64_t desc_k_major = ptx::make_smem_desc_sw128(0, 16, 1024);            // Q, K
       const uint64_t desc_mn_major = ptx::make_smem_desc_sw128(0, kHalfBytes, 1024);   // V
-      auto addr_field = [](uint32_t smem_addr) { return (uint64_t)((smem_addr & 0x3FFFFu) >> 4); };
-      // S_t = Q_t K^T : both operands K-major, 128-byte swizzle, D/16 steps of k = 16
-      auto issue_qk = [&](int t, uint32_t k_addr) {
-        const uint64_t ad0 = desc_k_major | addr_field(q_smem + t * C::kTileBytes);
-        const uint64_t bd0 = desc_k_major | addr_field(k_addr);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t o = (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
-          ptx::mma_ss(col_s[t], ad0 + o, bd0 + o, idesc_qk, ks > 0 ? 1u : 0u);
-        }
-      };
-      // O_t (+)= P_t V : P from TMEM (two 16-bit keys per 32-bit column), V is [key][d] = MN-major
-      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate, int ksteps) {
-        const uint64_t bd0 = desc_mn_major | addr_field(v_addr);
-#pragma unroll 1
-        for (int kk = 0; kk < ksteps; ++kk) {
-          const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
-          const uint64_t bd = bd0 + (uint64_t)(kk * (2048 >> 4));
-          if (a.options & 1) {
-#pragma unroll
-            for (int hf = 0; hf < C::kHalves; ++hf)
-              ptx::mma_ts(col_o[t] + hf * 64, col_s[t] + kk * 8, bd + (uint64_t)(hf * (kHalfBytes >> 4)), idesc_pv64, acc);
-          } else {
-            ptx::mma_ts(col_o[t], col_s[t] + kk * 8, bd, idesc_pv, acc);
-          }
-        }
-      };
+      const uint64_t qd0 = desc_k_major | (uint64_t)((q_smem & 0x3FFFFu) >> 4);
+      const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
+      const uint64_t ring_k = desc_k_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
+      const uint64_t ring_v = desc_mn_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
+      const uint32_t s0 = tmem + C::kColS0, s1 = tmem + C::kColS1, o0 = tmem + C::kColO0, o1 = tmem + C::kColO1;
 
-      if (!ptx::mbar_wait(&bars->q_full, 0, abort_flag)) {
+      if (!ptx::mbar_wait(&bars->q_full, 0, abort_flag) || !ptx::mbar_wait(&bars->kv_full[0], 0, abort_flag)) {
         atomicCAS(a.status, 0u, 1u);
         *abort_flag = 1;
         ok = false;
       }
-      if (ok && wait_full(0)) {
+      if (ok) {
         ptx::tc_fence_after();
-        for (int t = 0; t < ntile; ++t) {
-          issue_qk(t, slot_addr(0));
-          ptx::tc_commit(&bars->s_full[t]);
+        issue_qk<D>(s0, qd0, ring_k, idesc_qk);
+        ptx::tc_commit(&bars->s_full[0]);
+        if (ntile == 2) {
+          issue_qk<D>(s1, qd1, ring_k, idesc_qk);
+          ptx::tc_commit(&bars->s_full[1]);
         }
         ptx::tc_commit(&bars->kv_empty[0]);
-      } else {
-        ok = false;
       }
+      // ring position of V(j) and K(j+1): items are K0 V0 K1 V1 ...
+      int slot_v = 1 % C::kSlots, par_v = 0;
       for (int j = 0; j < nkv && ok; ++j) {
-        const int it_v = 2 * j + 1, it_kn = 2 * j + 2;
+        int slot_k = slot_v + 1, par_k = par_v;
+        if (slot_k == C::kSlots) { slot_k = 0; par_k ^= 1; }
         const bool more = j + 1 < nkv;
         const int valid = min(kBN, a.Sk - j * kBN);
         const int ksteps = (valid + 15) >> 4;
-        if (!wait_full(it_v)) { ok = false; break; }
-        if (more && !wait_full(it_kn)) { ok = false; break; }
-        for (int t = 0; t < ntile; ++t) {
-          if (!ptx::mbar_wait(&bars->p_full[t], j & 1, abort_flag)) {
+        if (!ptx::mbar_wait(&bars->kv_full[slot_v], par_v, abort_flag) ||
+            (more && !ptx::mbar_wait(&bars->kv_full[slot_k], par_k, abort_flag))) {
+          atomicCAS(a.status, 0u, 1u);
+          *abort_flag = 1;
+          break;
+        }
+        const uint64_t vd = ring_v + (uint64_t)(slot_v * (C::kTileBytes >> 4));
+        const uint64_t kd = ring_k + (uint64_t)(slot_k * (C::kTileBytes >> 4));
+        // ---- tile 0 ----
+        if (!ptx::mbar_wait(&bars->p_full[0], j & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 4u);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::tc_fence_after();
+        if (j < 40) stamp(a, (j * 2 + 0) * 2);
+        issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, ksteps);
+        if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
+        if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
+        ptx::tc_commit(&bars->s_full[0]);  // next S ready, or (last block) O complete
+        if (more && ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_k]);
+        if (j < 40) stamp(a, (j * 2 + 0) * 2 + 1);
+        // ---- tile 1 ----
+        if (ntile == 2) {
+          if (!ptx::mbar_wait(&bars->p_full[1], j & 1, abort_flag)) {
             atomicCAS(a.status, 0u, 4u);
             *abort_flag = 1;
-            ok = false;
             break;
           }
           ptx::tc_fence_after();
-          issue_pv(t, slot_addr(it_v), j > 0, ksteps);
-          if (t == ntile - 1) ptx::tc_commit(&bars->kv_empty[it_v % C::kSlots]);
-          if (more) issue_qk(t, slot_addr(it_kn));
-          ptx::tc_commit(&bars->s_full[t]);  // next S ready, or (last block) O complete
-          if (more && t == ntile - 1) ptx::tc_commit(&bars->kv_empty[it_kn % C::kSlots]);
+          if (j < 40) stamp(a, (j * 2 + 1) * 2);
+          issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, ksteps);
+          ptx::tc_commit(&bars->kv_empty[slot_v]);
+          if (more) issue_qk<D>(s1, qd1, kd, idesc_qk);
+          ptx::tc_commit(&bars->s_full[1]);
+          if (more) ptx::tc_commit(&bars->kv_empty[slot_k]);
+          if (j < 40) stamp(a, (j * 2 + 1) * 2 + 1);
         }
+        // advance two ring items
+        slot_v = slot_k + 1;
+        par_v = par_k;
+        if (slot_v == C::kSlots) { slot_v = 0; par_v ^= 1; }
       }
     }
   }
@@ -279,14 +307,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           break;
         }
         ptx::tc_fence_after();
+        const bool probe = (warp & 3) == 0 && lane == 0 && j < 40;
+        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 0);
         uint32_t s[4][32];
         ptx::tmem_ld32(t_s + 0, s[0]);
         ptx::tmem_ld32(t_s + 32, s[1]);
         ptx::tmem_ld32(t_s + 64, s[2]);
         ptx::tmem_ld32(t_s + 96, s[3]);
         ptx::tc_wait_ld();
+        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 1);
 
-        if (a.dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        if (a.dbg != nullptr && !(a.options & 2) && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
           float* dst = a.dbg + ((size_t)t * kBM + row_in_tile) * kBN;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -315,6 +346,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
         mx *= a.scale_log2;  // scale > 0 is a precondition of this kernel
+        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 2);
         const float m_cand = fmaxf(m_used, mx);
         // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
         const bool grow = (m_cand - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_cand != -INFINITY);
@@ -349,9 +381,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int i = 0; i < 16; ++i) {
             const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
                                                scale2, neg_m2);
-            float x0, x1;
-            ptx::unpack_f32x2(x2, x0, x1);
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            float p0, p1;
+            if ((i % kPolyPeriod) == kPolyPeriod - 1) {  // a share of the exponentials runs on the FMA pipes
+              ptx::exp2_poly_x2(x2, p0, p1);
+            } else {
+              float x0, x1;
+              ptx::unpack_f32x2(x2, x0, x1);
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+            }
             lsum[c] = ptx::add_f32x2(lsum[c], ptx::pack_f32x2(p0, p1));
             pk[i] = kBf16 ? ptx::cvt_pack_bf16(p0, p1) : ptx::cvt_pack_f16(p0, p1);
           }
@@ -363,9 +401,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ptx::unpack_f32x2(ptx::add_f32x2(lsum[2], lsum[3]), b0, b1);
           l += (a0 + a1) + (b0 + b1);
         }
+        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 3);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(&bars->p_full[t]);
+        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 4);
       }
 
       // ---- epilogue: O / l -> global ----

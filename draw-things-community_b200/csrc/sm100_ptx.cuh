@@ -267,6 +267,29 @@ __device__ __forceinline__ uint32_t cvt_pack_f16(float lo, float hi) {
   return d;
 }
 
+// 2^x for a pair of fp32 values on the FMA/ALU pipes instead of the special-function unit: round-to-nearest
+// range reduction with the 1.5*2^23 trick, degree-3 minimax polynomial on [-0.5, 0.5] (relative error
+// 7.5e-5, far below the rounding of the 16-bit P it feeds), exponent added with integer arithmetic.
+// Valid for x <= ~100; x below -125 (including -inf) is clamped and yields ~2^-125.
+__device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x0 = fmaxf(x0, -125.f);
+  x1 = fmaxf(x1, -125.f);
+  x2 = pack_f32x2(x0, x1);
+  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t r2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(r2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t q2 = fma_f32x2(pack_f32x2(0.05517166f, 0.05517166f), f2, pack_f32x2(0.24261113f, 0.24261113f));
+  q2 = fma_f32x2(q2, f2, pack_f32x2(0.69326097f, 0.69326097f));
+  q2 = fma_f32x2(q2, f2, pack_f32x2(0.99992806f, 0.99992806f));
+  float q0, q1, t0, t1;
+  unpack_f32x2(q2, q0, q1);
+  unpack_f32x2(t2, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>
