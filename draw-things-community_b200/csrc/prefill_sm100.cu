@@ -33,7 +33,10 @@ constexpr int kThreads = 384;
 constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 x 16-bit] = 16 KB, one TMA box
 constexpr float kRescaleThreshold = 8.f;
 // every kPolyPeriod-th pair of exponentials is evaluated with the polynomial instead of MUFU.EX2
-constexpr int kPolyPeriod = 2;
+#ifndef DT_POLY_PERIOD
+#define DT_POLY_PERIOD 4
+#endif
+constexpr int kPolyPeriod = DT_POLY_PERIOD;
 // 128 * kRegsLow + 256 * kRegsHigh must not exceed what the CTA was launched with (384 threads * 168)
 constexpr int kRegsLow = 80, kRegsHigh = 208;
 
@@ -65,7 +68,7 @@ struct PrefillArgs {
 struct Barriers {
   uint64_t q_full;
   uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t p_half[2][2];  // [tile][first / second 64 keys of P written]
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
   uint32_t tmem_base;
@@ -97,15 +100,17 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint64_t q_desc, uint6
 // O (+)= P V for one tile: P from TMEM (two 16-bit keys per 32-bit column, 8 columns per step), V is
 // [key][d] = MN-major; one step consumes 16 keys = 2 KB of each 64-wide half.
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc,
-                                         uint32_t accumulate, int ksteps) {
-  if (ksteps == kBN / 16) {
+                                         uint32_t accumulate, int k_begin, int k_end) {
+  if (k_end - k_begin == 4) {
 #pragma unroll
-    for (int kk = 0; kk < kBN / 16; ++kk)
-      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, kk > 0 ? 1u : accumulate);
+    for (int i = 0; i < 4; ++i) {
+      const int kk = k_begin + i;
+      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, (kk > 0) ? 1u : accumulate);
+    }
   } else {
 #pragma unroll 1
-    for (int kk = 0; kk < ksteps; ++kk)
-      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, kk > 0 ? 1u : accumulate);
+    for (int kk = k_begin; kk < k_end; ++kk)
+      ptx::mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc, (kk > 0) ? 1u : accumulate);
   }
 }
 
@@ -148,7 +153,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     ptx::mbar_init(&bars->q_full, 1);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(&bars->s_full[t], 1);
-      ptx::mbar_init(&bars->p_full[t], 128);
+      ptx::mbar_init(&bars->p_half[t][0], 4);  // one arrival per softmax warp
+      ptx::mbar_init(&bars->p_half[t][1], 4);
     }
     for (int i = 0; i < C::kSlots; ++i) {
       ptx::mbar_init(&bars->kv_full[i], 1);
@@ -248,35 +254,55 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const uint64_t vd = ring_v + (uint64_t)(slot_v * (C::kTileBytes >> 4));
         const uint64_t kd = ring_k + (uint64_t)(slot_k * (C::kTileBytes >> 4));
-        // ---- tile 0 ----
-        if (!ptx::mbar_wait(&bars->p_full[0], j & 1, abort_flag)) {
+        if (j < 40) stamp(a, 4000 + j * 16 + 0);
+        // ---- tile 0 ----  (P arrives in two halves of 64 keys so P*V starts while the softmax still runs)
+        const int k_mid = min(ksteps, 4);
+        if (!ptx::mbar_wait(&bars->p_half[0][0], j & 1, abort_flag)) {
           atomicCAS(a.status, 0u, 4u);
           *abort_flag = 1;
           break;
         }
         ptx::tc_fence_after();
-        if (j < 40) stamp(a, (j * 2 + 0) * 2);
-        issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, ksteps);
+        if (j < 40) stamp(a, 4000 + j * 16 + 1);
+        issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+        if (j < 40) stamp(a, 4000 + j * 16 + 2);
+        if (!ptx::mbar_wait(&bars->p_half[0][1], j & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 4u);
+          *abort_flag = 1;
+          break;
+        }
+        if (j < 40) stamp(a, 4000 + j * 16 + 3);
+        ptx::tc_fence_after();
+        issue_pv(o0, s0, vd, idesc_pv, 1u, k_mid, ksteps);
         if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
         if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
         ptx::tc_commit(&bars->s_full[0]);  // next S ready, or (last block) O complete
         if (more && ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_k]);
-        if (j < 40) stamp(a, (j * 2 + 0) * 2 + 1);
+        if (j < 40) stamp(a, 4000 + j * 16 + 4);
         // ---- tile 1 ----
         if (ntile == 2) {
-          if (!ptx::mbar_wait(&bars->p_full[1], j & 1, abort_flag)) {
+          if (!ptx::mbar_wait(&bars->p_half[1][0], j & 1, abort_flag)) {
             atomicCAS(a.status, 0u, 4u);
             *abort_flag = 1;
             break;
           }
           ptx::tc_fence_after();
-          if (j < 40) stamp(a, (j * 2 + 1) * 2);
-          issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, ksteps);
+          if (j < 40) stamp(a, 4000 + j * 16 + 5);
+          issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+          if (j < 40) stamp(a, 4000 + j * 16 + 6);
+          if (!ptx::mbar_wait(&bars->p_half[1][1], j & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 4u);
+            *abort_flag = 1;
+            break;
+          }
+          if (j < 40) stamp(a, 4000 + j * 16 + 7);
+          ptx::tc_fence_after();
+          issue_pv(o1, s1, vd, idesc_pv, 1u, k_mid, ksteps);
           ptx::tc_commit(&bars->kv_empty[slot_v]);
           if (more) issue_qk<D>(s1, qd1, kd, idesc_qk);
           ptx::tc_commit(&bars->s_full[1]);
           if (more) ptx::tc_commit(&bars->kv_empty[slot_k]);
-          if (j < 40) stamp(a, (j * 2 + 1) * 2 + 1);
+          if (j < 40) stamp(a, 4000 + j * 16 + 8);
         }
         // advance two ring items
         slot_v = slot_k + 1;
@@ -394,6 +420,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             pk[i] = kBf16 ? ptx::cvt_pack_bf16(p0, p1) : ptx::cvt_pack_f16(p0, p1);
           }
           ptx::tmem_st16(t_s + c * 16, pk);
+          if (c == 1 || c == 3) {  // 64 keys of P are in TMEM: let the MMA warp start on them
+            ptx::tc_wait_st();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&bars->p_half[t][c >> 1]);
+            if (lane == 0 && j < 40) stamp(a, 2048 + ((t * 4 + (warp & 3)) * 40 + j) * 2 + (c >> 1));
+            if (c == 1) {
+              // keep the second half's arithmetic after this hand-off: without the pin the compiler
+              // interleaves all four chunks and the first half is not finished any earlier
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                asm volatile("" : "+r"(s[2][i]));
+                asm volatile("" : "+r"(s[3][i]));
+              }
+            }
+          }
         }
         {
           float a0, a1, b0, b1;
@@ -402,9 +444,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           l += (a0 + a1) + (b0 + b1);
         }
         if (probe) stamp(a, 1024 + t * 512 + j * 8 + 3);
-        ptx::tc_wait_st();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(&bars->p_full[t]);
         if (probe) stamp(a, 1024 + t * 512 + j * 8 + 4);
       }
 

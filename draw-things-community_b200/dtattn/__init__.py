@@ -21,7 +21,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "..", "lib", "libdtattn.so")
+LIB_PATH = os.environ.get("DTATTN_LIB") or os.path.join(_HERE, "..", "lib", "libdtattn.so")
 
 DT_OK, DT_BAD_ARG, DT_UNSUPPORTED, DT_WORKSPACE, DT_CUDA, DT_NCCL, DT_TIMEOUT, DT_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6, -7
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
