@@ -71,6 +71,7 @@ struct Barriers {
   uint64_t p_half[2][2];  // [tile][first / second 64 keys of P written]
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
+  uint64_t probe_bar;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -160,6 +161,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ptx::mbar_init(&bars->kv_full[i], 1);
       ptx::mbar_init(&bars->kv_empty[i], 1);
     }
+    ptx::mbar_init(&bars->probe_bar, 1);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -240,6 +242,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       // ring position of V(j) and K(j+1): items are K0 V0 K1 V1 ...
       int slot_v = 1 % C::kSlots, par_v = 0;
+      uint32_t probe_ph = 0;
       for (int j = 0; j < nkv && ok; ++j) {
         int slot_k = slot_v + 1, par_k = par_v;
         if (slot_k == C::kSlots) { slot_k = 0; par_k ^= 1; }
@@ -264,7 +267,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         ptx::tc_fence_after();
         if (j < 40) stamp(a, 4000 + j * 16 + 1);
+        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 9); }
         issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; }
         if (j < 40) stamp(a, 4000 + j * 16 + 2);
         if (!ptx::mbar_wait(&bars->p_half[0][1], j & 1, abort_flag)) {
           atomicCAS(a.status, 0u, 4u);
@@ -274,8 +279,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (j < 40) stamp(a, 4000 + j * 16 + 3);
         ptx::tc_fence_after();
         issue_pv(o0, s0, vd, idesc_pv, 1u, k_mid, ksteps);
+        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 10); }
         if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
         if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
+        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 11); }
         ptx::tc_commit(&bars->s_full[0]);  // next S ready, or (last block) O complete
         if (more && ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_k]);
         if (j < 40) stamp(a, 4000 + j * 16 + 4);
