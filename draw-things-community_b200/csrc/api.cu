@@ -121,6 +121,7 @@ const char* dt_status_string(int status) {
     case DT_NCCL: return "NCCL unavailable or failed";
     case DT_TIMEOUT: return "bounded wait ran out";
     case DT_NO_DEVICE: return "no usable sm_100 device";
+    case DT_SCRATCH_LIMIT: return "request exceeds the built-in scratch of dt_sdpa_decode_noalloc";
   }
   return "unknown status";
 }

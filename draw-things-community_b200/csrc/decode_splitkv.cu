@@ -18,6 +18,8 @@
 //           CTA, so nothing can hang.
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "sm100_ptx.cuh"
 
 namespace dt {
@@ -514,3 +516,97 @@ int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaSt
 }
 
 }  // namespace dt
+
+// ---- entry point that allocates nothing ----------------------------------------------------------------
+// Scratch for the split-KV partials lives in a file-scope device array instead of a caller workspace.
+// Every GPU that loads the library holds these DT_NOALLOC_SCRATCH_BYTES until the process exits.
+namespace dt {
+namespace {
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DT_NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(256) unsigned int g_noalloc_status[64];
+
+// In host code the two names above are host-side stand-ins, not device addresses: the real addresses come
+// from cudaGetSymbolAddress, once per device, with that device current.
+struct NoAllocDevice {
+  unsigned char* scratch = nullptr;
+  unsigned int* status = nullptr;
+  bool attr[4] = {false, false, false, false};
+};
+NoAllocDevice g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
+
+int noalloc_setup(int dev, NoAllocDevice** out) {
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.scratch) {
+    void* ps = nullptr;
+    void* pst = nullptr;
+    DT_CUDA_TRY(cudaGetSymbolAddress(&ps, g_noalloc_scratch));
+    DT_CUDA_TRY(cudaGetSymbolAddress(&pst, g_noalloc_status));
+    d.scratch = reinterpret_cast<unsigned char*>(ps);
+    d.status = reinterpret_cast<unsigned int*>(pst);
+  }
+  *out = &d;
+  return DT_OK;
+}
+
+template <typename T, int D>
+int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, cudaStream_t stream) {
+  using C = Cfg<D>;
+  const Plan pl = make_plan(p);
+  const int G = p.Hq / p.Hkv, M = p.Sq * G;
+  const size_t pairs = (size_t)p.B * p.Hkv;
+  DecodeArgs a{};
+  if (pl.nsplit > 1) {
+    if (decode_workspace_bytes(p) > (size_t)DT_NOALLOC_SCRATCH_BYTES) return DT_SCRATCH_LIMIT;
+    unsigned char* w = dev->scratch;
+    a.counters = reinterpret_cast<unsigned int*>(w);
+    size_t off = align_up(pairs * sizeof(unsigned int), 256);
+    a.part_ml = reinterpret_cast<float*>(w + off);
+    off += align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256);
+    a.part_o = reinterpret_cast<float*>(w + off);
+    // the array keeps whatever the previous call left: the ticket counters must start at zero
+    DT_CUDA_TRY(cudaMemsetAsync(a.counters, 0, pairs * sizeof(unsigned int), stream));
+  }
+  CUtensorMap mk, mv;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
+  a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
+  a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
+  a.status = dev->status;
+  a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
+  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
+  a.scale_log2 = p.scale * kLog2e;
+  a.is_causal = p.is_causal;
+  auto kern = decode_splitkv_kernel<T, D>;
+  if (!dev->attr[variant]) {
+    DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    dev->attr[variant] = true;
+  }
+  dim3 grid(pl.nsplit, p.Hkv, p.B);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mk, mv, a);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace
+}  // namespace dt
+
+extern "C" int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream) {
+  using namespace dt;
+  if (!p || !p->q.ptr || !p->k.ptr || !p->v.ptr || !p->o.ptr) return DT_BAD_ARG;
+  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Hq % p->Hkv) return DT_BAD_ARG;
+  if (!decode_supported(*p)) return DT_UNSUPPORTED;
+  int dev = 0;
+  DT_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return DT_NO_DEVICE;
+  NoAllocDevice* d = nullptr;
+  int st = noalloc_setup(dev, &d);
+  if (st != DT_OK) return st;
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  if (p->dtype == DT_F16)
+    return p->D == 128 ? launch_noalloc_t<__half, 128>(*p, d, 0, s) : launch_noalloc_t<__half, 64>(*p, d, 1, s);
+  return p->D == 128 ? launch_noalloc_t<__nv_bfloat16, 128>(*p, d, 2, s) : launch_noalloc_t<__nv_bfloat16, 64>(*p, d, 3, s);
+}

@@ -24,6 +24,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("DTATTN_LIB") or os.path.join(_HERE, "..", "lib", "libdtattn.so")
 
 DT_OK, DT_BAD_ARG, DT_UNSUPPORTED, DT_WORKSPACE, DT_CUDA, DT_NCCL, DT_TIMEOUT, DT_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6, -7
+DT_SCRATCH_LIMIT = -8
+NOALLOC_SCRATCH_BYTES = 8 << 20
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 DT_FLAG_FP16_ACCUM_HINT, DT_FLAG_FORCE_GENERIC = 1, 2
 _DTYPES = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
@@ -64,6 +66,7 @@ SYMBOLS = [
     ("dt_sdpa_forward_host", ctypes.c_int, [_P(SdpaParams)]),
     ("dt_host_release", ctypes.c_int, []),
     ("dt_device_status", ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int)]),
+    ("dt_sdpa_decode_noalloc", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p]),
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
     ("dt_comm_destroy", ctypes.c_int, [ctypes.c_void_p]),

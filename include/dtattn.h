@@ -37,7 +37,8 @@ typedef enum {
   DT_CUDA = -4,         /* a CUDA runtime/driver call failed (dt_last_cuda_error gives the code)        */
   DT_NCCL = -5,         /* NCCL missing or a collective failed                                          */
   DT_TIMEOUT = -6,      /* a bounded wait ran out (device status word or communicator set-up)           */
-  DT_NO_DEVICE = -7     /* no sm_100 device / library built without the kernel                          */
+  DT_NO_DEVICE = -7,    /* no sm_100 device / library built without the kernel                          */
+  DT_SCRATCH_LIMIT = -8 /* dt_sdpa_decode_noalloc: the request needs more than DT_NOALLOC_SCRATCH_BYTES  */
 } dt_status;
 
 typedef enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2 } dt_dtype;
@@ -106,6 +107,28 @@ int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name);
  */
 int dt_sdpa_forward_host(const dt_sdpa_params* p_host);
 int dt_host_release(void);
+
+/* Decode without any allocation ---------------------------------------------------------------------
+ * No counterpart in the reference.  Some hosts of this library cannot obtain device memory at the moment
+ * they call: a runtime that handed the whole device to its own allocator at start-up (the reference's graph
+ * executor owns device memory this way) has nothing left for a late cudaMalloc, and inside a latency-bound
+ * token loop a device allocation would also stall every stream while it runs.  For them this entry point
+ * runs the split-KV decode kernel (the same shapes dt_sdpa_forward routes to "decode_splitkv": fp16/bf16,
+ * D 64 or 128, Sq * Hq/Hkv <= 16, no mask) with its partial results kept in a fixed array of
+ * DT_NOALLOC_SCRATCH_BYTES that is part of the library image; each GPU that loads the library holds that
+ * array until the process ends.  It calls no cudaMalloc, cudaFree or allocating library routine; the caller
+ * still owns q, k, v, o (and lse).
+ *   - A request whose partials do not fit returns DT_SCRATCH_LIMIT and launches nothing.
+ *   - The first call on a device looks the array's address up (once per device, with that device current);
+ *     make that first call outside of any stream capture.
+ *   - All calls on a device share the one array and it keeps what the last call wrote.  The call clears the
+ *     few words that must start at zero, on `cuda_stream`.  Two calls that overlap on the GPU (different
+ *     streams, or different host threads without ordering) race on it: serialise them.
+ *   - A device-side wait that runs out is recorded in a status word inside the library image, not the one
+ *     dt_device_status reads.
+ */
+#define DT_NOALLOC_SCRATCH_BYTES (8u << 20)
+int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream);
 
 /* Device status word ------------------------------------------------------------------------------
  * Kernels never spin without a bound: a wait that runs out stores a non-zero code into a per-device
