@@ -5,7 +5,7 @@
 // link-time NCCL dependency, and a process that already loaded an NCCL (PyTorch's) shares it.
 //
 // The reference has no counterpart: it is single-GPU per process (ccv is built with have_nccl = False,
-// WORKSPACE.linux:127).  No TMA multicast and no peer-memory TMA load is used anywhere on this path.
+// WORKSPACE.linux:127).  Every TMA load on this path is a plain per-CTA load from this GPU's own memory.
 #include <dlfcn.h>
 #include <nccl.h>
 

@@ -8,7 +8,7 @@
 //   grid  = (splits, Hkv, B); one CTA streams a contiguous range of 16-key units of ONE KV head and
 //           serves all M = Sq * (Hq/Hkv) <= 16 query rows that read it, so K/V are read exactly once.
 //   CTA   = 4 consumer warps + 1 producer warp.  The producer issues TMA tile loads (boxes of
-//           16 keys x 64 dims, 128-byte swizzle, no multicast) into a ring of stages; each consumer warp
+//           16 keys x 64 dims, 128-byte swizzle, per-CTA loads) into a ring of stages; each consumer warp
 //           owns one 16-key unit per stage: S^T = Q K^T and O += P V with mma.sync m16n8k16 (fp32
 //           accumulate) fed by ldmatrix from the swizzled tiles, online softmax in registers with
 //           warp-shuffle reductions.

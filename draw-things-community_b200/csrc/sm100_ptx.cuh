@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use: mbarrier, TMA
-// (cp.async.bulk.tensor, never with cluster multicast), tcgen05 MMA / TMEM, ldmatrix / mma.sync.
+// (cp.async.bulk.tensor, each CTA loading only for itself), tcgen05 MMA / TMEM, ldmatrix / mma.sync.
 // Every wait is bounded: it gives up after a wall-clock limit and reports failure to the caller.
 #pragma once
 

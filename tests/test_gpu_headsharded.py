@@ -1,0 +1,71 @@
+"""Head-sharded attention on 2 GPUs (skipped on a single-GPU box): each rank computes its heads, the output
+is exchanged with NCCL and laid out as [B,Sq,H,D]; every rank must hold the same full result as the oracle."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "draw-things-community_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    import dtattn
+    from dtattn import sharding
+    from oracle import sdpa_oracle as so
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        def bcast(b):
+            obj = [b]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+        comm = dtattn.HeadShardedComm(rank, world, bcast, timeout_ms=60000)
+        errs = []
+        for (B, S, H, D, chunks) in [(1, 1000, 8, 128, 3), (2, 300, 4, 64, 1)]:
+            cfg = so.AttnConfig("t", B, S, S, H, H, D, "bf16", 7)
+            q0, q1, kv0, kv1 = sharding.head_range(rank, world, H, H)
+            ql, kl, vl = so.make_inputs(cfg, heads=(q0, q1))
+            o_full = torch.zeros((B, S, H, D), dtype=torch.bfloat16, device=dev)
+            comm.forward(ql.to(dev), kl.to(dev), vl.to(dev), cfg.scale, o_full, chunks=chunks)
+            torch.cuda.synchronize()
+            qf, kf, vf = so.make_inputs(cfg, heads=(0, H))
+            ref = so.sdpa_explicit(qf, kf, vf, cfg.scale)
+            errs.append(so.error_stats(o_full.float().cpu(), ref))
+        comm.close()
+        q.put((rank, errs, dtattn.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, errs, status in res:
+        assert status == 0
+        for mx, mean in errs:
+            assert mx <= 2e-3 + 2 ** -8 and mean <= 4e-4, (rank, errs)
