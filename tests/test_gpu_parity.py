@@ -179,6 +179,19 @@ def test_decode_workspace_contract(dtattn):
     assert int(ws[:4096].view(torch.int32)[: cfg.B * cfg.Hkv].abs().sum()) == 0, "ticket counters must return to zero"
 
 
+def test_decode_shapes_share_one_workspace(dtattn):
+    """Calls of different shapes through the same workspace: the ticket counters of one call must never
+    land where another call left partial results."""
+    ws = dtattn.Workspace(torch.device(DEV))
+    shapes = [(1, 1, 8192, 32, 8, 128), (16, 1, 4096, 32, 8, 128), (2, 4, 2000, 16, 4, 128), (16, 1, 4096, 32, 8, 128),
+              (1, 1, 8192, 32, 8, 128)]
+    for i, (B, Sq, Sk, Hq, Hkv, D) in enumerate(shapes):
+        q, k, v = inputs(B, Sq, Sk, Hq, Hkv, D, torch.float16, 200 + i)
+        out = dtattn.sdpa_forward(q.to(DEV), k.to(DEV), v.to(DEV), D ** -0.5, True, workspace=ws)
+        torch.cuda.synchronize()
+        check(out, oracle(q, k, v, D ** -0.5, True), torch.float16, f"shared workspace {i}")
+
+
 # --------------------------------------------------------------------------------------------------
 # tcgen05 prefill kernel
 # --------------------------------------------------------------------------------------------------

@@ -5,6 +5,7 @@ bytes: this test runs two calls in a row on different inputs through the C ABI a
 workspace-based entry point (dt_sdpa_forward).  Collected last (file name) so that a failure here cannot hide
 another test when a run stops at the first failure."""
 import ctypes
+import os
 
 import pytest
 import torch
@@ -51,9 +52,14 @@ def test_noalloc_rejects_requests_beyond_its_array(dtattn):
     q, k, v = _case(331, 1, 256, 32, 8, 128, torch.float16)
     o = torch.empty_like(q)
     p = dtattn.make_params(q, k, v, o, 128 ** -0.5, True)
-    p.B, p.Sq, p.Sk = 16, 4, 8192  # sizes only (16 rows per KV head, many splits): refused before any pointer is used
-    assert dtattn.workspace_size(p) > dtattn.NOALLOC_SCRATCH_BYTES
-    assert lib.dt_sdpa_decode_noalloc(ctypes.byref(p), None) == dtattn.DT_SCRATCH_LIMIT
+    p.B, p.Sq, p.Sk = 16, 4, 8192  # sizes only: the request is refused before any pointer is used
+    # the library's own split choice keeps the partials small; a forced split count (tuning override) does not
+    os.environ["DTATTN_DECODE_SPLITS"] = "128"
+    try:
+        assert dtattn.workspace_size(p) > dtattn.NOALLOC_SCRATCH_BYTES
+        assert lib.dt_sdpa_decode_noalloc(ctypes.byref(p), None) == dtattn.DT_SCRATCH_LIMIT
+    finally:
+        del os.environ["DTATTN_DECODE_SPLITS"]
     assert "scratch" in dtattn.status_string(dtattn.DT_SCRATCH_LIMIT)
     # shapes the decode kernel does not serve are refused as well
     p2 = dtattn.make_params(torch.empty(1, 64, 8, 128, dtype=torch.float16, device=DEV), k[:1], v[:1],
