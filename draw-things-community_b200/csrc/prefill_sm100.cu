@@ -62,16 +62,18 @@ struct PrefillArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int is_causal;
-  int options;  // bit 1: record a clock64 timeline of CTA (0,0,0) into dbg (bring-up probe)
+  int options;  // reserved for bring-up experiments
+  int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
 };
 
 struct Barriers {
   uint64_t q_full;
+  uint64_t q_empty;
   uint64_t s_full[2];
+  uint64_t o_full[2];  // all P*V of an item done: O may be read (separate from s_full so no barrier runs two phases ahead)
   uint64_t p_half[2][2];  // [tile][first / second 64 keys of P written]
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
-  uint64_t probe_bar;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -115,12 +117,6 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint6
   }
 }
 
-// Timeline probe (options bit 1): clock64 stamps of CTA (0,0,0) into the debug buffer.
-__device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
-  if ((a.options & 2) && a.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-    reinterpret_cast<long long*>(a.dbg)[slot] = clock64();
-}
-
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -136,24 +132,41 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int kvh = h / (a.Hq / a.Hkv);
-  const int q0 = blockIdx.x * (2 * kBM);
-  const bool two = q0 + kBM < a.Sq;  // is the second query tile non-empty
-  const int off = a.Sk - a.Sq;       // causal: key j visible to query i iff j <= i + off
-  // number of key blocks this CTA visits
-  int nkv = (a.Sk + kBN - 1) / kBN;
-  if (a.is_causal) {
-    const int last_row = min(a.Sq, q0 + 2 * kBM) - 1;
-    const long long lim = (long long)last_row + off + 1;  // keys [0, lim) can be visible
-    const int need = (int)((max(0LL, min((long long)a.Sk, lim)) + kBN - 1) / kBN);
-    nkv = max(1, min(nkv, need));
-  }
+  const int off = a.Sk - a.Sq;  // causal: key j visible to query i iff j <= i + off
+  const int G = a.Hq / a.Hkv;
+
+  // Work items (batch, head, pair of query tiles), q-tile pair fastest so that CTAs running at the same
+  // time share one head's K/V in L2.  The CTA is persistent: it takes items blockIdx.x, + gridDim.x, ...
+  struct Item {
+    int b, h, kvh, q0, nkv;
+    bool two;
+  };
+  auto decode_item = [&](int item) {
+    Item it;
+    const int qt = item % a.n_qpairs;
+    const int bh = item / a.n_qpairs;
+    it.h = bh % a.Hq;
+    it.b = bh / a.Hq;
+    it.kvh = it.h / G;
+    it.q0 = qt * (2 * kBM);
+    it.two = it.q0 + kBM < a.Sq;
+    int nkv = (a.Sk + kBN - 1) / kBN;
+    if (a.is_causal) {
+      const int last_row = min(a.Sq, it.q0 + 2 * kBM) - 1;
+      const long long lim = (long long)last_row + off + 1;  // keys [0, lim) can be visible
+      const int need = (int)((max(0LL, min((long long)a.Sk, lim)) + kBN - 1) / kBN);
+      nkv = max(1, min(nkv, need));
+    }
+    it.nkv = nkv;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(&bars->q_full, 1);
+    ptx::mbar_init(&bars->q_empty, 1);
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(&bars->s_full[t], 1);
+      ptx::mbar_init(&bars->o_full[t], 1);
       ptx::mbar_init(&bars->p_half[t][0], 4);  // one arrival per softmax warp
       ptx::mbar_init(&bars->p_half[t][1], 4);
     }
@@ -161,7 +174,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ptx::mbar_init(&bars->kv_full[i], 1);
       ptx::mbar_init(&bars->kv_empty[i], 1);
     }
-    ptx::mbar_init(&bars->probe_bar, 1);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -178,185 +190,192 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // Register budget: the data-movement warpgroup gives registers back, the softmax warpgroups take them.
   // (Each setmaxnreg must dominate the code it governs, hence the nesting.)
   if (warp < 4) {
-  ptx::setmaxnreg_dec<kRegsLow>();
-  if (warp == 0) {
-    // =========================== TMA producer ===========================
-    if (lane == 0) {
-      ptx::prefetch_tensormap(&map_q);
-      ptx::prefetch_tensormap(&map_k);
-      ptx::prefetch_tensormap(&map_v);
-      ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)((two ? 2 : 1) * C::kTileBytes));
-      for (int t = 0; t < (two ? 2 : 1); ++t)
+    ptx::setmaxnreg_dec<kRegsLow>();
+    if (warp == 0) {
+      // =========================== TMA producer ===========================
+      if (lane == 0) {
+        ptx::prefetch_tensormap(&map_q);
+        ptx::prefetch_tensormap(&map_k);
+        ptx::prefetch_tensormap(&map_v);
+        int ring_it = 0;  // K/V ring position, continues across items
+        int n_item = 0;
+        bool ok = true;
+        auto load_kv = [&](const Item& w, int j, bool is_v) {
+          const int slot = ring_it % C::kSlots, use = ring_it / C::kSlots;
+          if (use > 0 && !ptx::mbar_wait(&bars->kv_empty[slot], (use - 1) & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 2u);
+            *abort_flag = 1;
+            return false;
+          }
+          ptx::mbar_arrive_expect_tx(&bars->kv_full[slot], (uint32_t)C::kTileBytes);
 #pragma unroll
-        for (int hf = 0; hf < C::kHalves; ++hf)
-          ptx::tma_load_4d(base_ptr + t * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full, hf * 64, h,
-                           q0 + t * kBM, b);
-      bool ok = true;
-      for (int it = 0; it < 2 * nkv && ok; ++it) {
-        const int slot = it % C::kSlots, use = it / C::kSlots;
-        if (use > 0 && !ptx::mbar_wait(&bars->kv_empty[slot], (use - 1) & 1, abort_flag)) {
-          atomicCAS(a.status, 0u, 2u);
+          for (int hf = 0; hf < C::kHalves; ++hf)
+            ptx::tma_load_4d(base_ptr + C::kQBytes + slot * C::kTileBytes + hf * kHalfBytes, is_v ? &map_v : &map_k,
+                             &bars->kv_full[slot], hf * 64, w.kvh, j * kBN, w.b);
+          ++ring_it;
+          return true;
+        };
+        for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
+          const Item w = decode_item(item);
+          // first K/V block of this item may be fetched while the previous item still owns the Q buffers
+          ok = load_kv(w, 0, false) && load_kv(w, 0, true);
+          if (!ok) break;
+          if (n_item > 0 && !ptx::mbar_wait(&bars->q_empty, (n_item - 1) & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 2u);
+            *abort_flag = 1;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)((w.two ? 2 : 1) * C::kTileBytes));
+          for (int t = 0; t < (w.two ? 2 : 1); ++t)
+#pragma unroll
+            for (int hf = 0; hf < C::kHalves; ++hf)
+              ptx::tma_load_4d(base_ptr + t * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full, hf * 64, w.h,
+                               w.q0 + t * kBM, w.b);
+          for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
+        }
+      }
+    } else if (warp == 1) {
+      // =========================== MMA issuer ===========================
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kBM, kBN, 0, 0);
+        constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kBM, D, 0, 1);
+        // Descriptors differ only in the 14-bit start-address field, so stepping through a tile is one add.
+        const uint64_t desc_k_major = ptx::make_smem_desc_sw128(0, 16, 1024);            // Q, K
+        const uint64_t desc_mn_major = ptx::make_smem_desc_sw128(0, kHalfBytes, 1024);   // V
+        const uint64_t qd0 = desc_k_major | (uint64_t)((q_smem & 0x3FFFFu) >> 4);
+        const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
+        const uint64_t ring_k = desc_k_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
+        const uint64_t ring_v = desc_mn_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
+        const uint32_t s0 = tmem + C::kColS0, s1 = tmem + C::kColS1, o0 = tmem + C::kColO0, o1 = tmem + C::kColO1;
+        int slot = 0, par = 0;     // ring position of the next K/V block to consume
+        uint32_t pph0 = 0, pph1 = 0;  // phases of the P hand-off barriers, per tile
+        int n_item = 0;
+        bool ok = true;
+        auto fail = [&](unsigned code) {
+          atomicCAS(a.status, 0u, code);
           *abort_flag = 1;
           ok = false;
-          break;
-        }
-        const int j = it >> 1;
-        const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
-        ptx::mbar_arrive_expect_tx(&bars->kv_full[slot], (uint32_t)C::kTileBytes);
-#pragma unroll
-        for (int hf = 0; hf < C::kHalves; ++hf)
-          ptx::tma_load_4d(base_ptr + C::kQBytes + slot * C::kTileBytes + hf * kHalfBytes, map, &bars->kv_full[slot],
-                           hf * 64, kvh, j * kBN, b);
-      }
-    }
-  } else if (warp == 1) {
-    // =========================== MMA issuer ===========================
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kBM, kBN, 0, 0);
-      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kBM, D, 0, 1);
-      const int ntile = two ? 2 : 1;
-      bool ok = true;
-      // Descriptors differ only in the 14-bit start-address field, so stepping through a tile is one add.
-      const uint64_t desc_k_major = ptx::make_smem_desc_sw128(0, 16, 1024);            // Q, K
-      const uint64_t desc_mn_major = ptx::make_smem_desc_sw128(0, kHalfBytes, 1024);   // V
-      const uint64_t qd0 = desc_k_major | (uint64_t)((q_smem & 0x3FFFFu) >> 4);
-      const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
-      const uint64_t ring_k = desc_k_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
-      const uint64_t ring_v = desc_mn_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
-      const uint32_t s0 = tmem + C::kColS0, s1 = tmem + C::kColS1, o0 = tmem + C::kColO0, o1 = tmem + C::kColO1;
-
-      if (!ptx::mbar_wait(&bars->q_full, 0, abort_flag) || !ptx::mbar_wait(&bars->kv_full[0], 0, abort_flag)) {
-        atomicCAS(a.status, 0u, 1u);
-        *abort_flag = 1;
-        ok = false;
-      }
-      if (ok) {
-        ptx::tc_fence_after();
-        issue_qk<D>(s0, qd0, ring_k, idesc_qk);
-        ptx::tc_commit(&bars->s_full[0]);
-        if (ntile == 2) {
-          issue_qk<D>(s1, qd1, ring_k, idesc_qk);
-          ptx::tc_commit(&bars->s_full[1]);
-        }
-        ptx::tc_commit(&bars->kv_empty[0]);
-      }
-      // ring position of V(j) and K(j+1): items are K0 V0 K1 V1 ...
-      int slot_v = 1 % C::kSlots, par_v = 0;
-      uint32_t probe_ph = 0;
-      for (int j = 0; j < nkv && ok; ++j) {
-        int slot_k = slot_v + 1, par_k = par_v;
-        if (slot_k == C::kSlots) { slot_k = 0; par_k ^= 1; }
-        const bool more = j + 1 < nkv;
-        const int valid = min(kBN, a.Sk - j * kBN);
-        const int ksteps = (valid + 15) >> 4;
-        if (!ptx::mbar_wait(&bars->kv_full[slot_v], par_v, abort_flag) ||
-            (more && !ptx::mbar_wait(&bars->kv_full[slot_k], par_k, abort_flag))) {
-          atomicCAS(a.status, 0u, 1u);
-          *abort_flag = 1;
-          break;
-        }
-        const uint64_t vd = ring_v + (uint64_t)(slot_v * (C::kTileBytes >> 4));
-        const uint64_t kd = ring_k + (uint64_t)(slot_k * (C::kTileBytes >> 4));
-        if (j < 40) stamp(a, 4000 + j * 16 + 0);
-        // ---- tile 0 ----  (P arrives in two halves of 64 keys so P*V starts while the softmax still runs)
-        const int k_mid = min(ksteps, 4);
-        if (!ptx::mbar_wait(&bars->p_half[0][0], j & 1, abort_flag)) {
-          atomicCAS(a.status, 0u, 4u);
-          *abort_flag = 1;
-          break;
-        }
-        ptx::tc_fence_after();
-        if (j < 40) stamp(a, 4000 + j * 16 + 1);
-        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 9); }
-        issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
-        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; }
-        if (j < 40) stamp(a, 4000 + j * 16 + 2);
-        if (!ptx::mbar_wait(&bars->p_half[0][1], j & 1, abort_flag)) {
-          atomicCAS(a.status, 0u, 4u);
-          *abort_flag = 1;
-          break;
-        }
-        if (j < 40) stamp(a, 4000 + j * 16 + 3);
-        ptx::tc_fence_after();
-        issue_pv(o0, s0, vd, idesc_pv, 1u, k_mid, ksteps);
-        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 10); }
-        if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
-        if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
-        if (a.options & 4) { ptx::tc_commit(&bars->probe_bar); ptx::mbar_wait(&bars->probe_bar, probe_ph, abort_flag); probe_ph ^= 1; if (j < 40) stamp(a, 4000 + j * 16 + 11); }
-        ptx::tc_commit(&bars->s_full[0]);  // next S ready, or (last block) O complete
-        if (more && ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_k]);
-        if (j < 40) stamp(a, 4000 + j * 16 + 4);
-        // ---- tile 1 ----
-        if (ntile == 2) {
-          if (!ptx::mbar_wait(&bars->p_half[1][0], j & 1, abort_flag)) {
-            atomicCAS(a.status, 0u, 4u);
-            *abort_flag = 1;
+        };
+        auto advance = [&]() {
+          if (++slot == C::kSlots) { slot = 0; par ^= 1; }
+        };
+        for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
+          const Item w = decode_item(item);
+          const int ntile = w.two ? 2 : 1;
+          // ---- S_t(0) = Q_t K(0)^T ----
+          if (!ptx::mbar_wait(&bars->q_full, n_item & 1, abort_flag) || !ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
+            fail(1u);
             break;
           }
           ptx::tc_fence_after();
-          if (j < 40) stamp(a, 4000 + j * 16 + 5);
-          issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
-          if (j < 40) stamp(a, 4000 + j * 16 + 6);
-          if (!ptx::mbar_wait(&bars->p_half[1][1], j & 1, abort_flag)) {
-            atomicCAS(a.status, 0u, 4u);
-            *abort_flag = 1;
-            break;
+          {
+            const uint64_t kd = ring_k + (uint64_t)(slot * (C::kTileBytes >> 4));
+            issue_qk<D>(s0, qd0, kd, idesc_qk);
+            ptx::tc_commit(&bars->s_full[0]);
+            if (ntile == 2) {
+              issue_qk<D>(s1, qd1, kd, idesc_qk);
+              ptx::tc_commit(&bars->s_full[1]);
+            }
+            ptx::tc_commit(&bars->kv_empty[slot]);
+            if (w.nkv == 1) ptx::tc_commit(&bars->q_empty);  // Q is no longer needed: the next item may load its own
+            advance();
           }
-          if (j < 40) stamp(a, 4000 + j * 16 + 7);
-          ptx::tc_fence_after();
-          issue_pv(o1, s1, vd, idesc_pv, 1u, k_mid, ksteps);
-          ptx::tc_commit(&bars->kv_empty[slot_v]);
-          if (more) issue_qk<D>(s1, qd1, kd, idesc_qk);
-          ptx::tc_commit(&bars->s_full[1]);
-          if (more) ptx::tc_commit(&bars->kv_empty[slot_k]);
-          if (j < 40) stamp(a, 4000 + j * 16 + 8);
+          for (int j = 0; j < w.nkv && ok; ++j) {
+            const int slot_v = slot, par_v = par;
+            advance();
+            const int slot_k = slot, par_k = par;
+            const bool more = j + 1 < w.nkv;
+            if (more) advance();
+            const int valid = min(kBN, a.Sk - j * kBN);
+            const int ksteps = (valid + 15) >> 4;
+            const int k_mid = min(ksteps, 4);
+            if (!ptx::mbar_wait(&bars->kv_full[slot_v], par_v, abort_flag) ||
+                (more && !ptx::mbar_wait(&bars->kv_full[slot_k], par_k, abort_flag))) {
+              fail(1u);
+              break;
+            }
+            const uint64_t vd = ring_v + (uint64_t)(slot_v * (C::kTileBytes >> 4));
+            const uint64_t kd = ring_k + (uint64_t)(slot_k * (C::kTileBytes >> 4));
+            const bool last_qk = more && (j + 2 == w.nkv);  // the QK issued in this iteration is the item's last
+            // ---- tile 0 ----  (P arrives in two halves of 64 keys so P*V starts while the softmax still runs)
+            if (!ptx::mbar_wait(&bars->p_half[0][0], pph0, abort_flag)) { fail(4u); break; }
+            ptx::tc_fence_after();
+            issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+            if (!ptx::mbar_wait(&bars->p_half[0][1], pph0, abort_flag)) { fail(4u); break; }
+            pph0 ^= 1;
+            ptx::tc_fence_after();
+            issue_pv(o0, s0, vd, idesc_pv, 1u, k_mid, ksteps);
+            if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
+            if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
+            ptx::tc_commit(more ? &bars->s_full[0] : &bars->o_full[0]);  // next S ready, or (last block) O complete
+            if (more && ntile == 1) {
+              ptx::tc_commit(&bars->kv_empty[slot_k]);
+              if (last_qk) ptx::tc_commit(&bars->q_empty);
+            }
+            // ---- tile 1 ----
+            if (ntile == 2) {
+              if (!ptx::mbar_wait(&bars->p_half[1][0], pph1, abort_flag)) { fail(4u); break; }
+              ptx::tc_fence_after();
+              issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+              if (!ptx::mbar_wait(&bars->p_half[1][1], pph1, abort_flag)) { fail(4u); break; }
+              pph1 ^= 1;
+              ptx::tc_fence_after();
+              issue_pv(o1, s1, vd, idesc_pv, 1u, k_mid, ksteps);
+              ptx::tc_commit(&bars->kv_empty[slot_v]);
+              if (more) issue_qk<D>(s1, qd1, kd, idesc_qk);
+              ptx::tc_commit(more ? &bars->s_full[1] : &bars->o_full[1]);
+              if (more) {
+                ptx::tc_commit(&bars->kv_empty[slot_k]);
+                if (last_qk) ptx::tc_commit(&bars->q_empty);
+              }
+            }
+          }
         }
-        // advance two ring items
-        slot_v = slot_k + 1;
-        par_v = par_k;
-        if (slot_v == C::kSlots) { slot_v = 0; par_v ^= 1; }
       }
     }
-  }
   } else {
     ptx::setmaxnreg_inc<kRegsHigh>();
     // =========================== softmax / correction / epilogue ===========================
     const int t = (warp - 4) >> 2;  // tile
-    if (t == 0 || two) {
-      const int row_in_tile = ((warp & 3) << 5) + lane;
-      const int row = q0 + t * kBM + row_in_tile;
-      const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
-      const uint32_t t_s = tmem + (t ? C::kColS1 : C::kColS0) + lane_addr;
-      const uint32_t t_o = tmem + (t ? C::kColO1 : C::kColO0) + lane_addr;
+    const int row_in_tile = ((warp & 3) << 5) + lane;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
+    const uint32_t t_s = tmem + (t ? C::kColS1 : C::kColS0) + lane_addr;
+    const uint32_t t_o = tmem + (t ? C::kColO1 : C::kColO0) + lane_addr;
+    uint32_t sph = 0, oph = 0;  // phases of s_full[t] / o_full[t], continue across items
+    bool ok = true;
+    bool first_dump = true;
+
+    for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
+      const Item w = decode_item(item);
+      if (t == 1 && !w.two) continue;  // this item has no second tile: neither side touches tile 1's barriers
+      const int row = w.q0 + t * kBM + row_in_tile;
       const long long vis = a.is_causal ? (long long)row + off : (long long)a.Sk;  // last visible key
       float m_used = -INFINITY, l = 0.f;
-      bool ok = true;
 
-      for (int j = 0; j < nkv; ++j) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], j & 1, abort_flag))) {
+      for (int j = 0; j < w.nkv; ++j) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
           atomicCAS(a.status, 0u, 3u);
           *abort_flag = 1;
           ok = false;
           break;
         }
+        sph ^= 1;
         ptx::tc_fence_after();
-        const bool probe = (warp & 3) == 0 && lane == 0 && j < 40;
-        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 0);
         uint32_t s[4][32];
         ptx::tmem_ld32(t_s + 0, s[0]);
         ptx::tmem_ld32(t_s + 32, s[1]);
         ptx::tmem_ld32(t_s + 64, s[2]);
         ptx::tmem_ld32(t_s + 96, s[3]);
         ptx::tc_wait_ld();
-        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 1);
 
-        if (a.dbg != nullptr && !(a.options & 2) && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        if (a.dbg != nullptr && first_dump && j == 0 && blockIdx.x == 0) {
           float* dst = a.dbg + ((size_t)t * kBM + row_in_tile) * kBN;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) dst[c * 32 + i] = __uint_as_float(s[c][i]);
         }
+        first_dump = false;
 
         const int key0 = j * kBN;
         const bool need_mask = (key0 + kBN > a.Sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis);
@@ -379,7 +398,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
         mx *= a.scale_log2;  // scale > 0 is a precondition of this kernel
-        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 2);
         const float m_cand = fmaxf(m_used, mx);
         // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
         const bool grow = (m_cand - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_cand != -INFINITY);
@@ -400,8 +418,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
           }
         }
-        // p = exp2(s * scale_log2 - m): packed fp32x2 multiply-add, one MUFU per element, packed row sums in
-        // four independent accumulators, packed conversion to the 16-bit P the second MMA reads from TMEM
+        // p = exp2(s * scale_log2 - m): packed fp32x2 multiply-add, packed row sums in four independent
+        // accumulators, packed conversion to the 16-bit P the second MMA reads from TMEM
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
         const uint64_t scale2 = ptx::pack_f32x2(a.scale_log2, a.scale_log2);
@@ -432,16 +450,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bars->p_half[t][c >> 1]);
-            if (lane == 0 && j < 40) stamp(a, 2048 + ((t * 4 + (warp & 3)) * 40 + j) * 2 + (c >> 1));
-            if (c == 1) {
-              // keep the second half's arithmetic after this hand-off: without the pin the compiler
-              // interleaves all four chunks and the first half is not finished any earlier
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                asm volatile("" : "+r"(s[2][i]));
-                asm volatile("" : "+r"(s[3][i]));
-              }
-            }
           }
         }
         {
@@ -450,38 +458,41 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ptx::unpack_f32x2(ptx::add_f32x2(lsum[2], lsum[3]), b0, b1);
           l += (a0 + a1) + (b0 + b1);
         }
-        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 3);
-        if (probe) stamp(a, 1024 + t * 512 + j * 8 + 4);
       }
+      if (!ok) break;
 
-      // ---- epilogue: O / l -> global ----
-      if (ok && __all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], nkv & 1, abort_flag))) {
-        ptx::tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        T* orow = reinterpret_cast<T*>(a.o) + b * a.o_sb + (int64_t)row * a.o_ss + (int64_t)h * a.o_sh;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t ov[32];
-          ptx::tmem_ld32(t_o + c * 32, ov);
-          ptx::tc_wait_ld();
-          if (row < a.Sq) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 pk;
-              pk.x = pack_pair<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
-              pk.y = pack_pair<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
-              pk.z = pack_pair<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
-              pk.w = pack_pair<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pk;
-            }
-          }
-        }
-        if (a.lse && row < a.Sq)
-          a.lse[((int64_t)b * a.Hq + h) * a.Sq + row] = l > 0.f ? m_used * kLn2 + logf(l) : -INFINITY;
-      } else if (ok) {
+      // ---- epilogue: O / l -> global (the MMA warp already works on the next item's first S meanwhile) ----
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->o_full[t], oph, abort_flag))) {
         atomicCAS(a.status, 0u, 5u);
         *abort_flag = 1;
+        ok = false;
+        break;
       }
+      oph ^= 1;
+      ptx::tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* orow = reinterpret_cast<T*>(a.o) + w.b * a.o_sb + (int64_t)row * a.o_ss + (int64_t)w.h * a.o_sh;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ov[32];
+        ptx::tmem_ld32(t_o + c * 32, ov);
+        ptx::tc_wait_ld();
+        if (row < a.Sq) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            pk.x = pack_pair<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
+            pk.y = pack_pair<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
+            pk.z = pack_pair<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
+            pk.w = pack_pair<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pk;
+          }
+        }
+      }
+      if (a.lse && row < a.Sq)
+        a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m_used * kLn2 + logf(l) : -INFINITY;
+      // the next item's first P*V overwrites O: order this thread's TMEM reads before its later arrivals
+      ptx::tc_fence_before();
     }
   }
 
@@ -515,9 +526,17 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
   a.options = g_options;
+  a.n_qpairs = (p.Sq + 2 * kBM - 1) / (2 * kBM);
+  a.n_items = a.n_qpairs * p.Hq * p.B;
   auto kern = prefill_tcgen05_kernel<T, D>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-  dim3 grid((p.Sq + 2 * kBM - 1) / (2 * kBM), p.Hq, p.B);
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+  }
+  dim3 grid(a.n_items < n_sm ? a.n_items : n_sm);  // one persistent CTA per SM
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;
