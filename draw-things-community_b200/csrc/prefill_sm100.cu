@@ -44,11 +44,12 @@ template <int D>
 struct Cfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = kHalves * kHalfBytes;  // one Q tile / one K block / one V block
-  static constexpr int kSlots = D == 128 ? 5 : 8;
+  static constexpr int kSlots = D == 128 ? 4 : 8;
+  static constexpr int kStageBytes = 8 * 32 * 128;  // per softmax warp: 32 rows x 64 x 16-bit of O for the TMA store
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kSmemBytes = kQBytes + kRingBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + kBarBytes + 1024;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
 };
@@ -62,7 +63,7 @@ struct PrefillArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int is_causal;
-  int options;  // reserved for bring-up experiments
+  int options;  // bit 1: timeline probe of CTA 0 into dbg (bring-up only)
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
 };
 
@@ -117,10 +118,17 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint6
   }
 }
 
+// Timeline probe (options bit 1): globaltimer stamps of CTA 0 into the debug buffer (bring-up only).
+__device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
+  if ((a.options & 2) && a.dbg != nullptr && blockIdx.x == 0 && slot < 4096)
+    reinterpret_cast<unsigned long long*>(a.dbg)[slot] = ptx::globaltimer_ns();
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                       const PrefillArgs a) {
   using C = Cfg<D>;
   constexpr int kBf16 = std::is_same<T, __half>::value ? 0 : 1;
   extern __shared__ uint8_t smem_raw[];
@@ -129,7 +137,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t q_smem = base;
   const uint32_t ring_smem = base + C::kQBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes);
+  const uint32_t stage_smem = base + C::kQBytes + C::kRingBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int off = a.Sk - a.Sq;  // causal: key j visible to query i iff j <= i + off
@@ -197,6 +206,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ptx::prefetch_tensormap(&map_q);
         ptx::prefetch_tensormap(&map_k);
         ptx::prefetch_tensormap(&map_v);
+        ptx::prefetch_tensormap(&map_o);
         int ring_it = 0;  // K/V ring position, continues across items
         int n_item = 0;
         bool ok = true;
@@ -217,6 +227,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         };
         for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
+          // The Q tiles of the NEXT item are pulled into L2 now: their rows are 256-byte pieces a whole
+          // token stride apart (slow to gather from HBM), and the real load sits on the critical path
+          // between two items.
+          if (item + (int)gridDim.x < a.n_items) {
+            const Item nx = decode_item(item + gridDim.x);
+            for (int t = 0; t < (nx.two ? 2 : 1); ++t)
+#pragma unroll
+              for (int hf = 0; hf < C::kHalves; ++hf) ptx::tma_prefetch_l2_4d(&map_q, hf * 64, nx.h, nx.q0 + t * kBM, nx.b);
+          }
           // first K/V block of this item may be fetched while the previous item still owns the Q buffers
           ok = load_kv(w, 0, false) && load_kv(w, 0, true);
           if (!ok) break;
@@ -225,6 +244,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             *abort_flag = 1;
             break;
           }
+          stamp(a, 16 * n_item + 0);
           ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)((w.two ? 2 : 1) * C::kTileBytes));
           for (int t = 0; t < (w.two ? 2 : 1); ++t)
 #pragma unroll
@@ -267,6 +287,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             fail(1u);
             break;
           }
+          stamp(a, 16 * n_item + 1);
           ptx::tc_fence_after();
           {
             const uint64_t kd = ring_k + (uint64_t)(slot * (C::kTileBytes >> 4));
@@ -299,6 +320,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool last_qk = more && (j + 2 == w.nkv);  // the QK issued in this iteration is the item's last
             // ---- tile 0 ----  (P arrives in two halves of 64 keys so P*V starts while the softmax still runs)
             if (!ptx::mbar_wait(&bars->p_half[0][0], pph0, abort_flag)) { fail(4u); break; }
+            if (j == 0) stamp(a, 16 * n_item + 2);
             ptx::tc_fence_after();
             issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
             if (!ptx::mbar_wait(&bars->p_half[0][1], pph0, abort_flag)) { fail(4u); break; }
@@ -308,6 +330,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (ntile == 1) ptx::tc_commit(&bars->kv_empty[slot_v]);
             if (more) issue_qk<D>(s0, qd0, kd, idesc_qk);
             ptx::tc_commit(more ? &bars->s_full[0] : &bars->o_full[0]);  // next S ready, or (last block) O complete
+            if (!more) stamp(a, 16 * n_item + 3);
             if (more && ntile == 1) {
               ptx::tc_commit(&bars->kv_empty[slot_k]);
               if (last_qk) ptx::tc_commit(&bars->q_empty);
@@ -344,6 +367,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t sph = 0, oph = 0;  // phases of s_full[t] / o_full[t], continue across items
     bool ok = true;
     bool first_dump = true;
+    int n_item = 0;
+    const bool probe = (warp == 4 && lane == 0);
 
     for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
       const Item w = decode_item(item);
@@ -360,6 +385,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           break;
         }
         sph ^= 1;
+        if (probe && j == 0) stamp(a, 16 * n_item + 8);
         ptx::tc_fence_after();
         uint32_t s[4][32];
         ptx::tmem_ld32(t_s + 0, s[0]);
@@ -460,6 +486,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       if (!ok) break;
+      if (probe) stamp(a, 16 * n_item + 9);
 
       // ---- epilogue: O / l -> global (the MMA warp already works on the next item's first S meanwhile) ----
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->o_full[t], oph, abort_flag))) {
@@ -469,34 +496,56 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
       oph ^= 1;
+      if (probe) stamp(a, 16 * n_item + 10);
       ptx::tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(a.o) + w.b * a.o_sb + (int64_t)row * a.o_ss + (int64_t)w.h * a.o_sh;
+      // O goes out through shared memory and a TMA store per warp (32 rows x 64 columns): whole 128-byte
+      // row pieces reach L2, instead of 16-byte pieces scattered over 32 rows per instruction.
+      {
+        const uint32_t my_stage = stage_smem + (uint32_t)(warp - 4) * (32 * 128);
+        const int wrow0 = w.q0 + t * kBM + ((warp & 3) << 5);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t ov[32];
-        ptx::tmem_ld32(t_o + c * 32, ov);
-        ptx::tc_wait_ld();
-        if (row < a.Sq) {
+        for (int hf = 0; hf < D / 64; ++hf) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 pk;
-            pk.x = pack_pair<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
-            pk.y = pack_pair<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
-            pk.z = pack_pair<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
-            pk.w = pack_pair<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pk;
+          for (int c = 0; c < 2; ++c) {
+            uint32_t ov[32];
+            ptx::tmem_ld32(t_o + hf * 64 + c * 32, ov);
+            ptx::tc_wait_ld();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack_pair<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
+              pk.y = pack_pair<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
+              pk.z = pack_pair<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
+              pk.w = pack_pair<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
+              // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
+              const uint32_t q = (uint32_t)(c * 4 + v);
+              const uint32_t addr = my_stage + (uint32_t)lane * 128 + ((q ^ ((uint32_t)lane & 7u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                           : "memory");
+            }
           }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && wrow0 < a.Sq) {
+            ptx::tma_store_4d(&map_o, my_stage, hf * 64, w.h, wrow0, w.b);
+            ptx::bulk_commit_group();
+            ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
+          }
+          __syncwarp();
         }
       }
       if (a.lse && row < a.Sq)
         a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m_used * kLn2 + logf(l) : -INFINITY;
       // the next item's first P*V overwrites O: order this thread's TMEM reads before its later arrivals
       ptx::tc_fence_before();
+      if (probe) stamp(a, 16 * n_item + 11);
+      ++n_item;
     }
   }
 
   // =========================== teardown ===========================
+  if (warp >= 4 && lane == 0) ptx::bulk_wait_all();
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -511,10 +560,11 @@ float* g_dbg = nullptr;
 template <typename T, int D>
 int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
   using C = Cfg<D>;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, D, p.dtype, kBM)) return DT_UNSUPPORTED;
   if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
   if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mo, p.o, p.B, p.Sq, p.Hq, D, p.dtype, 32)) return DT_UNSUPPORTED;
   PrefillArgs a{};
   a.o = p.o.ptr;
   a.lse = p.lse;
@@ -537,7 +587,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
   }
   dim3 grid(a.n_items < n_sm ? a.n_items : n_sm);  // one persistent CTA per SM
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, a);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, mo, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;
 }
