@@ -46,7 +46,8 @@ struct Cfg {
   static constexpr int kTileBytes = kHalves * kHalfBytes;  // one Q tile / one K block / one V block
   static constexpr int kSlots = D == 128 ? 4 : 8;
   static constexpr int kStageBytes = 8 * 32 * 128;  // per softmax warp: 32 rows x 64 x 16-bit of O for the TMA store
-  static constexpr int kQBytes = 2 * kTileBytes;
+  static constexpr int kQBufs = D == 128 ? 1 : 2;       // Q buffers: with D = 64 there is room to load the next item's Q early
+  static constexpr int kQBytes = kQBufs * 2 * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarBytes = 512;
   static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + kBarBytes + 1024;
@@ -68,8 +69,8 @@ struct PrefillArgs {
 };
 
 struct Barriers {
-  uint64_t q_full;
-  uint64_t q_empty;
+  uint64_t q_full[2];
+  uint64_t q_empty[2];
   uint64_t s_full[2];
   uint64_t o_full[2];  // all P*V of an item done: O may be read (separate from s_full so no barrier runs two phases ahead)
   uint64_t p_half[2][2];  // [tile][first / second 64 keys of P written]
@@ -171,8 +172,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   };
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(&bars->q_full, 1);
-    ptx::mbar_init(&bars->q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&bars->q_full[i], 1);
+      ptx::mbar_init(&bars->q_empty[i], 1);
+    }
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(&bars->s_full[t], 1);
       ptx::mbar_init(&bars->o_full[t], 1);
@@ -239,18 +242,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // first K/V block of this item may be fetched while the previous item still owns the Q buffers
           ok = load_kv(w, 0, false) && load_kv(w, 0, true);
           if (!ok) break;
-          if (n_item > 0 && !ptx::mbar_wait(&bars->q_empty, (n_item - 1) & 1, abort_flag)) {
+          const int qb = n_item % C::kQBufs, quse = n_item / C::kQBufs;
+          if (quse > 0 && !ptx::mbar_wait(&bars->q_empty[qb], (quse - 1) & 1, abort_flag)) {
             atomicCAS(a.status, 0u, 2u);
             *abort_flag = 1;
             break;
           }
           stamp(a, 16 * n_item + 0);
-          ptx::mbar_arrive_expect_tx(&bars->q_full, (uint32_t)((w.two ? 2 : 1) * C::kTileBytes));
+          ptx::mbar_arrive_expect_tx(&bars->q_full[qb], (uint32_t)((w.two ? 2 : 1) * C::kTileBytes));
           for (int t = 0; t < (w.two ? 2 : 1); ++t)
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
-              ptx::tma_load_4d(base_ptr + t * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full, hf * 64, w.h,
-                               w.q0 + t * kBM, w.b);
+              ptx::tma_load_4d(base_ptr + (qb * 2 + t) * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full[qb], hf * 64,
+                               w.h, w.q0 + t * kBM, w.b);
           for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
         }
       }
@@ -262,8 +266,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // Descriptors differ only in the 14-bit start-address field, so stepping through a tile is one add.
         const uint64_t desc_k_major = ptx::make_smem_desc_sw128(0, 16, 1024);            // Q, K
         const uint64_t desc_mn_major = ptx::make_smem_desc_sw128(0, kHalfBytes, 1024);   // V
-        const uint64_t qd0 = desc_k_major | (uint64_t)((q_smem & 0x3FFFFu) >> 4);
-        const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
+        const uint64_t qd_base = desc_k_major | (uint64_t)((q_smem & 0x3FFFFu) >> 4);
         const uint64_t ring_k = desc_k_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
         const uint64_t ring_v = desc_mn_major | (uint64_t)((ring_smem & 0x3FFFFu) >> 4);
         const uint32_t s0 = tmem + C::kColS0, s1 = tmem + C::kColS1, o0 = tmem + C::kColO0, o1 = tmem + C::kColO1;
@@ -282,8 +285,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
           const int ntile = w.two ? 2 : 1;
+          const int qb = n_item % C::kQBufs;
+          const uint64_t qd0 = qd_base + (uint64_t)(qb * 2 * (C::kTileBytes >> 4));
+          const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
           // ---- S_t(0) = Q_t K(0)^T ----
-          if (!ptx::mbar_wait(&bars->q_full, n_item & 1, abort_flag) || !ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
+          if (!ptx::mbar_wait(&bars->q_full[qb], (n_item / C::kQBufs) & 1, abort_flag) || !ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
             fail(1u);
             break;
           }
@@ -298,7 +304,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               ptx::tc_commit(&bars->s_full[1]);
             }
             ptx::tc_commit(&bars->kv_empty[slot]);
-            if (w.nkv == 1) ptx::tc_commit(&bars->q_empty);  // Q is no longer needed: the next item may load its own
+            if (w.nkv == 1) ptx::tc_commit(&bars->q_empty[qb]);  // Q is no longer needed: the next item may load its own
             advance();
           }
           for (int j = 0; j < w.nkv && ok; ++j) {
@@ -333,7 +339,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!more) stamp(a, 16 * n_item + 3);
             if (more && ntile == 1) {
               ptx::tc_commit(&bars->kv_empty[slot_k]);
-              if (last_qk) ptx::tc_commit(&bars->q_empty);
+              if (last_qk) ptx::tc_commit(&bars->q_empty[qb]);
             }
             // ---- tile 1 ----
             if (ntile == 2) {
@@ -349,7 +355,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               ptx::tc_commit(more ? &bars->s_full[1] : &bars->o_full[1]);
               if (more) {
                 ptx::tc_commit(&bars->kv_empty[slot_k]);
-                if (last_qk) ptx::tc_commit(&bars->q_empty);
+                if (last_qk) ptx::tc_commit(&bars->q_empty[qb]);
               }
             }
           }
@@ -413,10 +419,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < 32; ++i)
               if ((long long)(key0 + c * 32 + i) > lim) s[c][i] = 0xff800000u;  // -inf
         }
+        // chunks of 32 keys that lie entirely beyond Sk are skipped (short K/V such as 77 text tokens)
+        const int nch = (min(kBN, a.Sk - key0) + 31) >> 5;
         // row max: four independent chains of 3-input max (one per 32-column chunk)
         float mxc[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
+          if (c >= nch) {
+            mxc[c] = -INFINITY;
+            continue;
+          }
           mxc[c] = ptx::max3(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]), __uint_as_float(s[c][2]));
 #pragma unroll
           for (int i = 3; i < 31; i += 2) mxc[c] = ptx::max3(mxc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
@@ -454,6 +466,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
           lsum[c] = 0ull;
+          if (c < nch) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
@@ -471,6 +484,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             pk[i] = kBf16 ? ptx::cvt_pack_bf16(p0, p1) : ptx::cvt_pack_f16(p0, p1);
           }
           ptx::tmem_st16(t_s + c * 16, pk);
+          }
           if (c == 1 || c == 3) {  // 64 keys of P are in TMEM: let the MMA warp start on them
             ptx::tc_wait_st();
             ptx::tc_fence_before();
