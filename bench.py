@@ -27,6 +27,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "draw-things-community_b200"))
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+# (profiles/prefill_tcgen05_flux_joint.md, profiles/decode_splitkv_gqa_8192.md); None = not captured
+NCU_TRAFFIC_BYTES = {"flux_joint": 93.3e6, "decode_b16": 541.3e6, "decode_b1": 33.6e6, "wan_self": None, "sdxl_cross": None}
+
 METRIC = "sdpa_fwd_tflops"
 UNIT = "TFLOP/s"
 L2_BYTES = 126 * 1024 * 1024
@@ -309,13 +313,15 @@ def run_single(args, dtattn, device, peaks):
     is_tensor = name in ("flux_joint", "wan_self")
     if is_tensor:
         roof = {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
-                "frac": round(tflops / peak, 4), "traffic": None, "peak_source": peaks["source"] + " (burst bf16 GEMM)",
+                "frac": round(tflops / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(name), "traffic_unit": "bytes/launch",
+                "algorithmic_bytes": nbytes, "peak_source": peaks["source"] + " (burst bf16 GEMM)",
                 "frac_of_sustained_peak": round(tflops / peaks["bf16_tflops_sustained"], 4) if peaks["bf16_tflops_sustained"] else None,
                 "kernel": "prefill_tcgen05_kernel", "launches_timed": args.steps}
     else:
         gbs = nbytes / (ms_step * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peaks["source"],
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES.get(name), "traffic_unit": "bytes/launch",
+                "algorithmic_bytes": nbytes, "peak_source": peaks["source"],
                 "launches_timed": args.steps}
     line = {"metric": METRIC, "value": round(tflops, 3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
