@@ -356,6 +356,10 @@ def run_sharded(args, dtattn, device, peaks):
     sets = make_sets(w, n_sets, device, heads=hl, seed=rank)
     o_full = [torch.empty((w["B"], w["Sq"], w["Hq"], w["D"]), dtype=TDT[w["dtype"]], device=device) for _ in range(2)]
     chunks = args.chunks
+    fused = not args.no_fused
+    if fused:  # collective: every rank maps every rank's output buffers (CUDA IPC over NVLink)
+        for o in o_full:
+            comm.register_output(o)
 
     def step(i):
         s = sets[i % n_sets]
@@ -407,7 +411,8 @@ def run_sharded(args, dtattn, device, peaks):
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te.item())
     n_chunks_run = chunks
-    launches = args.steps * 2 * n_chunks_run  # attention + permute kernel per chunk (NCCL's own kernels not counted)
+    # fused: one attention kernel per step; else attention + permute kernel per chunk (NCCL's own kernels not counted)
+    launches = args.steps if fused else args.steps * 2 * n_chunks_run
 
     # same workload on ONE GPU in the same run (rank 0 only), so the strong-scaling ratio has its own T1
     t1 = None
@@ -423,7 +428,9 @@ def run_sharded(args, dtattn, device, peaks):
                 "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
                 "config": {"workload": name, **{k2: w[k2] for k2 in ("B", "Sq", "Sk", "Hq", "Hkv", "D")},
-                           "parallelism": f"heads sharded {hl} per GPU + all-gather of O in {chunks} row chunks",
+                           "parallelism": (f"heads sharded {hl} per GPU; O tiles stored into every GPU's buffer from the attention "
+                                           f"epilogue (peer stores over NVLink) + one rendezvous" if fused else
+                                           f"heads sharded {hl} per GPU + NCCL all-gather of O in {chunks} row chunks + permute"),
                            "l2": f"rotating {n_sets} input sets per rank; each set larger than L2" if nbytes_local > L2_BYTES
                                  else f"rotating {n_sets} input sets per rank"},
                 "clocks": clk.summary(),
@@ -452,6 +459,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=4)
     ap.add_argument("--no-side", action="store_true", help="skip the decode / SDXL side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-fused", action="store_true", help="head-sharded mode through NCCL all-gather + permute instead of peer stores")
     ap.add_argument("--no-t1", action="store_true", help="skip the single-GPU run of the sharded workload")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")

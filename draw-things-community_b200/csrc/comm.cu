@@ -6,6 +6,7 @@
 //
 // The reference has no counterpart: it is single-GPU per process (ccv is built with have_nccl = False,
 // WORKSPACE.linux:127).  Every TMA load on this path is a plain per-CTA load from this GPU's own memory.
+#include <cuda.h>
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -27,6 +28,7 @@ struct NcclApi {
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   bool ok = false;
 };
 
@@ -48,9 +50,10 @@ NcclApi& nccl() {
   LOAD(CommAbort, "ncclCommAbort");
   LOAD(CommDestroy, "ncclCommDestroy");
   LOAD(AllGather, "ncclAllGather");
+  LOAD(AllReduce, "ncclAllReduce");
 #undef LOAD
   api.ok = api.GetUniqueId && api.CommInitRankConfig && api.CommGetAsyncError && api.CommAbort && api.CommDestroy &&
-           api.AllGather;
+           api.AllGather && api.AllReduce;
   return api;
 }
 
@@ -63,6 +66,23 @@ struct Comm {
   cudaStream_t side = nullptr;
   cudaEvent_t chunk_done[kMaxChunks];
   cudaEvent_t all_done = nullptr;
+  // output buffers registered for the fused mode: every rank's buffer mapped into this process
+  static constexpr int kMaxRegs = 4;
+  struct Reg {
+    void* local = nullptr;
+    size_t bytes = 0;
+    void* peer[8] = {nullptr};       // peer[r] = rank r's buffer as seen from here (own rank: the local pointer)
+    void* opened[8] = {nullptr};     // bases returned by cudaIpcOpenMemHandle, to close later
+  } regs[kMaxRegs];
+  int n_regs = 0;
+  int* flag = nullptr;               // 4 bytes for the in-stream rendezvous after a fused step
+  void* xchg = nullptr;              // small device buffer for exchanging handles
+};
+
+struct IpcInfo {
+  cudaIpcMemHandle_t handle;
+  unsigned long long offset;
+  unsigned long long bytes;
 };
 
 // Poll the communicator until the pending operation left the in-progress state or the limit ran out.
@@ -171,11 +191,79 @@ int dt_comm_destroy(void* comm) {
   Comm* c = reinterpret_cast<Comm*>(comm);
   NcclApi& api = nccl();
   if (c->side) cudaStreamSynchronize(c->side);
+  for (int i = 0; i < c->n_regs; ++i)
+    for (int r = 0; r < 8; ++r)
+      if (c->regs[i].opened[r]) cudaIpcCloseMemHandle(c->regs[i].opened[r]);
+  if (c->flag) cudaFree(c->flag);
+  if (c->xchg) cudaFree(c->xchg);
   if (c->comm && api.ok) api.CommDestroy(c->comm);
   for (int i = 0; i < kMaxChunks; ++i) cudaEventDestroy(c->chunk_done[i]);
   if (c->all_done) cudaEventDestroy(c->all_done);
   if (c->side) cudaStreamDestroy(c->side);
   delete c;
+  return DT_OK;
+}
+
+// Fused mode set-up: every rank hands the others an IPC handle of its output buffer, so that the attention
+// epilogue can store O tiles straight into all ranks' [B,Sq,H,D] buffers over NVLink (ordinary peer stores).
+int dt_comm_register_output(void* comm, void* o_full, size_t bytes) {
+  if (!comm || !o_full || bytes == 0) return DT_BAD_ARG;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  NcclApi& api = nccl();
+  if (!api.ok) return DT_NCCL;
+  if (c->world > 8) return DT_UNSUPPORTED;
+  if (c->n_regs >= Comm::kMaxRegs) return DT_UNSUPPORTED;
+  if (c->world == 1) {
+    Comm::Reg& r = c->regs[c->n_regs++];
+    r.local = o_full; r.bytes = bytes; r.peer[0] = o_full;
+    return DT_OK;
+  }
+  // allocation base of the buffer (a framework may hand out pieces of a larger allocation)
+  typedef CUresult (*GetRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static GetRangeFn get_range = nullptr;
+  if (!get_range) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) != cudaSuccess || !sym) return DT_CUDA;
+    get_range = reinterpret_cast<GetRangeFn>(sym);
+  }
+  CUdeviceptr base = 0;
+  size_t range = 0;
+  if (get_range(&base, &range, (CUdeviceptr)o_full) != CUDA_SUCCESS) return DT_CUDA;
+  IpcInfo mine;
+  memset(&mine, 0, sizeof(mine));
+  DT_CUDA_TRY(cudaIpcGetMemHandle(&mine.handle, reinterpret_cast<void*>(base)));
+  mine.offset = (unsigned long long)((CUdeviceptr)o_full - base);
+  mine.bytes = bytes;
+  if (!c->xchg) DT_CUDA_TRY(cudaMalloc(&c->xchg, sizeof(IpcInfo) * 9));
+  if (!c->flag) {
+    DT_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->flag), 256));
+    DT_CUDA_TRY(cudaMemset(c->flag, 0, 256));
+  }
+  IpcInfo* dev = reinterpret_cast<IpcInfo*>(c->xchg);
+  DT_CUDA_TRY(cudaMemcpyAsync(dev + 8, &mine, sizeof(mine), cudaMemcpyHostToDevice, c->side));
+  ncclResult_t r = api.AllGather(dev + 8, dev, sizeof(IpcInfo), ncclChar, c->comm, c->side);
+  int st = wait_nccl(c, r, c->timeout_ms);
+  if (st != DT_OK) return st;
+  IpcInfo all[8];
+  DT_CUDA_TRY(cudaMemcpyAsync(all, dev, sizeof(IpcInfo) * c->world, cudaMemcpyDeviceToHost, c->side));
+  DT_CUDA_TRY(cudaStreamSynchronize(c->side));
+  Comm::Reg& reg = c->regs[c->n_regs];
+  reg = Comm::Reg();
+  reg.local = o_full;
+  reg.bytes = bytes;
+  for (int q = 0; q < c->world; ++q) {
+    if (all[q].bytes != bytes) return DT_BAD_ARG;  // every rank must register the same size
+    if (q == c->rank) {
+      reg.peer[q] = o_full;
+      continue;
+    }
+    void* pb = nullptr;
+    DT_CUDA_TRY(cudaIpcOpenMemHandle(&pb, all[q].handle, cudaIpcMemLazyEnablePeerAccess));
+    reg.opened[q] = pb;
+    reg.peer[q] = static_cast<char*>(pb) + all[q].offset;
+  }
+  ++c->n_regs;
   return DT_OK;
 }
 
@@ -201,6 +289,32 @@ int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tens
   if (chunks <= 0 || chunks > kMaxChunks) return DT_BAD_ARG;
   if (local->is_causal && chunks != 1) return DT_UNSUPPORTED;  // a row chunk would shift the causal diagonal
   if (local->mask || local->lse) return DT_UNSUPPORTED;
+  // ---- fused mode: o_full was registered on every rank -> the epilogue stores each O tile into all ranks'
+  // buffers while the tensor cores work on the next tile; one small in-stream rendezvous ends the step ----
+  for (int i = 0; i < c->n_regs; ++i) {
+    const Comm::Reg& reg = c->regs[i];
+    if (reg.local != o_full.ptr) continue;
+    const size_t es = dtype_size(local->dtype);
+    dt_sdpa_params p = *local;
+    const size_t head_off = (size_t)c->rank * local->Hq * o_full.stride_h * es;
+    p.o = o_full;
+    p.o.ptr = static_cast<char*>(o_full.ptr) + head_off;
+    if (!prefill_supported(p) || (p.flags & DT_FLAG_FORCE_GENERIC)) break;  // only the tensor-core kernel has the extra stores
+    void* extra[8];
+    int n_extra = 0;
+    for (int q = 0; q < c->world; ++q)
+      if (q != c->rank) extra[n_extra++] = static_cast<char*>(reg.peer[q]) + head_off;
+    cudaStream_t fs = (cudaStream_t)cuda_stream;
+    int st2 = launch_prefill(p, fs, extra, n_extra);
+    if (st2 != DT_OK) return st2;
+    if (c->world > 1) {
+      // kernel completion makes this rank's peer stores visible; after the rendezvous every rank's have landed
+      ncclResult_t r = api.AllReduce(c->flag, c->flag, 1, ncclInt, ncclSum, c->comm, fs);
+      st2 = wait_nccl(c, r, c->timeout_ms);
+      if (st2 != DT_OK) return st2;
+    }
+    return DT_OK;
+  }
   if (chunks > local->Sq) chunks = local->Sq;
   size_t need = 0, inner = 0;
   int st = dt_sdpa_headsharded_workspace_size(local, c->world, chunks, &need);
@@ -216,9 +330,20 @@ int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tens
   const size_t slice = (size_t)B * local->Sq * Hl * D * es;
   uint8_t* gath = stage + al256(slice);
 
-  // rows per chunk, rounded to the 256-row pair of query tiles the tensor-core kernel works in
+  // Rows per chunk.  The attention kernel is persistent (one CTA per SM, work items of 256 query rows x one
+  // head), so a chunk should hold a whole number of rounds over the SMs: round the rows up to a multiple of
+  // 256 * sms / gcd(sms, B * heads), which may leave fewer chunks than asked for.
   int rows_per = (local->Sq + chunks - 1) / chunks;
-  if (chunks > 1) rows_per = (rows_per + 255) / 256 * 256;
+  if (chunks > 1) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    long long x = sms, y = (long long)B * Hl;
+    while (y) { long long r = x % y; x = y; y = r; }
+    const long long unit = 256LL * (sms / x);
+    long long rp = ((long long)rows_per + unit - 1) / unit * unit;
+    rows_per = rp > local->Sq ? local->Sq : (int)rp;
+  }
   size_t stage_off = 0, gath_off = 0;
   int ci = 0;
   for (int r0 = 0; r0 < local->Sq; r0 += rows_per, ++ci) {

@@ -38,7 +38,9 @@ int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaSt
 
 // TMA + tcgen05 flash attention: fp16/bf16, D in {64,128}, no mask.
 bool prefill_supported(const dt_sdpa_params& p);
-int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream);
+// extra_outputs: up to 7 more [B,Sq,Hq,D] views with the same strides as p.o (other GPUs' buffers in the
+// head-sharded mode) that receive a copy of every O tile.
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs = nullptr, int n_extra = 0);
 
 // [world][rows][Hl][D] -> [B,Sq,world*Hl,D]
 int launch_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D,

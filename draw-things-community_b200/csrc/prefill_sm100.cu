@@ -32,6 +32,7 @@ constexpr int kBN = 128;       // keys per block
 constexpr int kThreads = 384;
 constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 x 16-bit] = 16 KB, one TMA box
 constexpr float kRescaleThreshold = 8.f;
+constexpr int kMaxExtraOutputs = 7;
 // every kPolyPeriod-th pair of exponentials is evaluated with the polynomial instead of MUFU.EX2
 #ifndef DT_POLY_PERIOD
 #define DT_POLY_PERIOD 4
@@ -66,6 +67,10 @@ struct PrefillArgs {
   int is_causal;
   int options;  // bit 1: timeline probe of CTA 0 into dbg (bring-up only)
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
+  // head-sharded mode: the same O tile is also stored into these views (other GPUs' output buffers, same
+  // strides as o) with ordinary 16-byte stores
+  void* extra_o[kMaxExtraOutputs];
+  int n_extra;
 };
 
 struct Barriers {
@@ -544,8 +549,24 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (lane == 0 && wrow0 < a.Sq) {
             ptx::tma_store_4d(&map_o, my_stage, hf * 64, w.h, wrow0, w.b);
             ptx::bulk_commit_group();
-            ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
           }
+          if (a.n_extra > 0) {
+            // copies of the tile for the other GPUs: 8 lanes write one row's 128 bytes, 4 rows per instruction
+            const int64_t row_off = (int64_t)w.b * a.o_sb + (int64_t)w.h * a.o_sh + hf * 64;
+#pragma unroll 1
+            for (int e = 0; e < a.n_extra; ++e) {
+              T* dst = reinterpret_cast<T*>(a.extra_o[e]) + row_off;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = i * 4 + (lane >> 3), ch = lane & 7;
+                uint4 val;
+                const uint32_t addr = my_stage + (uint32_t)r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+                if (wrow0 + r < a.Sq) *reinterpret_cast<uint4*>(dst + (int64_t)(wrow0 + r) * a.o_ss + ch * 8) = val;
+              }
+            }
+          }
+          if (lane == 0 && wrow0 < a.Sq) ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
           __syncwarp();
         }
       }
@@ -572,7 +593,7 @@ int g_options = 0;
 float* g_dbg = nullptr;
 
 template <typename T, int D>
-int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
+int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, int n_extra) {
   using C = Cfg<D>;
   CUtensorMap mq, mk, mv, mo;
   if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, D, p.dtype, kBM)) return DT_UNSUPPORTED;
@@ -590,6 +611,9 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream) {
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
   a.options = g_options;
+  if (n_extra < 0 || n_extra > kMaxExtraOutputs) return DT_BAD_ARG;
+  a.n_extra = n_extra;
+  for (int i = 0; i < n_extra; ++i) a.extra_o[i] = extra[i];
   a.n_qpairs = (p.Sq + 2 * kBM - 1) / (2 * kBM);
   a.n_items = a.n_qpairs * p.Hq * p.B;
   auto kern = prefill_tcgen05_kernel<T, D>;
@@ -623,10 +647,11 @@ bool prefill_supported(const dt_sdpa_params& p) {
   return ok(p.q) && ok(p.k) && ok(p.v) && ok(p.o);
 }
 
-int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream) {
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra) {
   if (p.dtype == DT_F16)
-    return p.D == 128 ? launch_t<__half, 128>(p, stream) : launch_t<__half, 64>(p, stream);
-  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, stream) : launch_t<__nv_bfloat16, 64>(p, stream);
+    return p.D == 128 ? launch_t<__half, 128>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64>(p, stream, extra_outputs, n_extra);
+  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, stream, extra_outputs, n_extra)
+                    : launch_t<__nv_bfloat16, 64>(p, stream, extra_outputs, n_extra);
 }
 
 }  // namespace dt

@@ -70,6 +70,7 @@ SYMBOLS = [
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
     ("dt_comm_destroy", ctypes.c_int, [ctypes.c_void_p]),
+    ("dt_comm_register_output", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]),
     ("dt_sdpa_headsharded_workspace_size", ctypes.c_int, [_P(SdpaParams), ctypes.c_int, ctypes.c_int, _P(ctypes.c_size_t)]),
     ("dt_sdpa_forward_headsharded", ctypes.c_int,
      [ctypes.c_void_p, _P(SdpaParams), Tensor4, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
@@ -268,6 +269,13 @@ class HeadShardedComm:
         self.handle = ctypes.c_void_p()
         _check(lib().dt_comm_init(ctypes.byref(self.handle), rank, world, ident, timeout_ms), "dt_comm_init")
         self.ws = None
+
+    def register_output(self, o_full):
+        """Collective.  After this, forward(..., o_full) stores output tiles straight into every rank's o_full
+        from the attention epilogue (fused mode) instead of all-gather + permute."""
+        assert o_full.is_contiguous()
+        _check(lib().dt_comm_register_output(self.handle, ctypes.c_void_p(o_full.data_ptr()),
+                                             o_full.numel() * o_full.element_size()), "dt_comm_register_output")
 
     def forward(self, q_local, k_local, v_local, scale, o_full, chunks=1, is_causal=False, stream=None):
         """q_local [B,Sq,H/world,D] etc. -> o_full [B,Sq,H,D] on every rank."""

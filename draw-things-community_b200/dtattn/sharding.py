@@ -30,10 +30,15 @@ def gathered_to_bshd(gathered, world: int):
     return gathered.permute(1, 2, 0, 3, 4).reshape(B, S, world * Hl, D)
 
 
-def chunk_rows(Sq: int, chunks: int, tile: int = 256):
-    """Row ranges dt_sdpa_forward_headsharded cuts the queries into (multiples of the 256-row CTA tile)."""
+def chunk_rows(Sq: int, chunks: int, items_per_row_block: int = 1, sms: int = 148, tile: int = 256):
+    """Row ranges dt_sdpa_forward_headsharded cuts the queries into.  The attention kernel is persistent (one
+    CTA per SM; a work item is 256 query rows of one head), so a chunk holds a whole number of rounds over the
+    SMs: rows per chunk are a multiple of tile * sms / gcd(sms, items_per_row_block), where items_per_row_block
+    = batch * local heads."""
     if chunks <= 1:
         return [(0, Sq)]
+    import math
+    unit = tile * (sms // math.gcd(sms, items_per_row_block))
     per = -(-Sq // chunks)
-    per = -(-per // tile) * tile
+    per = min(Sq, -(-per // unit) * unit)
     return [(r0, min(Sq, r0 + per)) for r0 in range(0, Sq, per)]

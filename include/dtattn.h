@@ -148,6 +148,13 @@ int dt_comm_unique_id(void* id_out_128);
    within timeout_ms. */
 int dt_comm_init(void** comm, int rank, int world, const void* unique_id_128, int timeout_ms);
 int dt_comm_destroy(void* comm);
+/* Fused mode (optional): register this rank's full output buffer.  Collective: every rank calls it with a
+ * buffer of the same size; the buffers are exchanged as CUDA IPC handles and mapped into every process.  A later
+ * dt_sdpa_forward_headsharded whose o_full.ptr is a registered buffer stores each output tile straight into
+ * all ranks' buffers from the attention kernel's epilogue (ordinary peer stores over NVLink, overlapped with
+ * the tensor-core work) and ends with one small in-stream rendezvous, instead of all-gather + permute.
+ * Up to 4 buffers per communicator, up to 8 ranks. */
+int dt_comm_register_output(void* comm, void* o_full, size_t bytes);
 /* Run the local head slice (`local`: Hq and Hkv are the per-rank counts, o is ignored) and gather the
  * full output into o_full ([B, Sq, Hq*world, D], contiguous rows) on every rank.  `chunks` >= 1 splits
  * the query rows into that many pieces so the gather of one piece overlaps the attention of the next.

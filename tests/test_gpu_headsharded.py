@@ -36,6 +36,7 @@ def _worker(rank, world, port, q):
             return obj[0]
         comm = dtattn.HeadShardedComm(rank, world, bcast, timeout_ms=60000)
         errs = []
+        keep = []
         for (B, S, H, D, chunks) in [(1, 1000, 8, 128, 3), (2, 300, 4, 64, 1)]:
             cfg = so.AttnConfig("t", B, S, S, H, H, D, "bf16", 7)
             q0, q1, kv0, kv1 = sharding.head_range(rank, world, H, H)
@@ -46,6 +47,16 @@ def _worker(rank, world, port, q):
             qf, kf, vf = so.make_inputs(cfg, heads=(0, H))
             ref = so.sdpa_explicit(qf, kf, vf, cfg.scale)
             errs.append(so.error_stats(o_full.float().cpu(), ref))
+            # fused mode: the same call on a registered buffer stores tiles straight into both ranks' buffers
+            o_fused = torch.zeros((B, S, H, D), dtype=torch.bfloat16, device=dev)
+            comm.register_output(o_fused)
+            for _ in range(2):
+                comm.forward(ql.to(dev), kl.to(dev), vl.to(dev), cfg.scale, o_fused, chunks=chunks)
+            torch.cuda.synchronize()
+            dist.barrier()
+            errs.append(so.error_stats(o_fused.float().cpu(), ref))
+            assert torch.equal(o_fused, o_full), "fused and gathered results must be bitwise equal"
+            keep.append(o_fused)
         comm.close()
         q.put((rank, errs, dtattn.device_status()))
     finally:

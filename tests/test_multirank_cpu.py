@@ -35,7 +35,7 @@ def _worker(rank, world, port, q):
         ql, kl, vl = so.make_inputs(cfg, heads=(q0, q1))
         assert ql.shape[2] == q1 - q0 and kl.shape[2] == kv1 - kv0
         out_chunks = []
-        for r0, r1 in sharding.chunk_rows(cfg.Sq, 2, tile=32):
+        for r0, r1 in sharding.chunk_rows(cfg.Sq, 2, sms=1, tile=32):
             out_chunks.append(so.sdpa_explicit(ql[:, r0:r1], kl, vl, cfg.scale))
         ol = torch.cat(out_chunks, 1).contiguous()
         bufs = [torch.empty_like(ol) for _ in range(world)]
@@ -93,5 +93,6 @@ def test_head_range_rules():
     assert sharding.head_range(3, 8, 32, 4) == (12, 16, 1, 2)            # two ranks share one KV head
     with pytest.raises(ValueError):
         sharding.head_range(0, 7, 24, 24)
-    assert sharding.chunk_rows(75600, 4) == [(0, 18944), (18944, 37888), (37888, 56832), (56832, 75600)]
+    assert sharding.chunk_rows(75600, 4, items_per_row_block=10) == [(0, 18944), (18944, 37888), (37888, 56832), (56832, 75600)]
+    assert sharding.chunk_rows(75600, 4, items_per_row_block=5) == [(0, 37888), (37888, 75600)]   # Wan on 8 GPUs
     assert sharding.chunk_rows(100, 1) == [(0, 100)]
