@@ -379,7 +379,12 @@ def run_sharded(args, dtattn, device, peaks):
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+        timed_ms = e0.elapsed_time(e1)
+        if timed_ms < 1200 and not args.profile:  # keep the load on while the 200 ms clock sampler collects a few samples
+            for i in range(int(min(400, 1200 / max(timed_ms / args.steps, 1e-3)))):
+                step(i)
+            torch.cuda.synchronize()
+    t = torch.tensor([timed_ms], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / args.steps
     status = dtattn.device_status()
