@@ -71,6 +71,7 @@ struct PrefillArgs {
   // strides as o) with ordinary 16-byte stores
   void* extra_o[kMaxExtraOutputs];
   int n_extra;
+  int d_real;  // the tensors' head dim (<= the kernel's D): TMA zero-fills the columns beyond it on load and clips them on store
 };
 
 struct Barriers {
@@ -562,7 +563,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 uint4 val;
                 const uint32_t addr = my_stage + (uint32_t)r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
-                if (wrow0 + r < a.Sq) *reinterpret_cast<uint4*>(dst + (int64_t)(wrow0 + r) * a.o_ss + ch * 8) = val;
+                if (wrow0 + r < a.Sq && hf * 64 + ch * 8 < a.d_real) *reinterpret_cast<uint4*>(dst + (int64_t)(wrow0 + r) * a.o_ss + ch * 8) = val;
               }
             }
           }
@@ -596,10 +597,10 @@ template <typename T, int D>
 int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, int n_extra) {
   using C = Cfg<D>;
   CUtensorMap mq, mk, mv, mo;
-  if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, D, p.dtype, kBM)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kBN)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mo, p.o, p.B, p.Sq, p.Hq, D, p.dtype, 32)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, p.D, p.dtype, kBM)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, p.D, p.dtype, kBN)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, p.D, p.dtype, kBN)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mo, p.o, p.B, p.Sq, p.Hq, p.D, p.dtype, 32)) return DT_UNSUPPORTED;
   PrefillArgs a{};
   a.o = p.o.ptr;
   a.lse = p.lse;
@@ -613,6 +614,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   a.options = g_options;
   if (n_extra < 0 || n_extra > kMaxExtraOutputs) return DT_BAD_ARG;
   a.n_extra = n_extra;
+  a.d_real = p.D;
   for (int i = 0; i < n_extra; ++i) a.extra_o[i] = extra[i];
   a.n_qpairs = (p.Sq + 2 * kBM - 1) / (2 * kBM);
   a.n_items = a.n_qpairs * p.Hq * p.B;
@@ -634,7 +636,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
 
 bool prefill_supported(const dt_sdpa_params& p) {
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
-  if (p.D != 64 && p.D != 128) return false;
+  if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)
   if (p.mask) return false;
   if (!(p.scale > 0.f)) return false;
   if (p.Hq % p.Hkv) return false;
@@ -649,8 +651,8 @@ bool prefill_supported(const dt_sdpa_params& p) {
 
 int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra) {
   if (p.dtype == DT_F16)
-    return p.D == 128 ? launch_t<__half, 128>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64>(p, stream, extra_outputs, n_extra);
-  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, stream, extra_outputs, n_extra)
+    return p.D > 64 ? launch_t<__half, 128>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64>(p, stream, extra_outputs, n_extra);
+  return p.D > 64 ? launch_t<__nv_bfloat16, 128>(p, stream, extra_outputs, n_extra)
                     : launch_t<__nv_bfloat16, 64>(p, stream, extra_outputs, n_extra);
 }
 

@@ -84,7 +84,8 @@ def test_kernel_selection(dtattn):
             setattr(p, name, dtattn.Tensor4(0x10000, t.stride(0), t.stride(1), t.stride(2)))
         return dtattn.kernel_name(p)
 
-    assert pick(2, 4096, 4096, 8, 8, 40, torch.float32) == "generic"              # SD1.5 self-attention
+    assert pick(2, 4096, 4096, 8, 8, 40, torch.float32) == "generic"              # SD1.5 self-attention, fp32 (upcast)
+    assert pick(2, 4096, 4096, 8, 8, 40, torch.float16) == "prefill_tcgen05"       # SD1.5 in half precision: D padded to 64
     assert pick(2, 4096, 77, 20, 20, 64, torch.float16) == "prefill_tcgen05"       # SDXL cross-attention
     assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16) == "prefill_tcgen05"   # Flux joint attention
     assert pick(1, 75600, 75600, 5, 5, 128, torch.bfloat16) == "prefill_tcgen05"   # Wan, one rank's heads

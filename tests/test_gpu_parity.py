@@ -209,6 +209,10 @@ PREFILL = [
     (1, 384, 384, 2, 2, 128, torch.bfloat16, True),    # causal
     (1, 200, 456, 2, 1, 128, torch.float16, True),     # causal, bottom-right aligned, ragged
     (1, 100, 100, 1, 1, 64, torch.bfloat16, True),
+    (2, 320, 320, 8, 8, 40, torch.float16, False),     # SD1.5 head dims in half precision: zero-padded to 64 / 128 by TMA
+    (1, 200, 300, 4, 4, 80, torch.float16, False),
+    (1, 130, 77, 2, 2, 96, torch.bfloat16, False),
+    (1, 256, 256, 2, 1, 8, torch.float16, True),
 ]
 
 
