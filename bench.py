@@ -53,6 +53,9 @@ WORKLOADS = {
     "sdxl_cross": dict(B=2, Sq=4096, Sk=77, Hq=20, Hkv=20, D=64, dtype="f16", causal=False),
     "decode_b1": dict(B=1, Sq=1, Sk=8192, Hq=32, Hkv=8, D=128, dtype="f16", causal=True),
     "decode_b16": dict(B=16, Sq=1, Sk=8192, Hq=32, Hkv=8, D=128, dtype="f16", causal=True),
+    # side measurements only
+    "sd15_self_f16": dict(B=2, Sq=4096, Sk=4096, Hq=8, Hkv=8, D=40, dtype="f16", causal=False),
+    "wan_self_5heads": dict(B=1, Sq=75600, Sk=75600, Hq=5, Hkv=5, D=128, dtype="bf16", causal=False),
 }
 TDT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
@@ -178,17 +181,18 @@ def time_graph(fns, reps, warmup_reps=3):
 def side_measurements(dtattn, device, peaks):
     """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention."""
     out = {}
-    for name in ("decode_b16", "decode_b1", "sdxl_cross"):
+    for name in ("decode_b16", "decode_b1", "sdxl_cross", "sd15_self_f16", "wan_self_5heads"):
         w = WORKLOADS[name]
         nbytes = bytes_of(w)
         n_sets = max(2, -(-3 * L2_BYTES // nbytes))  # rotate through > 3x L2 worth of distinct inputs
         n_sets = min(n_sets, 16)
+        reps = 20 if flops_of(w) < 1e12 else 2
         sets = make_sets(w, n_sets, device, seed=7)
         scale = w["D"] ** -0.5
         fns = [(lambda s=s: dtattn.sdpa_forward(s[0], s[1], s[2], scale, w["causal"], out=s[3])) for s in sets]
-        ms_stream = time_device(lambda i: fns[i % n_sets](), 20 * n_sets, 2 * n_sets) / (20 * n_sets)
+        ms_stream = time_device(lambda i: fns[i % n_sets](), reps * n_sets, 2 * n_sets) / (reps * n_sets)
         try:
-            ms_graph = time_graph(fns, reps=20)
+            ms_graph = time_graph(fns, reps=reps)
         except Exception as e:  # graph capture is a convenience for the tiny shapes, not a requirement
             ms_graph = None
             out[name + "_graph_error"] = str(e)[:120]
@@ -460,7 +464,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="dtattn", choices=["dtattn", "reference"])
-    ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=["flux_joint", "wan_self", "sdxl_cross", "decode_b1", "decode_b16"])
     ap.add_argument("--chunks", type=int, default=4)
     ap.add_argument("--no-side", action="store_true", help="skip the decode / SDXL side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")

@@ -52,8 +52,44 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+namespace {
+// Encoding a tensor map costs a driver call of about a microsecond; a decode step re-uses the same views
+// thousands of times.  Small per-thread direct-mapped cache keyed by everything the encoding depends on.
+struct MapKey {
+  const void* ptr;
+  int64_t sb, ss, sh;
+  int B, S, H, D, dtype, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && sb == o.sb && ss == o.ss && sh == o.sh && B == o.B && S == o.S && H == o.H && D == o.D &&
+           dtype == o.dtype && box_rows == o.box_rows;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapCacheSize = 64;
+thread_local MapEntry g_map_cache[kMapCacheSize];
+
+size_t map_hash(const MapKey& k) {
+  size_t h = reinterpret_cast<size_t>(k.ptr) >> 4;
+  h = h * 1000003u ^ (size_t)k.S;
+  h = h * 1000003u ^ (size_t)k.box_rows;
+  h = h * 1000003u ^ (size_t)k.ss;
+  h = h * 1000003u ^ (size_t)k.B;
+  return h;
+}
+}  // namespace
+
 bool make_bshd_tensor_map(CUtensorMap* map, const dt_tensor4& t, int B, int S, int H, int D, int dtype,
                           int box_rows) {
+  const MapKey key{t.ptr, t.stride_b, t.stride_s, t.stride_h, B, S, H, D, dtype, box_rows};
+  MapEntry& slot = g_map_cache[map_hash(key) % kMapCacheSize];
+  if (slot.valid && slot.key == key) {
+    *map = slot.map;
+    return true;
+  }
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return false;
   if (dtype != DT_F16 && dtype != DT_BF16) return false;
@@ -75,7 +111,11 @@ bool make_bshd_tensor_map(CUtensorMap* map, const dt_tensor4& t, int B, int S, i
   CUresult r = enc(map, dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                    t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  slot.key = key;
+  slot.map = *map;
+  slot.valid = true;
+  return true;
 }
 
 // ---- validation and dispatch -------------------------------------------------------------------------
