@@ -230,6 +230,8 @@ struct HostScratch {
   void* ws = nullptr;
   size_t ws_bytes = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t s_in = nullptr, s_out = nullptr;  // copy streams of the pipelined path
+  cudaEvent_t ev_in[8] = {nullptr}, ev_done[8] = {nullptr};
 };
 thread_local HostScratch g_hs;
 
@@ -243,6 +245,12 @@ int dt_host_release(void) {
   if (g_hs.dev) cudaFree(g_hs.dev);
   if (g_hs.ws) cudaFree(g_hs.ws);
   if (g_hs.stream) cudaStreamDestroy(g_hs.stream);
+  if (g_hs.s_in) cudaStreamDestroy(g_hs.s_in);
+  if (g_hs.s_out) cudaStreamDestroy(g_hs.s_out);
+  for (int i = 0; i < 8; ++i) {
+    if (g_hs.ev_in[i]) cudaEventDestroy(g_hs.ev_in[i]);
+    if (g_hs.ev_done[i]) cudaEventDestroy(g_hs.ev_done[i]);
+  }
   g_hs = HostScratch();
   return DT_OK;
 }
@@ -284,6 +292,60 @@ int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
     DT_CUDA_TRY(cudaMemsetAsync(g_hs.ws, 0, wsb, g_hs.stream));
   }
   cudaStream_t s = g_hs.stream;
+  // Pipelined path for the large tensor-core shapes: heads are independent, so the host->device copy of one
+  // group of heads overlaps the attention of the previous group and the device->host copy of the one before
+  // (three streams, both copy engines busy).  Needs heads contiguous inside a token row and regular rows.
+  {
+    const int G = p.Hq / p.Hkv;
+    int groups = 0;
+    for (int g : {8, 6, 4, 3, 2})
+      if (p.Hkv % g == 0) { groups = g; break; }
+    auto regular = [&](const dt_tensor4& t, int S, int H) {
+      return t.stride_h == p.D && t.stride_s >= (int64_t)H * p.D && (p.B == 1 || t.stride_b == (int64_t)S * t.stride_s);
+    };
+    const bool big = nq + nk + nv >= (size_t)(16u << 20);
+    if (groups >= 2 && big && !p.lse && choose(p) == kPrefill && regular(p.q, p.Sq, p.Hq) && regular(p.k, p.Sk, p.Hkv) &&
+        regular(p.v, p.Sk, p.Hkv) && regular(p.o, p.Sq, p.Hq)) {
+      if (!g_hs.s_in) {
+        DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_in, cudaStreamNonBlocking));
+        DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 8; ++i) {
+          DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_in[i], cudaEventDisableTiming));
+          DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_done[i], cudaEventDisableTiming));
+        }
+      }
+      const int hk = p.Hkv / groups, hq = hk * G;
+      auto copy2d = [&](void* dst, const void* src, const dt_tensor4& t, int S, int heads, int h0, cudaMemcpyKind kind,
+                        cudaStream_t cs) {
+        const size_t off = (size_t)h0 * p.D * es;
+        return cudaMemcpy2DAsync(static_cast<char*>(dst) + off, (size_t)t.stride_s * es,
+                                 static_cast<const char*>(src) + off, (size_t)t.stride_s * es, (size_t)heads * p.D * es,
+                                 (size_t)p.B * S, kind, cs);
+      };
+      for (int g = 0; g < groups; ++g) {
+        DT_CUDA_TRY(copy2d(p.k.ptr, ph->k.ptr, p.k, p.Sk, hk, g * hk, cudaMemcpyHostToDevice, g_hs.s_in));
+        DT_CUDA_TRY(copy2d(p.v.ptr, ph->v.ptr, p.v, p.Sk, hk, g * hk, cudaMemcpyHostToDevice, g_hs.s_in));
+        DT_CUDA_TRY(copy2d(p.q.ptr, ph->q.ptr, p.q, p.Sq, hq, g * hq, cudaMemcpyHostToDevice, g_hs.s_in));
+        DT_CUDA_TRY(cudaEventRecord(g_hs.ev_in[g], g_hs.s_in));
+        DT_CUDA_TRY(cudaStreamWaitEvent(s, g_hs.ev_in[g], 0));
+        dt_sdpa_params pg = p;
+        pg.Hq = hq;
+        pg.Hkv = hk;
+        pg.q.ptr = static_cast<char*>(p.q.ptr) + (size_t)g * hq * p.D * es;
+        pg.k.ptr = static_cast<char*>(p.k.ptr) + (size_t)g * hk * p.D * es;
+        pg.v.ptr = static_cast<char*>(p.v.ptr) + (size_t)g * hk * p.D * es;
+        pg.o.ptr = static_cast<char*>(p.o.ptr) + (size_t)g * hq * p.D * es;
+        st = dt_sdpa_forward(&pg, g_hs.ws, g_hs.ws_bytes, s);
+        if (st != DT_OK) return st;
+        DT_CUDA_TRY(cudaEventRecord(g_hs.ev_done[g], s));
+        DT_CUDA_TRY(cudaStreamWaitEvent(g_hs.s_out, g_hs.ev_done[g], 0));
+        DT_CUDA_TRY(copy2d(ph->o.ptr, p.o.ptr, p.o, p.Sq, hq, g * hq, cudaMemcpyDeviceToHost, g_hs.s_out));
+      }
+      DT_CUDA_TRY(cudaStreamSynchronize(g_hs.s_out));
+      DT_CUDA_TRY(cudaStreamSynchronize(s));
+      return DT_OK;
+    }
+  }
   DT_CUDA_TRY(cudaMemcpyAsync(p.q.ptr, ph->q.ptr, nq, cudaMemcpyHostToDevice, s));
   DT_CUDA_TRY(cudaMemcpyAsync(p.k.ptr, ph->k.ptr, nk, cudaMemcpyHostToDevice, s));
   DT_CUDA_TRY(cudaMemcpyAsync(p.v.ptr, ph->v.ptr, nv, cudaMemcpyHostToDevice, s));

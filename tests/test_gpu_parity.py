@@ -346,6 +346,13 @@ def test_host_entry_point(dtattn):
         out = dtattn.sdpa_forward(q, k, v, D ** -0.5, causal)
         assert not out.is_cuda
         check(out, oracle(q, k, v, D ** -0.5, causal), dtype, "host path")
+    # a large tensor-core shape takes the pipelined path (copies of one head group overlap the attention of another)
+    q, k, v = inputs(1, 2304, 2304, 16, 8, 128, torch.bfloat16, 97)
+    out = dtattn.sdpa_forward(q, k, v, 128 ** -0.5)
+    rows = torch.arange(0, 2304, 11)
+    check(out[:, rows], oracle(q[:, rows].contiguous(), k, v, 128 ** -0.5), torch.bfloat16, "host path, pipelined")
+    out2 = dtattn.sdpa_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5).cpu()
+    assert torch.equal(out, out2), "host path and device path must agree bitwise"
     assert dtattn.lib().dt_host_release() == 0
 
 
