@@ -56,6 +56,7 @@ WORKLOADS = {
     # side measurements only
     "sd15_self_f16": dict(B=2, Sq=4096, Sk=4096, Hq=8, Hkv=8, D=40, dtype="f16", causal=False),
     "wan_self_5heads": dict(B=1, Sq=75600, Sk=75600, Hq=5, Hkv=5, D=128, dtype="bf16", causal=False),
+    "decode_qwen35_d256": dict(B=1, Sq=1, Sk=8192, Hq=16, Hkv=4, D=256, dtype="bf16", causal=True),
 }
 TDT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
@@ -181,7 +182,7 @@ def time_graph(fns, reps, warmup_reps=3):
 def side_measurements(dtattn, device, peaks):
     """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention."""
     out = {}
-    for name in ("decode_b16", "decode_b1", "sdxl_cross", "sd15_self_f16", "wan_self_5heads"):
+    for name in ("decode_b16", "decode_b1", "decode_qwen35_d256", "sdxl_cross", "sd15_self_f16", "wan_self_5heads"):
         w = WORKLOADS[name]
         nbytes = bytes_of(w)
         n_sets = max(2, -(-3 * L2_BYTES // nbytes))  # rotate through > 3x L2 worth of distinct inputs

@@ -38,9 +38,14 @@ constexpr int kMaxSplitPairs = (int)(kCounterBytes / sizeof(unsigned int));
 template <int D>
 struct Cfg {
   static constexpr int kHalves = D / 64;
-  static constexpr int kWarpTileBytes = 2 * kHalves * kBoxBytes;  // K boxes then V boxes
-  static constexpr int kStageBytes = kConsumerWarps * kWarpTileBytes;
-  static constexpr int kStages = D == 128 ? 3 : 4;
+  static constexpr int kWarpTileBytes = 2 * kHalves * kBoxBytes;  // one 16-key unit: K boxes then V boxes
+  // D = 256: two warps share a unit (both compute the scores, each accumulates 128 of the 256 output dims),
+  // so that the per-thread accumulators stay at 64 registers
+  static constexpr int kDimSplit = D > 128 ? 2 : 1;
+  static constexpr int kUnitsPerStage = kConsumerWarps / kDimSplit;
+  static constexpr int kDW = D / kDimSplit;  // output dims accumulated by one warp
+  static constexpr int kStageBytes = kUnitsPerStage * kWarpTileBytes;
+  static constexpr int kStages = D == 64 ? 4 : 3;
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -92,7 +97,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int unit_begin = split * a.units_per_split;
   const int unit_end = min(a.total_units, unit_begin + a.units_per_split);
   const int n_units = max(0, unit_end - unit_begin);
-  const int n_stages = (n_units + kConsumerWarps - 1) / kConsumerWarps;
+  const int n_stages = (n_units + C::kUnitsPerStage - 1) / C::kUnitsPerStage;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -107,9 +112,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   // per-lane running state of rows lane/4 (lo) and lane/4 + 8 (hi)
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-  float oacc[D / 8][4];
+  float oacc[C::kDW / 8][4];
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  for (int i = 0; i < C::kDW / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  const int uslot = warp % C::kUnitsPerStage;  // which unit of a stage this warp works on
+  const int dhalf = warp / C::kUnitsPerStage;  // which slice of the output dims it accumulates (consumer warps)
 
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
@@ -125,8 +132,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             break;
           }
         }
-        const int u0 = unit_begin + st * kConsumerWarps;
-        const int nu = min(kConsumerWarps, unit_end - u0);
+        const int u0 = unit_begin + st * C::kUnitsPerStage;
+        const int nu = min(C::kUnitsPerStage, unit_end - u0);
         ptx::mbar_arrive_expect_tx(&full_bar[slot], (uint32_t)(nu * C::kWarpTileBytes));
         for (int w = 0; w < nu; ++w) {
           uint8_t* dst = ring_ptr + slot * C::kStageBytes + w * C::kWarpTileBytes;
@@ -172,9 +179,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         break;
       }
       if (dbg && st == 0 && threadIdx.x == 0) dbg[1] = ptx::globaltimer_ns();
-      const int unit = unit_begin + st * kConsumerWarps + warp;
+      const int unit = unit_begin + st * C::kUnitsPerStage + uslot;
       if (unit < unit_end) {
-        const uint32_t kbase = ring + slot * C::kStageBytes + warp * C::kWarpTileBytes;
+        const uint32_t kbase = ring + slot * C::kStageBytes + uslot * C::kWarpTileBytes;
         const uint32_t vbase = kbase + C::kHalves * kBoxBytes;
         const int key0 = unit * kUnitKeys;
 
@@ -239,7 +246,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         pa[2] = pack2(sacc[1][0], sacc[1][1], kBf16);
         pa[3] = pack2(sacc[1][2], sacc[1][3], kBf16);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
+        for (int i = 0; i < C::kDW / 8; ++i) {
           oacc[i][0] *= al_lo;
           oacc[i][1] *= al_lo;
           oacc[i][2] *= al_hi;
@@ -248,8 +255,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         {
           const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
 #pragma unroll
-          for (int dp = 0; dp < D / 16; ++dp) {
-            const int chunk = dp * 2 + (lane >> 4);
+          for (int dp = 0; dp < C::kDW / 16; ++dp) {
+            const int chunk = dhalf * (C::kDW / 8) + dp * 2 + (lane >> 4);
             const uint32_t addr = vbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
             uint32_t v00, v01, v10, v11;
             ptx::ldmatrix_x4_trans(v00, v01, v10, v11, addr);
@@ -271,25 +278,25 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   __syncthreads();
   if (dbg && threadIdx.x == 0) dbg[2] = ptx::globaltimer_ns();
   float* obuf = reinterpret_cast<float*>(ring_ptr);                    // [4][16][D]
-  float* mbuf = obuf + kConsumerWarps * kMaxRows * D;                  // [4][16]
-  float* lbuf = mbuf + kConsumerWarps * kMaxRows;                      // [4][16]
+  float* mbuf = obuf + C::kUnitsPerStage * kMaxRows * D;               // [units per stage][16]
+  float* lbuf = mbuf + C::kUnitsPerStage * kMaxRows;                   // [units per stage][16]
   if (warp < kConsumerWarps) {
     const int r_lo = lane >> 2, r_hi = r_lo + 8, cq = (lane & 3) * 2;
-    float* ob = obuf + warp * kMaxRows * D;
+    float* ob = obuf + uslot * kMaxRows * D + dhalf * C::kDW;
     // only the M valid rows are merged; float2 stores, row pitch D floats
     if (r_lo < a.M) {
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(&ob[r_lo * D + i * 8 + cq]) = make_float2(oacc[i][0], oacc[i][1]);
+      for (int i = 0; i < C::kDW / 8; ++i) *reinterpret_cast<float2*>(&ob[r_lo * D + i * 8 + cq]) = make_float2(oacc[i][0], oacc[i][1]);
     }
     if (r_hi < a.M) {
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(&ob[r_hi * D + i * 8 + cq]) = make_float2(oacc[i][2], oacc[i][3]);
+      for (int i = 0; i < C::kDW / 8; ++i) *reinterpret_cast<float2*>(&ob[r_hi * D + i * 8 + cq]) = make_float2(oacc[i][2], oacc[i][3]);
     }
-    if ((lane & 3) == 0) {
-      mbuf[warp * kMaxRows + r_lo] = m_lo;
-      mbuf[warp * kMaxRows + r_hi] = m_hi;
-      lbuf[warp * kMaxRows + r_lo] = l_lo;
-      lbuf[warp * kMaxRows + r_hi] = l_hi;
+    if ((lane & 3) == 0 && dhalf == 0) {
+      mbuf[uslot * kMaxRows + r_lo] = m_lo;
+      mbuf[uslot * kMaxRows + r_hi] = m_hi;
+      lbuf[uslot * kMaxRows + r_lo] = l_lo;
+      lbuf[uslot * kMaxRows + r_hi] = l_hi;
     }
   }
   __syncthreads();
@@ -300,11 +307,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int r = idx / D, d = idx - r * D;
     float mstar = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) mstar = fmaxf(mstar, mbuf[w * kMaxRows + r]);
+    for (int w = 0; w < C::kUnitsPerStage; ++w) mstar = fmaxf(mstar, mbuf[w * kMaxRows + r]);
     float lt = 0.f, ot = 0.f;
     if (mstar != -INFINITY) {
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) {
+      for (int w = 0; w < C::kUnitsPerStage; ++w) {
         const float wgt = fast_exp2(mbuf[w * kMaxRows + r] - mstar);
         lt += wgt * lbuf[w * kMaxRows + r];
         ot += wgt * obuf[(w * kMaxRows + r) * D + d];
@@ -487,7 +494,7 @@ int launch_t(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_
 
 bool decode_supported(const dt_sdpa_params& p) {
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
-  if (p.D != 64 && p.D != 128) return false;
+  if (p.D != 64 && p.D != 128 && p.D != 256) return false;  // 256: the reference's Qwen3.5 configs (Qwen3_5.swift:59-82)
   if (p.mask) return false;
   if (p.Hq % p.Hkv) return false;
   const int M = p.Sq * (p.Hq / p.Hkv);
@@ -512,8 +519,10 @@ size_t decode_workspace_bytes(const dt_sdpa_params& p) {
 
 int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
   if (p.dtype == DT_F16) {
+    if (p.D == 256) return launch_t<__half, 256>(p, workspace, bytes, stream);
     return p.D == 128 ? launch_t<__half, 128>(p, workspace, bytes, stream) : launch_t<__half, 64>(p, workspace, bytes, stream);
   }
+  if (p.D == 256) return launch_t<__nv_bfloat16, 256>(p, workspace, bytes, stream);
   return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, workspace, bytes, stream)
                     : launch_t<__nv_bfloat16, 64>(p, workspace, bytes, stream);
 }
@@ -601,7 +610,7 @@ extern "C" int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream
   using namespace dt;
   if (!p || !p->q.ptr || !p->k.ptr || !p->v.ptr || !p->o.ptr) return DT_BAD_ARG;
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Hq % p->Hkv) return DT_BAD_ARG;
-  if (!decode_supported(*p)) return DT_UNSUPPORTED;
+  if (!decode_supported(*p) || p->D == 256) return DT_UNSUPPORTED;
   int dev = 0;
   DT_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return DT_NO_DEVICE;

@@ -117,6 +117,9 @@ DECODE = [
     (1, 4, 777, 8, 2, 128, torch.bfloat16),       # multi-token verify: 4 new tokens x 4 heads = 16 rows
     (1, 2, 4096, 16, 2, 128, torch.float16),      # group of 8
     (2, 1, 8192, 16, 4, 64, torch.float16),
+    (1, 1, 4096, 16, 4, 256, torch.bfloat16),     # the reference's Qwen3.5 attention: head dim 256, 4 KV heads (Qwen3_5.swift:59-82)
+    (2, 2, 1000, 24, 4, 256, torch.float16),      # 24 query heads: groups of 6, two new tokens -> 12 rows
+    (1, 1, 300, 4, 4, 256, torch.float16),
 ]
 
 
