@@ -205,6 +205,58 @@ def side_measurements(dtattn, device, peaks):
                      "tflops": round(flops_of(w) / (best * 1e-3) / 1e12, 2), "rotating_sets": n_sets}
         del sets, fns
         torch.cuda.empty_cache()
+    out.update(decode_step_measurements(dtattn, device))
+    return out
+
+
+def decode_step_measurements(dtattn, device):
+    """One KV-cache step (rotary on q and k, cache append, attention) as ONE launch of the fused entry point,
+    beside the same step as separate launches (elementwise rotary and row copies through torch, then
+    dt_sdpa_forward), both replayed from CUDA graphs over rotating caches larger than L2."""
+    out = {}
+    for name in ("decode_qwen35_d256", "decode_b16"):
+        w = WORKLOADS[name]
+        dt = TDT[w["dtype"]]
+        B, T, Hq, Hkv, D = w["B"], w["Sk"], w["Hq"], w["Hkv"], w["D"]
+        nbytes = bytes_of(w)
+        n_sets = min(16, max(2, -(-3 * L2_BYTES // nbytes)))
+        g = torch.Generator(device=device).manual_seed(11)
+        rnd = lambda *shape: torch.randn(*shape, generator=g, device=device, dtype=torch.float32).to(dt)
+        sets = [dict(q=rnd(B, 1, Hq, D), kn=rnd(B, 1, Hkv, D), vn=rnd(B, 1, Hkv, D), kc=rnd(B, T, Hkv, D),
+                     vc=rnd(B, T, Hkv, D), o=torch.empty(B, 1, Hq, D, device=device, dtype=dt)) for _ in range(n_sets)]
+        ang = torch.rand(1, 1, D // 2, generator=g, device=device) * 6.28
+        rot = torch.stack([ang.cos(), ang.sin()], dim=-1).reshape(1, 1, D).to(dt)
+        scale = D ** -0.5
+
+        def fused(s):
+            dtattn.decode_step(s["q"], s["kc"], s["vc"], s["kn"], s["vn"], rot, scale, T - 1, out=s["o"])
+
+        def cmul(x):
+            x0, x1 = x[..., 0::2].float(), x[..., 1::2].float()
+            c, sn = rot[:, :, None, 0::2].float(), rot[:, :, None, 1::2].float()
+            return torch.stack([x0 * c - x1 * sn, x0 * sn + x1 * c], dim=-1).reshape(x.shape).to(x.dtype)
+
+        def separate(s):
+            qr = cmul(s["q"])
+            s["kc"][:, T - 1:T] = cmul(s["kn"])
+            s["vc"][:, T - 1:T] = s["vn"]
+            dtattn.sdpa_forward(qr, s["kc"], s["vc"], scale, True, out=s["o"])
+
+        res = {}
+        for label, fn in (("fused", fused), ("separate", separate)):
+            fns = [(lambda s=s, fn=fn: fn(s)) for s in sets]
+            try:
+                res[label] = time_graph(fns, reps=20)
+            except Exception as e:
+                res[label] = None
+                out[f"decode_step_{name}_{label}_error"] = str(e)[:120]
+        out["decode_step_" + name] = {
+            "us_per_step_fused_1_launch": round(res["fused"] * 1e3, 2) if res["fused"] else None,
+            "us_per_step_separate_launches": round(res["separate"] * 1e3, 2) if res["separate"] else None,
+            "gbs_fused": round(nbytes / (res["fused"] * 1e-3) / 1e9, 1) if res["fused"] else None,
+            "rotating_sets": n_sets}
+        del sets
+        torch.cuda.empty_cache()
     return out
 
 

@@ -60,7 +60,12 @@ struct DecodeArgs {
   float* part_o;           // [B*Hkv][nsplit][M][D]
   unsigned int* status;
   unsigned long long* dbg;  // optional per-CTA timeline (bring-up probe)
+  // decode-step fusion (all null / 0 for a plain attention call): new K/V rows to rotate, append and attend
+  const void* k_new; const void* v_new; const void* rotary; void* k_cache; void* v_cache;
+  int64_t kn_sb, kn_ss, kn_sh, vn_sb, vn_ss, vn_sh, rot_sb, rot_ss, kc_sb, kc_ss, kc_sh, vc_sb, vc_ss, vc_sh;
   int Sq, Sk, Hq, Hkv, G, M;
+  int stream_keys;  // cache rows streamed through the ring: Sk, or Sk - Tn with the step fusion
+  int Tn;           // new rows appended by the step fusion (<= 16), 0 otherwise
   int nsplit, units_per_split, total_units;
   float scale_log2;
   int is_causal;
@@ -73,6 +78,25 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   }
   __half2 t = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// (x0 + i x1) * (cos + i sin) on one packed 16-bit pair: fp32 products and sum without fused multiply-add
+// (so that the result does not depend on how the compiler contracts it), rounded once to T: the reference's
+// Functional.cmul (Libraries/SwiftLLM/Sources/Models/Qwen3_5.swift:170-182) on adjacent head dims.
+template <typename T>
+__device__ __forceinline__ uint32_t cmul_pair(uint32_t x, uint32_t cs) {
+  float x0, x1, c, s;
+  if constexpr (std::is_same<T, __half>::value) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x));
+    const float2 r = __half22float2(*reinterpret_cast<const __half2*>(&cs));
+    x0 = a.x; x1 = a.y; c = r.x; s = r.y;
+  } else {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+    const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cs));
+    x0 = a.x; x1 = a.y; c = r.x; s = r.y;
+  }
+  return pack2(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)), __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)),
+               !std::is_same<T, __half>::value);
 }
 
 template <typename T, int D>
@@ -118,6 +142,140 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int uslot = warp % C::kUnitsPerStage;  // which unit of a stage this warp works on
   const int dhalf = warp / C::kUnitsPerStage;  // which slice of the output dims it accumulates (consumer warps)
 
+  // ---------------- per-warp set-up of the consumer warps (declared here so that the streamed units and
+  // the optional extra unit of freshly appended rows share one code path) ----------------
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+  const int cq = (lane & 3) * 2;
+  // Q fragments (A operand, rows = (query token, group head), k = head dim)
+  uint32_t qa[D / 16][4];
+  if (warp < kConsumerWarps) {
+    const T* q = reinterpret_cast<const T*>(a.q);
+    const T* rot = reinterpret_cast<const T*>(a.rotary);
+    const T* p_lo = nullptr;
+    const T* p_hi = nullptr;
+    const T* t_lo = nullptr;
+    const T* t_hi = nullptr;
+    if (r_lo < a.M) {
+      p_lo = q + b * a.q_sb + (int64_t)(r_lo / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_lo % a.G) * a.q_sh;
+      if (rot) t_lo = rot + b * a.rot_sb + (int64_t)(a.Tn - a.Sq + r_lo / a.G) * a.rot_ss;
+    }
+    if (r_hi < a.M) {
+      p_hi = q + b * a.q_sb + (int64_t)(r_hi / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_hi % a.G) * a.q_sh;
+      if (rot) t_hi = rot + b * a.rot_sb + (int64_t)(a.Tn - a.Sq + r_hi / a.G) * a.rot_ss;
+    }
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa[ks][0] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq) : 0u;
+      qa[ks][1] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq) : 0u;
+      qa[ks][2] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq + 8) : 0u;
+      qa[ks][3] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq + 8) : 0u;
+    }
+    // rotation as a second pass, so that the loads above stay back to back when there is no table: a fragment
+    // register holds head dims (d, d+1) with d even, exactly one (cos, sin) pair of the rotary table
+    if (rot) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t c0 = t_lo ? *reinterpret_cast<const uint32_t*>(t_lo + ks * 16 + cq) : 0u;
+        const uint32_t c1 = t_hi ? *reinterpret_cast<const uint32_t*>(t_hi + ks * 16 + cq) : 0u;
+        const uint32_t c2 = t_lo ? *reinterpret_cast<const uint32_t*>(t_lo + ks * 16 + cq + 8) : 0u;
+        const uint32_t c3 = t_hi ? *reinterpret_cast<const uint32_t*>(t_hi + ks * 16 + cq + 8) : 0u;
+        qa[ks][0] = cmul_pair<T>(qa[ks][0], c0);
+        qa[ks][1] = cmul_pair<T>(qa[ks][1], c1);
+        qa[ks][2] = cmul_pair<T>(qa[ks][2], c2);
+        qa[ks][3] = cmul_pair<T>(qa[ks][3], c3);
+      }
+    }
+  }
+  // last visible key per row (inclusive)
+  const int off = a.Sk - a.Sq;
+  const int vis_lo = a.is_causal ? min(a.Sk - 1, r_lo / a.G + off) : a.Sk - 1;
+  const int vis_hi = a.is_causal ? min(a.Sk - 1, r_hi / a.G + off) : a.Sk - 1;
+
+  // one 16-key unit: scores, online softmax, P V.  kbase / vbase: swizzled K and V tiles in shared memory.
+  // Keys beyond `last_key` are masked on top of the causal rule (rows past the streamed range are TMA zero fill).
+  auto process_unit = [&](uint32_t kbase, uint32_t vbase, int key0, int last_key) {
+    const int vl_lo = min(vis_lo, last_key), vl_hi = min(vis_hi, last_key);
+    float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const int key = ((lane >> 4) << 3) + (lane & 7);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int chunk = ks * 2 + ((lane >> 3) & 1);
+        const uint32_t addr = kbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        uint32_t b00, b01, b10, b11;
+        ptx::ldmatrix_x4(b00, b01, b10, b11, addr);
+        ptx::mma_m16n8k16<kBf16>(sacc[0], qa[ks], b00, b01);
+        ptx::mma_m16n8k16<kBf16>(sacc[1], qa[ks], b10, b11);
+      }
+    }
+    // scale, mask, online softmax
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = key0 + nt * 8 + cq + e;
+        float s0 = sacc[nt][e] * a.scale_log2;
+        float s1 = sacc[nt][2 + e] * a.scale_log2;
+        if (j > vl_lo) s0 = -INFINITY;
+        if (j > vl_hi) s1 = -INFINITY;
+        sacc[nt][e] = s0;
+        sacc[nt][2 + e] = s1;
+        mx_lo = fmaxf(mx_lo, s0);
+        mx_hi = fmaxf(mx_hi, s1);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+    const float ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+    const float al_lo = fast_exp2(m_lo - ms_lo), al_hi = fast_exp2(m_hi - ms_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float p0 = fast_exp2(sacc[nt][e] - ms_lo);
+        const float p1 = fast_exp2(sacc[nt][2 + e] - ms_hi);
+        sacc[nt][e] = p0;
+        sacc[nt][2 + e] = p1;
+        ps_lo += p0;
+        ps_hi += p1;
+      }
+    }
+    l_lo = l_lo * al_lo + ps_lo;
+    l_hi = l_hi * al_hi + ps_hi;
+    uint32_t pa[4];
+    pa[0] = pack2(sacc[0][0], sacc[0][1], kBf16);
+    pa[1] = pack2(sacc[0][2], sacc[0][3], kBf16);
+    pa[2] = pack2(sacc[1][0], sacc[1][1], kBf16);
+    pa[3] = pack2(sacc[1][2], sacc[1][3], kBf16);
+#pragma unroll
+    for (int i = 0; i < C::kDW / 8; ++i) {
+      oacc[i][0] *= al_lo;
+      oacc[i][1] *= al_lo;
+      oacc[i][2] *= al_hi;
+      oacc[i][3] *= al_hi;
+    }
+    {
+      const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+      for (int dp = 0; dp < C::kDW / 16; ++dp) {
+        const int chunk = dhalf * (C::kDW / 8) + dp * 2 + (lane >> 4);
+        const uint32_t addr = vbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        uint32_t v00, v01, v10, v11;
+        ptx::ldmatrix_x4_trans(v00, v01, v10, v11, addr);
+        ptx::mma_m16n8k16<kBf16>(oacc[2 * dp], pa, v00, v01);
+        ptx::mma_m16n8k16<kBf16>(oacc[2 * dp + 1], pa, v10, v11);
+      }
+    }
+  };
+
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
     if (lane == 0) {
@@ -148,29 +306,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
   } else {
     // ---------------- consumers ----------------
-    const int r_lo = lane >> 2, r_hi = r_lo + 8;
-    const int cq = (lane & 3) * 2;
-    // Q fragments (A operand, rows = (query token, group head), k = head dim)
-    uint32_t qa[D / 16][4];
-    {
-      const T* q = reinterpret_cast<const T*>(a.q);
-      const T* p_lo = nullptr;
-      const T* p_hi = nullptr;
-      if (r_lo < a.M) p_lo = q + b * a.q_sb + (int64_t)(r_lo / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_lo % a.G) * a.q_sh;
-      if (r_hi < a.M) p_hi = q + b * a.q_sb + (int64_t)(r_hi / a.G) * a.q_ss + (int64_t)(kvh * a.G + r_hi % a.G) * a.q_sh;
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        qa[ks][0] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq) : 0u;
-        qa[ks][1] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq) : 0u;
-        qa[ks][2] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq + 8) : 0u;
-        qa[ks][3] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq + 8) : 0u;
-      }
-    }
-    // last visible key per row (inclusive)
-    const int off = a.Sk - a.Sq;
-    const int vis_lo = a.is_causal ? min(a.Sk - 1, r_lo / a.G + off) : a.Sk - 1;
-    const int vis_hi = a.is_causal ? min(a.Sk - 1, r_hi / a.G + off) : a.Sk - 1;
-
     for (int st = 0; st < n_stages; ++st) {
       const int slot = st % C::kStages;
       if (!ptx::mbar_wait(&full_bar[slot], (st / C::kStages) & 1, &s_abort)) {
@@ -182,92 +317,57 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       const int unit = unit_begin + st * C::kUnitsPerStage + uslot;
       if (unit < unit_end) {
         const uint32_t kbase = ring + slot * C::kStageBytes + uslot * C::kWarpTileBytes;
-        const uint32_t vbase = kbase + C::kHalves * kBoxBytes;
-        const int key0 = unit * kUnitKeys;
-
-        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        {
-          const int key = ((lane >> 4) << 3) + (lane & 7);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const int chunk = ks * 2 + ((lane >> 3) & 1);
-            const uint32_t addr = kbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
-            uint32_t b00, b01, b10, b11;
-            ptx::ldmatrix_x4(b00, b01, b10, b11, addr);
-            ptx::mma_m16n8k16<kBf16>(sacc[0], qa[ks], b00, b01);
-            ptx::mma_m16n8k16<kBf16>(sacc[1], qa[ks], b10, b11);
-          }
-        }
-        // scale, mask, online softmax
-        float mx_lo = -INFINITY, mx_hi = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = key0 + nt * 8 + cq + e;
-            float s0 = sacc[nt][e] * a.scale_log2;
-            float s1 = sacc[nt][2 + e] * a.scale_log2;
-            if (j > vis_lo) s0 = -INFINITY;
-            if (j > vis_hi) s1 = -INFINITY;
-            sacc[nt][e] = s0;
-            sacc[nt][2 + e] = s1;
-            mx_lo = fmaxf(mx_lo, s0);
-            mx_hi = fmaxf(mx_hi, s1);
-          }
-        }
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-        const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
-        const float ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-        const float al_lo = fast_exp2(m_lo - ms_lo), al_hi = fast_exp2(m_hi - ms_hi);
-        m_lo = mn_lo;
-        m_hi = mn_hi;
-        float ps_lo = 0.f, ps_hi = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float p0 = fast_exp2(sacc[nt][e] - ms_lo);
-            const float p1 = fast_exp2(sacc[nt][2 + e] - ms_hi);
-            sacc[nt][e] = p0;
-            sacc[nt][2 + e] = p1;
-            ps_lo += p0;
-            ps_hi += p1;
-          }
-        }
-        l_lo = l_lo * al_lo + ps_lo;
-        l_hi = l_hi * al_hi + ps_hi;
-        uint32_t pa[4];
-        pa[0] = pack2(sacc[0][0], sacc[0][1], kBf16);
-        pa[1] = pack2(sacc[0][2], sacc[0][3], kBf16);
-        pa[2] = pack2(sacc[1][0], sacc[1][1], kBf16);
-        pa[3] = pack2(sacc[1][2], sacc[1][3], kBf16);
-#pragma unroll
-        for (int i = 0; i < C::kDW / 8; ++i) {
-          oacc[i][0] *= al_lo;
-          oacc[i][1] *= al_lo;
-          oacc[i][2] *= al_hi;
-          oacc[i][3] *= al_hi;
-        }
-        {
-          const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
-#pragma unroll
-          for (int dp = 0; dp < C::kDW / 16; ++dp) {
-            const int chunk = dhalf * (C::kDW / 8) + dp * 2 + (lane >> 4);
-            const uint32_t addr = vbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
-            uint32_t v00, v01, v10, v11;
-            ptx::ldmatrix_x4_trans(v00, v01, v10, v11, addr);
-            ptx::mma_m16n8k16<kBf16>(oacc[2 * dp], pa, v00, v01);
-            ptx::mma_m16n8k16<kBf16>(oacc[2 * dp + 1], pa, v10, v11);
-          }
-        }
+        process_unit(kbase, kbase + C::kHalves * kBoxBytes, unit * kUnitKeys, a.stream_keys - 1);
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
     }
+  }
+
+  // ---------------- decode step fusion: rotate, append and attend the new K/V rows ----------------
+  // The cache rows streamed above end at Sk - Tn; the Tn new rows come from k_new / v_new.  The last split of
+  // each (batch, KV head) rotates the new keys, stores new keys and values into the cache for later steps and
+  // attends to them as one more unit built in shared memory (the ring is idle after the barrier).
+  if (a.k_new != nullptr) {
+    __syncthreads();
+    if (split == a.nsplit - 1 && warp < kConsumerWarps && uslot == 0) {
+      const uint32_t tile = ring + dhalf * C::kWarpTileBytes;  // with D = 256 the two warps of the pair build one copy each
+      const T* kn = reinterpret_cast<const T*>(a.k_new);
+      const T* vn = reinterpret_cast<const T*>(a.v_new);
+      const T* rot = reinterpret_cast<const T*>(a.rotary);
+      T* kc = reinterpret_cast<T*>(a.k_cache);
+      T* vc = reinterpret_cast<T*>(a.v_cache);
+      const int t_old = a.stream_keys;
+      constexpr int kChunks = D / 8;  // 16-byte chunks per row
+      for (int it = lane; it < kUnitKeys * kChunks; it += 32) {
+        const int row = it / kChunks, ch = it - row * kChunks;
+        uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = make_uint4(0u, 0u, 0u, 0u);
+        if (row < a.Tn) {
+          kq = *reinterpret_cast<const uint4*>(kn + b * a.kn_sb + (int64_t)row * a.kn_ss + (int64_t)kvh * a.kn_sh + ch * 8);
+          vq = *reinterpret_cast<const uint4*>(vn + b * a.vn_sb + (int64_t)row * a.vn_ss + (int64_t)kvh * a.vn_sh + ch * 8);
+          if (rot) {
+            const uint4 rq = *reinterpret_cast<const uint4*>(rot + b * a.rot_sb + (int64_t)row * a.rot_ss + ch * 8);
+            kq.x = cmul_pair<T>(kq.x, rq.x);
+            kq.y = cmul_pair<T>(kq.y, rq.y);
+            kq.z = cmul_pair<T>(kq.z, rq.z);
+            kq.w = cmul_pair<T>(kq.w, rq.w);
+          }
+          if (dhalf == 0) {
+            *reinterpret_cast<uint4*>(kc + b * a.kc_sb + (int64_t)(t_old + row) * a.kc_ss + (int64_t)kvh * a.kc_sh + ch * 8) = kq;
+            *reinterpret_cast<uint4*>(vc + b * a.vc_sb + (int64_t)(t_old + row) * a.vc_ss + (int64_t)kvh * a.vc_sh + ch * 8) = vq;
+          }
+        }
+        const uint32_t o = (uint32_t)(ch >> 3) * kBoxBytes + (uint32_t)row * 128 + ((((uint32_t)ch & 7u) ^ ((uint32_t)row & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile + o), "r"(kq.x), "r"(kq.y), "r"(kq.z), "r"(kq.w) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile + C::kHalves * kBoxBytes + o), "r"(vq.x), "r"(vq.y),
+                     "r"(vq.z), "r"(vq.w)
+                     : "memory");
+      }
+      __syncwarp();
+      process_unit(tile, tile + C::kHalves * kBoxBytes, t_old, a.Sk - 1);
+    }
+  }
+  if (warp < kConsumerWarps) {
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
@@ -430,9 +530,14 @@ struct Plan {
 // ticket, combine), so use as few CTAs as keep every SM streaming: the largest power of two with
 // pairs * splits <= 2 CTAs per SM, and at least four 16-key units per split.  (Measured on B200: B=16
 // runs at 99% of the copy peak with 2 splits and at 57% with 37.)
-Plan make_plan(const dt_sdpa_params& p) {
+Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
   Plan pl;
-  pl.total_units = (p.Sk + kUnitKeys - 1) / kUnitKeys;
+  pl.total_units = (stream_keys + kUnitKeys - 1) / kUnitKeys;
+  if (pl.total_units == 0) {  // empty cache (first step of a sequence): one CTA per pair, nothing streamed
+    pl.nsplit = 1;
+    pl.units_per_split = 0;
+    return pl;
+  }
   const int pairs = p.B * p.Hkv;
   const int slots = 2 * sm_count();
   int ns = 1;
@@ -448,15 +553,26 @@ Plan make_plan(const dt_sdpa_params& p) {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+size_t plan_workspace_bytes(const dt_sdpa_params& p, const Plan& pl) {
+  if (pl.nsplit <= 1) return 0;
+  const size_t pairs = (size_t)p.B * p.Hkv;
+  const size_t M = (size_t)p.Sq * (p.Hq / p.Hkv);
+  return kCounterBytes + align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256) +
+         align_up(pairs * pl.nsplit * M * p.D * sizeof(float), 256);
+}
+
 template <typename T, int D>
-int launch_t(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
+int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* workspace, size_t bytes,
+             cudaStream_t stream) {
   using C = Cfg<D>;
-  const Plan pl = make_plan(p);
+  const int Tn = step ? step->T_new : 0;
+  const int stream_keys = p.Sk - Tn;
+  const Plan pl = make_plan(p, stream_keys);
   const int G = p.Hq / p.Hkv, M = p.Sq * G;
   const size_t pairs = (size_t)p.B * p.Hkv;
   DecodeArgs a{};
   if (pl.nsplit > 1) {
-    const size_t need = decode_workspace_bytes(p);
+    const size_t need = plan_workspace_bytes(p, pl);
     if (!workspace || bytes < need) return DT_WORKSPACE;
     uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
     a.counters = reinterpret_cast<unsigned int*>(w);
@@ -465,9 +581,12 @@ int launch_t(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_
     off += align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256);
     a.part_o = reinterpret_cast<float*>(w + off);
   }
+  // The maps cover exactly the streamed rows: what a unit reads past them is TMA zero fill, never the rows
+  // another CTA of this launch is appending.  (An empty cache still needs a valid map; it is never read.)
   CUtensorMap mk, mv;
-  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  const int map_rows = stream_keys > 0 ? stream_keys : 1;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, map_rows, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, map_rows, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
   a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
   a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
@@ -475,6 +594,17 @@ int launch_t(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_
   if (!a.status) return DT_CUDA;
   a.dbg = g_decode_dbg;
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
+  a.stream_keys = stream_keys;
+  a.Tn = Tn;
+  if (step) {
+    a.k_new = step->k_new.ptr; a.v_new = step->v_new.ptr; a.rotary = step->rotary;
+    a.k_cache = p.k.ptr; a.v_cache = p.v.ptr;
+    a.kn_sb = step->k_new.stride_b; a.kn_ss = step->k_new.stride_s; a.kn_sh = step->k_new.stride_h;
+    a.vn_sb = step->v_new.stride_b; a.vn_ss = step->v_new.stride_s; a.vn_sh = step->v_new.stride_h;
+    a.rot_sb = step->rotary_stride_b; a.rot_ss = step->rotary_stride_s;
+    a.kc_sb = p.k.stride_b; a.kc_ss = p.k.stride_s; a.kc_sh = p.k.stride_h;
+    a.vc_sb = p.v.stride_b; a.vc_ss = p.v.stride_s; a.vc_sh = p.v.stride_h;
+  }
   a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
@@ -508,26 +638,65 @@ bool decode_supported(const dt_sdpa_params& p) {
   return ok(p.q) && ok(p.k) && ok(p.v);
 }
 
-size_t decode_workspace_bytes(const dt_sdpa_params& p) {
-  const Plan pl = make_plan(p);
-  if (pl.nsplit <= 1) return 0;
-  const size_t pairs = (size_t)p.B * p.Hkv;
-  const size_t M = (size_t)p.Sq * (p.Hq / p.Hkv);
-  return kCounterBytes + align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256) +
-         align_up(pairs * pl.nsplit * M * p.D * sizeof(float), 256);
+size_t decode_workspace_bytes(const dt_sdpa_params& p) { return plan_workspace_bytes(p, make_plan(p, p.Sk)); }
+
+namespace {
+int dispatch_decode(const dt_sdpa_params& p, const dt_decode_step_params* step, void* workspace, size_t bytes,
+                    cudaStream_t stream) {
+  if (p.dtype == DT_F16) {
+    if (p.D == 256) return launch_t<__half, 256>(p, step, workspace, bytes, stream);
+    return p.D == 128 ? launch_t<__half, 128>(p, step, workspace, bytes, stream)
+                      : launch_t<__half, 64>(p, step, workspace, bytes, stream);
+  }
+  if (p.D == 256) return launch_t<__nv_bfloat16, 256>(p, step, workspace, bytes, stream);
+  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, step, workspace, bytes, stream)
+                    : launch_t<__nv_bfloat16, 64>(p, step, workspace, bytes, stream);
 }
 
+// Argument rules of the fused decode step on top of decode_supported().
+int validate_step(const dt_decode_step_params* s) {
+  if (!s) return DT_BAD_ARG;
+  const dt_sdpa_params& p = s->attn;
+  if (!p.q.ptr || !p.k.ptr || !p.v.ptr || !p.o.ptr || !s->k_new.ptr || !s->v_new.ptr) return DT_BAD_ARG;
+  if (p.B <= 0 || p.Sq <= 0 || p.Sk <= 0 || p.Hq <= 0 || p.Hkv <= 0 || p.Hq % p.Hkv) return DT_BAD_ARG;
+  if (s->T_new < p.Sq || s->T_new > p.Sk) return DT_BAD_ARG;
+  if (s->T_new > kUnitKeys) return DT_UNSUPPORTED;  // the new rows form one 16-key unit
+  if (!p.is_causal && s->T_new != p.Sq) return DT_BAD_ARG;
+  if (!decode_supported(p)) return DT_UNSUPPORTED;
+  auto ok = [](const dt_tensor4& t) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && t.stride_b % 8 == 0 && t.stride_s % 8 == 0 &&
+           t.stride_h % 8 == 0;
+  };
+  if (!ok(s->k_new) || !ok(s->v_new)) return DT_UNSUPPORTED;
+  if (s->rotary && (reinterpret_cast<uintptr_t>(s->rotary) % 16 || s->rotary_stride_b % 8 || s->rotary_stride_s % 8))
+    return DT_UNSUPPORTED;
+  return DT_OK;
+}
+}  // namespace
+
 int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
-  if (p.dtype == DT_F16) {
-    if (p.D == 256) return launch_t<__half, 256>(p, workspace, bytes, stream);
-    return p.D == 128 ? launch_t<__half, 128>(p, workspace, bytes, stream) : launch_t<__half, 64>(p, workspace, bytes, stream);
-  }
-  if (p.D == 256) return launch_t<__nv_bfloat16, 256>(p, workspace, bytes, stream);
-  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, workspace, bytes, stream)
-                    : launch_t<__nv_bfloat16, 64>(p, workspace, bytes, stream);
+  return dispatch_decode(p, nullptr, workspace, bytes, stream);
 }
 
 }  // namespace dt
+
+// ---- fused decode step -------------------------------------------------------------------------------
+extern "C" int dt_sdpa_decode_step_workspace_size(const dt_decode_step_params* s, size_t* bytes) {
+  using namespace dt;
+  if (!bytes) return DT_BAD_ARG;
+  const int st = validate_step(s);
+  if (st != DT_OK) return st;
+  *bytes = plan_workspace_bytes(s->attn, make_plan(s->attn, s->attn.Sk - s->T_new));
+  return DT_OK;
+}
+
+extern "C" int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspace, size_t workspace_bytes,
+                                   void* cuda_stream) {
+  using namespace dt;
+  const int st = validate_step(s);
+  if (st != DT_OK) return st;
+  return dispatch_decode(s->attn, s, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
 
 // ---- entry point that allocates nothing ----------------------------------------------------------------
 // Scratch for the split-KV partials lives in a file-scope device array instead of a caller workspace.
@@ -566,7 +735,7 @@ int noalloc_setup(int dev, NoAllocDevice** out) {
 template <typename T, int D>
 int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, cudaStream_t stream) {
   using C = Cfg<D>;
-  const Plan pl = make_plan(p);
+  const Plan pl = make_plan(p, p.Sk);
   const int G = p.Hq / p.Hkv, M = p.Sq * G;
   const size_t pairs = (size_t)p.B * p.Hkv;
   DecodeArgs a{};
@@ -589,6 +758,7 @@ int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, c
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
   a.status = dev->status;
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
+  a.stream_keys = p.Sk;
   a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;

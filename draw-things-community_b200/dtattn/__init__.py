@@ -45,6 +45,11 @@ class SdpaParams(ctypes.Structure):
                 ("mask_stride_q", ctypes.c_int64), ("lse", ctypes.c_void_p)]
 
 
+class DecodeStepParams(ctypes.Structure):
+    _fields_ = [("attn", SdpaParams), ("k_new", Tensor4), ("v_new", Tensor4), ("T_new", ctypes.c_int32),
+                ("rotary", ctypes.c_void_p), ("rotary_stride_b", ctypes.c_int64), ("rotary_stride_s", ctypes.c_int64)]
+
+
 class DtError(RuntimeError):
     def __init__(self, status, what):
         self.status = status
@@ -66,6 +71,8 @@ SYMBOLS = [
     ("dt_sdpa_forward_host", ctypes.c_int, [_P(SdpaParams)]),
     ("dt_host_release", ctypes.c_int, []),
     ("dt_device_status", ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int)]),
+    ("dt_sdpa_decode_step_workspace_size", ctypes.c_int, [_P(DecodeStepParams), _P(ctypes.c_size_t)]),
+    ("dt_sdpa_decode_step", ctypes.c_int, [_P(DecodeStepParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_sdpa_decode_noalloc", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p]),
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
@@ -189,6 +196,45 @@ def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None,
                                      ctypes.c_void_p(s)), "dt_sdpa_forward")
     else:
         _check(lib().dt_sdpa_forward_host(ctypes.byref(p)), "dt_sdpa_forward_host")
+    return out
+
+
+def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_len, is_causal=True,
+                     lse=None) -> DecodeStepParams:
+    """k_cache / v_cache: [B, capacity, Hkv, D]; the step attends over their first `total_len` rows, of which
+    the last k_new.shape[1] are written by the call."""
+    sp = DecodeStepParams()
+    sp.attn = make_params(q, k_cache[:, :total_len], v_cache[:, :total_len], o, scale, is_causal, None, lse)
+    sp.k_new, sp.v_new = _view4(k_new), _view4(v_new)
+    sp.T_new = k_new.shape[1]
+    if rotary is not None:
+        assert rotary.dim() == 3 and rotary.dtype == q.dtype and rotary.shape[1] == k_new.shape[1]
+        assert rotary.stride(2) == 1
+        sp.rotary = rotary.data_ptr()
+        sp.rotary_stride_b = rotary.stride(0) if rotary.shape[0] > 1 else 0
+        sp.rotary_stride_s = rotary.stride(1)
+    return sp
+
+
+def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, out=None, lse=None, workspace=None,
+                stream=None):
+    """One KV-cache step in one launch (Qwen3_5.swift:167-196): rotate q and k_new with `rotary`
+    ([B or 1, T_new, D], interleaved cos/sin), write rotated k_new and v_new into cache rows
+    [cached_len, cached_len + T_new) and return causal attention of the rotated queries over rows
+    [0, cached_len + T_new).  q holds the last Sq <= T_new tokens' queries."""
+    assert q.is_cuda, "the fused decode step takes device tensors"
+    B, Sq, Hq, D = q.shape
+    if out is None:
+        out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
+    sp = make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, out, scale, cached_len + k_new.shape[1], True, lse)
+    need = ctypes.c_size_t(0)
+    _check(lib().dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)),
+           "dt_sdpa_decode_step_workspace_size")
+    s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    ws = workspace if workspace is not None else _default_workspace(q.device)
+    ptr, nbytes = ws.ensure(need.value, s)
+    _check(lib().dt_sdpa_decode_step(ctypes.byref(sp), ctypes.c_void_p(ptr) if ptr else None, nbytes,
+                                     ctypes.c_void_p(s)), "dt_sdpa_decode_step")
     return out
 
 

@@ -108,6 +108,33 @@ int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name);
 int dt_sdpa_forward_host(const dt_sdpa_params* p_host);
 int dt_host_release(void);
 
+/* Fused decode step ---------------------------------------------------------------------------------
+ * One launch for what the reference's attention block does around the node in a KV-cache step
+ * (Libraries/SwiftLLM/Sources/Models/Qwen3_5.swift:167-196):
+ *     queries = Functional.cmul(queries, rotary rows of the last Sq tokens)          (:167-181)
+ *     keys    = Functional.cmul(keys, rotary)                                        (:182)
+ *     keys.moved(to: kIn[.., cachedTokenLength.., ..]); values.moved(to: vIn[...])   (:183-192)
+ *     out = ScaledDotProductAttention(scale:, isCausal: true)(queries, kIn, vIn)     (:193-196)
+ * attn.k / attn.v are the CACHE views [B, Sk, Hkv, D] with Sk = cached rows + T_new (the rows
+ * [Sk - T_new, Sk) are written by this call); attn.q holds the un-rotated queries of the last Sq <= T_new
+ * tokens; k_new / v_new are the un-rotated new rows [B, T_new, Hkv, D], T_new <= 16.  rotary is the
+ * reference's table for the new tokens, [B or 1, T_new, D] in the tensors' dtype with (cos, sin) interleaved
+ * on adjacent head dims (cmul multiplies (x[2i] + i x[2i+1]) by (cos_i + i sin_i)); NULL skips the rotation.
+ * attn.is_causal must be 1 when Sq < T_new.  The rotated keys are rounded to the tensors' dtype before
+ * they are attended to and stored, as the reference's separate cmul node does.  Same dtypes, head dims and
+ * alignment rules as the "decode_splitkv" kernel; anything else returns DT_UNSUPPORTED.
+ */
+typedef struct {
+  dt_sdpa_params attn;
+  dt_tensor4 k_new, v_new;
+  int32_t T_new;
+  const void* rotary;
+  int64_t rotary_stride_b, rotary_stride_s; /* stride_b 0 = one table for the whole batch */
+} dt_decode_step_params;
+int dt_sdpa_decode_step_workspace_size(const dt_decode_step_params* s, size_t* bytes);
+int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream);
+
 /* Decode without any allocation ---------------------------------------------------------------------
  * No counterpart in the reference.  Some hosts of this library cannot obtain device memory at the moment
  * they call: a runtime that handed the whole device to its own allocator at start-up (the reference's graph

@@ -141,6 +141,39 @@ def cmul(x, rot):
     return out
 
 
+def qwen_rotary_table(sequence_length, cached_len, head_dim, rotary_dim=None, theta=10_000_000.0):
+    """[1, sequence_length, head_dim] interleaved (cos, sin) table, restating Qwen3_5RotaryEmbedding
+    (Qwen3_5.swift:85-108): token i sits at position cached_len + i; pair k < rotary_dim/2 holds
+    (cos, sin) of position / theta^(2k/rotary_dim) computed in float64; the remaining pairs hold (1, 0), so
+    the head dims beyond rotary_dim pass through cmul unchanged (the reference's configs rotate 64 of 256 dims,
+    Qwen3_5.swift:59-82)."""
+    rotary_dim = head_dim if rotary_dim is None else rotary_dim
+    pos = (cached_len + np.arange(sequence_length, dtype=np.float64))[:, None]
+    k = np.arange(rotary_dim // 2, dtype=np.float64)[None, :]
+    ang = pos / theta ** (k * 2.0 / rotary_dim)
+    tab = np.zeros((1, sequence_length, head_dim), dtype=np.float32)
+    tab[0, :, 0:rotary_dim:2] = np.cos(ang)
+    tab[0, :, 1:rotary_dim:2] = np.sin(ang)
+    tab[0, :, rotary_dim::2] = 1.0
+    return torch.from_numpy(tab)
+
+
+def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, dtype):
+    """The reference's KV-cache step as separate nodes (Qwen3_5.swift:167-196), every node's output rounded to
+    `dtype` as a graph of 16-bit tensors does: cmul on the queries (rotary rows of the last Sq tokens) and on the
+    new keys, new keys / values moved into the cache at row cached_len, causal attention over rows
+    [0, cached_len + T_new).  Inputs are `dtype` tensors on the CPU; k_cache / v_cache ([B, capacity, Hkv, D])
+    are updated in place.  Returns fp32 attention output computed from the rounded operands."""
+    Sq, Tn = q.shape[1], k_new.shape[1]
+    rot = None if rotary is None else rotary.float()[:, :, None, :]
+    qr = q.float() if rot is None else cmul(q.float(), rot[:, Tn - Sq:]).to(dtype).float()
+    kr = k_new if rot is None else cmul(k_new.float(), rot).to(dtype)
+    k_cache[:, cached_len:cached_len + Tn] = kr
+    v_cache[:, cached_len:cached_len + Tn] = v_new
+    total = cached_len + Tn
+    return sdpa_explicit(qr.to(dtype), k_cache[:, :total], v_cache[:, :total], scale, True)
+
+
 # --------------------------------------------------------------------------------------------------
 # Seeded N(0,1): restatement of TorchRandomSource (MT19937 + 16-wide Box-Muller)
 # --------------------------------------------------------------------------------------------------
