@@ -206,6 +206,34 @@ def side_measurements(dtattn, device, peaks):
         del sets, fns
         torch.cuda.empty_cache()
     out.update(decode_step_measurements(dtattn, device))
+    out.update(prologue_measurements(dtattn, device, peaks))
+    return out
+
+
+def prologue_measurements(dtattn, device, peaks):
+    """The Q/K prologue (RMSNorm + rotary, one pass) on the Flux and Wan-slice shapes: GB/s of the bytes it must
+    move (read and write Q and K once, read the table once) against the copy peak, rotating buffers > L2."""
+    out = {}
+    for name, (S, H, D, per_token, post) in {"flux_joint": (4608, 24, 128, False, 1.0),
+                                            "wan_self_5heads": (75600, 5, 128, True, 128 ** -0.25)}.items():
+        dt = torch.bfloat16
+        nbytes = 2 * 2 * S * H * D * 2 + S * D * 2
+        n_sets = min(8, max(2, -(-3 * L2_BYTES // nbytes)))
+        g = torch.Generator(device=device).manual_seed(13)
+        rnd = lambda *shape: torch.randn(*shape, generator=g, device=device, dtype=torch.float32).to(dt)
+        sets = [(rnd(1, S, H, D), rnd(1, S, H, D), torch.empty(1, S, H, D, device=device, dtype=dt),
+                 torch.empty(1, S, H, D, device=device, dtype=dt)) for _ in range(n_sets)]
+        wq, wk = rnd(H * D if per_token else D), rnd(H * D if per_token else D)
+        rot = rnd(1, S, 1, D)
+        fns = [(lambda s=s: dtattn.qk_prologue(s[0], s[1], q_out=s[2], k_out=s[3], q_weight=wq, k_weight=wk, rotary=rot,
+                                               norm_per_token=per_token, post_scale=post)) for s in sets]
+        ms = time_graph(fns, reps=10)
+        out["qk_prologue_" + name] = {"us_per_call": round(ms * 1e3, 2), "algorithmic_bytes": nbytes,
+                                      "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                                      "frac_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                                      "rotating_sets": n_sets}
+        del sets, fns
+        torch.cuda.empty_cache()
     return out
 
 
@@ -525,6 +553,8 @@ def main():
     ap.add_argument("--no-t1", action="store_true", help="skip the single-GPU run of the sharded workload")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
+    ap.add_argument("--only", default=None, choices=["prologue", "decode_step"],
+                    help="run one group of side measurements alone and print it (for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
     if args.impl == "reference":
@@ -539,6 +569,11 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    if args.only:
+        fn = {"prologue": lambda: prologue_measurements(dtattn, device, peaks),
+              "decode_step": lambda: decode_step_measurements(dtattn, device)}[args.only]
+        print(json.dumps({"only": args.only, "also": fn()}))
+        return
     if world > 1:
         run_sharded(args, dtattn, device, peaks)
     else:

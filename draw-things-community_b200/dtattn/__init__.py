@@ -50,6 +50,14 @@ class DecodeStepParams(ctypes.Structure):
                 ("rotary", ctypes.c_void_p), ("rotary_stride_b", ctypes.c_int64), ("rotary_stride_s", ctypes.c_int64)]
 
 
+class QkPrologueParams(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("S", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("x", Tensor4), ("y", Tensor4), ("norm_weight", ctypes.c_void_p),
+                ("norm_per_token", ctypes.c_int32), ("eps", ctypes.c_float), ("rotary", ctypes.c_void_p),
+                ("rotary_stride_b", ctypes.c_int64), ("rotary_stride_s", ctypes.c_int64),
+                ("rotary_stride_h", ctypes.c_int64), ("post_scale", ctypes.c_float)]
+
+
 class DtError(RuntimeError):
     def __init__(self, status, what):
         self.status = status
@@ -74,6 +82,7 @@ SYMBOLS = [
     ("dt_sdpa_decode_step_workspace_size", ctypes.c_int, [_P(DecodeStepParams), _P(ctypes.c_size_t)]),
     ("dt_sdpa_decode_step", ctypes.c_int, [_P(DecodeStepParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_sdpa_decode_noalloc", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p]),
+    ("dt_qk_prologue", ctypes.c_int, [_P(QkPrologueParams), _P(QkPrologueParams), ctypes.c_void_p]),
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
     ("dt_comm_destroy", ctypes.c_int, [ctypes.c_void_p]),
@@ -236,6 +245,48 @@ def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, ou
     _check(lib().dt_sdpa_decode_step(ctypes.byref(sp), ctypes.c_void_p(ptr) if ptr else None, nbytes,
                                      ctypes.c_void_p(s)), "dt_sdpa_decode_step")
     return out
+
+
+def make_prologue_params(x, y, norm_weight=None, rotary=None, eps=1e-6, norm_per_token=False,
+                         post_scale=1.0) -> QkPrologueParams:
+    p = QkPrologueParams()
+    p.B, p.S, p.H, p.D = x.shape
+    p.dtype = _DTYPES[x.dtype]
+    p.x, p.y = _view4(x), _view4(y)
+    if norm_weight is not None:
+        assert norm_weight.dtype == x.dtype and norm_weight.is_contiguous()
+        assert norm_weight.numel() == (p.H * p.D if norm_per_token else p.D)
+        p.norm_weight = norm_weight.data_ptr()
+    p.norm_per_token = int(bool(norm_per_token))
+    p.eps = float(eps)
+    if rotary is not None:
+        assert rotary.dim() == 4 and rotary.dtype == x.dtype and rotary.stride(3) == 1
+        assert rotary.shape[1] == p.S and rotary.shape[3] == p.D
+        p.rotary = rotary.data_ptr()
+        p.rotary_stride_b = rotary.stride(0) if rotary.shape[0] > 1 else 0
+        p.rotary_stride_s = rotary.stride(1)
+        p.rotary_stride_h = rotary.stride(2) if rotary.shape[2] > 1 else 0
+    p.post_scale = float(post_scale)
+    return p
+
+
+def qk_prologue(q, k=None, *, q_out=None, k_out=None, q_weight=None, k_weight=None, rotary=None, rotary_k=None,
+                eps=1e-6, norm_per_token=False, post_scale=1.0, stream=None):
+    """RMSNorm, rotary cmul and pre-scale of queries and keys in one launch (the nodes before the attention
+    node at Flux1.swift:164-188, Wan.swift:86-98, Qwen3_5.swift:164-182).  Outputs default to new tensors; pass
+    q_out / k_out views (e.g. row-offset views of a joint buffer) to write in place or to fuse a concat."""
+    assert q.is_cuda
+    q_out = torch.empty_like(q) if q_out is None else q_out
+    pq = make_prologue_params(q, q_out, q_weight, rotary, eps, norm_per_token, post_scale)
+    pk = None
+    if k is not None:
+        k_out = torch.empty_like(k) if k_out is None else k_out
+        pk = make_prologue_params(k, k_out, k_weight, rotary if rotary_k is None else rotary_k, eps, norm_per_token,
+                                  post_scale)
+    s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    _check(lib().dt_qk_prologue(ctypes.byref(pq), ctypes.byref(pk) if pk is not None else None, ctypes.c_void_p(s)),
+           "dt_qk_prologue")
+    return q_out, k_out
 
 
 _workspaces = {}

@@ -135,6 +135,34 @@ int dt_sdpa_decode_step_workspace_size(const dt_decode_step_params* s, size_t* b
 int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspace, size_t workspace_bytes,
                         void* cuda_stream);
 
+/* Q/K prologue -----------------------------------------------------------------------------------------
+ * The steps the reference runs on queries and keys immediately before the attention node, as one pass over HBM
+ * instead of one graph node (a full read and write of the tensor) per step:
+ *   RMSNorm(epsilon:, axis: [3]) per head row      Flux1.swift:164-181, Qwen3_5.swift:164-167
+ *   RMSNorm(epsilon:, axis: [2]) over all h*k channels of a token    Wan.swift:86-91   (norm_per_token = 1)
+ *   Functional.cmul(left:, right: rotary)          Flux1.swift:187-188, Wan.swift:92-93, Qwen3_5.swift:168-182
+ *   multiplication by D^(-1/4)                     Wan.swift:94-97                      (post_scale)
+ * y = post_scale * cmul(rmsnorm(x) * norm_weight, rotary); each step is skipped when its operand is NULL / 1 and
+ * each step's result is rounded to `dtype` (DT_F16 or DT_BF16) before the next one, as separate 16-bit graph nodes
+ * do.  x and y are [B, S, H, D] views (y may alias x, or be a row-offset view of a larger buffer, which fuses the
+ * reference's concat of text and image tokens, Flux1.swift:184-186); D % 8 == 0, D <= 256, 16-byte aligned bases,
+ * strides multiples of 8 elements.  rotary: [B or 1, S, H or 1, D] in `dtype`, (cos, sin) interleaved on adjacent
+ * channels; a broadcast axis has stride 0.  norm_weight: [D], or [H*D] with norm_per_token.
+ * dt_qk_prologue(q, k, stream) processes both tensors in one launch (k may be NULL).
+ */
+typedef struct {
+  int32_t B, S, H, D;
+  int32_t dtype;
+  dt_tensor4 x, y;
+  const void* norm_weight;
+  int32_t norm_per_token;
+  float eps;
+  const void* rotary;
+  int64_t rotary_stride_b, rotary_stride_s, rotary_stride_h;
+  float post_scale; /* 0 is read as 1 */
+} dt_qk_prologue_params;
+int dt_qk_prologue(const dt_qk_prologue_params* q, const dt_qk_prologue_params* k, void* cuda_stream);
+
 /* Decode without any allocation ---------------------------------------------------------------------
  * No counterpart in the reference.  Some hosts of this library cannot obtain device memory at the moment
  * they call: a runtime that handed the whole device to its own allocator at start-up (the reference's graph

@@ -158,6 +158,30 @@ def qwen_rotary_table(sequence_length, cached_len, head_dim, rotary_dim=None, th
     return torch.from_numpy(tab)
 
 
+def qk_prologue_explicit(x, weight, rotary, eps, dtype, norm_per_token=False, post_scale=1.0):
+    """The nodes the reference runs on queries / keys before the attention node, each output rounded to `dtype`:
+    RMSNorm over the head dim (Flux1.swift:164-181, Qwen3_5.swift:164-167) or over all h*k channels of a token
+    (Wan.swift:86-91), y = x / sqrt(mean(x^2) + eps) * weight in fp32; Functional.cmul with the rotary table
+    (Flux1.swift:187-188); multiplication by a constant (Wan.swift:94-97).  x [B,S,H,D] in `dtype` on the CPU;
+    weight [D] or [H*D]; rotary broadcastable to x.  Returns a `dtype` tensor."""
+    y = x
+    if weight is not None:
+        xf = x.float()
+        if norm_per_token:
+            B, S, H, D = x.shape
+            flat = xf.reshape(B, S, H * D)
+            inv = 1.0 / torch.sqrt(flat.pow(2).mean(dim=-1, keepdim=True) + eps)
+            y = ((flat * inv) * weight.float().reshape(1, 1, H * D)).reshape(B, S, H, D).to(dtype)
+        else:
+            inv = 1.0 / torch.sqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+            y = ((xf * inv) * weight.float()).to(dtype)
+    if rotary is not None:
+        y = cmul(y.float(), rotary.float()).to(dtype)
+    if post_scale != 1.0:
+        y = (y.float() * torch.tensor(post_scale, dtype=torch.float32)).to(dtype)
+    return y
+
+
 def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, dtype):
     """The reference's KV-cache step as separate nodes (Qwen3_5.swift:167-196), every node's output rounded to
     `dtype` as a graph of 16-bit tensors does: cmul on the queries (rotary rows of the last Sq tokens) and on the
