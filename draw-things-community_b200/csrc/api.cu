@@ -132,6 +132,14 @@ static int validate(const dt_sdpa_params* p) {
   for (auto t : ts)
     if (reinterpret_cast<uintptr_t>(t->ptr) % es) return DT_BAD_ARG;
   if (p->D > 256) return DT_UNSUPPORTED;
+  if (p->sliding_window < 0) return DT_BAD_ARG;
+  if (p->sinks && reinterpret_cast<uintptr_t>(p->sinks) % es) return DT_BAD_ARG;
+  if ((p->seq_offsets_q != nullptr) != (p->seq_offsets_k != nullptr)) return DT_BAD_ARG;
+  if (p->seq_offsets_q) {
+    if (p->B != 1 || p->n_seq <= 0 || p->max_seq_q <= 0 || p->max_seq_k <= 0) return DT_BAD_ARG;
+    if (p->max_seq_q > p->Sq || p->max_seq_k > p->Sk) return DT_BAD_ARG;
+    if (p->mask) return DT_UNSUPPORTED;
+  }
   return DT_OK;
 }
 
@@ -168,7 +176,7 @@ const char* dt_status_string(int status) {
 
 int dt_last_cuda_error(void) { return g_last_cuda_error; }
 
-int dt_abi_version(void) { return 1; }
+int dt_abi_version(void) { return 2; }
 
 int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name) {
   int st = validate(p);

@@ -623,6 +623,8 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
 }  // namespace
 
 bool decode_supported(const dt_sdpa_params& p) {
+  if (p.seq_offsets_q) return false;  // variable-length batches: generic kernel
+  if (p.sinks || p.sliding_window > 0) return false;
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D != 64 && p.D != 128 && p.D != 256) return false;  // 256: the reference's Qwen3.5 configs (Qwen3_5.swift:59-82)
   if (p.mask) return false;

@@ -635,6 +635,8 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
 }  // namespace
 
 bool prefill_supported(const dt_sdpa_params& p) {
+  if (p.seq_offsets_q) return false;  // variable-length batches: generic kernel
+  if (p.sinks || p.sliding_window > 0) return false;
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)
   if (p.mask) return false;

@@ -42,7 +42,10 @@ class SdpaParams(ctypes.Structure):
                 ("is_causal", ctypes.c_int32), ("flags", ctypes.c_uint32),
                 ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4),
                 ("mask", ctypes.c_void_p), ("mask_stride_b", ctypes.c_int64), ("mask_stride_h", ctypes.c_int64),
-                ("mask_stride_q", ctypes.c_int64), ("lse", ctypes.c_void_p)]
+                ("mask_stride_q", ctypes.c_int64), ("lse", ctypes.c_void_p),
+                ("sinks", ctypes.c_void_p), ("sliding_window", ctypes.c_int32), ("n_seq", ctypes.c_int32),
+                ("max_seq_q", ctypes.c_int32), ("max_seq_k", ctypes.c_int32),
+                ("seq_offsets_q", ctypes.c_void_p), ("seq_offsets_k", ctypes.c_void_p)]
 
 
 class DecodeStepParams(ctypes.Structure):
@@ -124,7 +127,8 @@ def _view4(t: torch.Tensor) -> Tensor4:
     return Tensor4(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
 
 
-def make_params(q, k, v, o, scale, is_causal=False, mask=None, lse=None, flags=0) -> SdpaParams:
+def make_params(q, k, v, o, scale, is_causal=False, mask=None, lse=None, flags=0, sinks=None, sliding_window=0,
+                seq_offsets_q=None, seq_offsets_k=None, max_seq_q=0, max_seq_k=0) -> SdpaParams:
     B, Sq, Hq, D = q.shape
     _, Sk, Hkv, _ = k.shape
     p = SdpaParams()
@@ -144,6 +148,17 @@ def make_params(q, k, v, o, scale, is_causal=False, mask=None, lse=None, flags=0
     if lse is not None:
         assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, Hq, Sq)
         p.lse = lse.data_ptr()
+    if sinks is not None:
+        assert sinks.dtype == q.dtype and sinks.is_contiguous() and sinks.numel() == Hq
+        p.sinks = sinks.data_ptr()
+    p.sliding_window = int(sliding_window)
+    if seq_offsets_q is not None:
+        for t in (seq_offsets_q, seq_offsets_k):
+            assert t.dtype == torch.int32 and t.is_contiguous() and t.device == q.device
+        assert seq_offsets_q.numel() == seq_offsets_k.numel() >= 2
+        p.n_seq = seq_offsets_q.numel() - 1
+        p.seq_offsets_q, p.seq_offsets_k = seq_offsets_q.data_ptr(), seq_offsets_k.data_ptr()
+        p.max_seq_q, p.max_seq_k = int(max_seq_q or Sq), int(max_seq_k or Sk)
     return p
 
 
@@ -187,7 +202,8 @@ class Workspace:
 
 
 def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None, flags=0, workspace=None,
-                 stream=None):
+                 stream=None, sinks=None, sliding_window=0, seq_offsets_q=None, seq_offsets_k=None, max_seq_q=0,
+                 max_seq_k=0):
     """O = softmax(scale * Q K^T [+mask] [causal]) V through the C ABI.
 
     CUDA tensors -> dt_sdpa_forward on the current (or given) stream; CPU tensors -> dt_sdpa_forward_host,
@@ -196,7 +212,8 @@ def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None,
     B, Sq, Hq, D = q.shape
     if out is None:
         out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
-    p = make_params(q, k, v, out, scale, is_causal, mask, lse, flags)
+    p = make_params(q, k, v, out, scale, is_causal, mask, lse, flags, sinks, sliding_window, seq_offsets_q,
+                    seq_offsets_k, max_seq_q, max_seq_k)
     if q.is_cuda:
         s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
         ws = workspace if workspace is not None else _default_workspace(q.device)
@@ -319,6 +336,10 @@ class ScaledDotProductAttention:
       is_causal             bottom-right aligned causal mask (Qwen3_5.swift:193-196)
       has_attention_mask    a 4th input [B|1, H|1, Sq, Sk] is added to the scores (CLIPTextModel.swift:46-51)
       flags                 GEMMFlag set; accepted for signature parity
+      has_attention_sinks   a 4th input [1,1,H,1]: one extra unscaled score per head in the softmax denominator
+      sliding_window        only the last W keys up to the query's own position are visible
+      is_variable_length    packed rows; two more inputs hold the int32 sequence offsets (n_seq + 1 entries each);
+                            max_sequence_length = (query, keyValue) bounds of one sequence
       multi_head_output_projection_fused
                             the reference fuses the output Dense into the op (UNet.swift:122-130); not built
                             here -> the constructor raises, as the reference would on an unsupported back end
@@ -326,7 +347,14 @@ class ScaledDotProductAttention:
     """
 
     def __init__(self, scale, is_causal=False, has_attention_mask=False, flags=(), multi_head_output_projection_fused=False,
-                 name=""):
+                 name="", has_attention_sinks=False, sliding_window=0, is_variable_length=False,
+                 max_sequence_length=None):
+        # hasAttentionSinks / slidingWindow: DeepSeek4.swift:482-493; isVariableLength / maxSequenceLength
+        # (query:, keyValue:): Qwen3_5VL.swift:428-437
+        self.has_attention_sinks = bool(has_attention_sinks)
+        self.sliding_window = int(sliding_window or 0)
+        self.is_variable_length = bool(is_variable_length)
+        self.max_sequence_length = max_sequence_length
         if multi_head_output_projection_fused:
             raise NotImplementedError("multiHeadOutputProjectionFused is outside this library's scope")
         self.scale = float(scale)
@@ -340,11 +368,31 @@ class ScaledDotProductAttention:
         if GEMMFlag.Int8 in f:
             raise NotImplementedError("quantised attention ([.Int8, .Float16]) is never selected off Metal")
 
-    def __call__(self, queries, keys, values, mask=None, *, out=None, lse=None):
+    def __call__(self, queries, keys, values, *extra, mask=None, out=None, lse=None):
+        """Extra positional inputs follow the reference's order: the mask (hasAttentionMask), or the sinks tensor
+        (hasAttentionSinks, DeepSeek4.swift:489-493), or the two sequence-offset tensors (isVariableLength,
+        Qwen3_5VL.swift:434)."""
+        extra = list(extra)
+        sinks = offs_q = offs_k = None
+        if self.has_attention_mask and mask is None and extra:
+            mask = extra.pop(0)
+        if self.has_attention_sinks:
+            if not extra:
+                raise ValueError("hasAttentionSinks needs the sinks input")
+            sinks = extra.pop(0).reshape(-1).contiguous()
+        if self.is_variable_length:
+            if len(extra) < 2:
+                raise ValueError("isVariableLength needs the query and key/value sequence offsets")
+            offs_q, offs_k = extra.pop(0), extra.pop(0)
+        if extra:
+            raise ValueError("more inputs than the operator was built for")
         if self.has_attention_mask != (mask is not None):
             raise ValueError("hasAttentionMask and the number of inputs disagree")
         abi_flags = DT_FLAG_FP16_ACCUM_HINT if GEMMFlag.Float16 in self.flags else 0
-        return sdpa_forward(queries, keys, values, self.scale, self.is_causal, mask, out=out, lse=lse, flags=abi_flags)
+        mq, mk = self.max_sequence_length if self.max_sequence_length else (0, 0)
+        return sdpa_forward(queries, keys, values, self.scale, self.is_causal, mask, out=out, lse=lse, flags=abi_flags,
+                            sinks=sinks, sliding_window=self.sliding_window, seq_offsets_q=offs_q, seq_offsets_k=offs_k,
+                            max_seq_q=mq, max_seq_k=mk)
 
 
 # --------------------------------------------------------------------------------------------------

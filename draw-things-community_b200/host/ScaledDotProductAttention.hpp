@@ -75,6 +75,17 @@ class ScaledDotProductAttention {
     return n;
   }
 
+  // Operator variants of the reference's initialiser: hasAttentionSinks + slidingWindow
+  // (SwiftLLM/Sources/Models/DeepSeek4.swift:482-493) and isVariableLength + maxSequenceLength
+  // (SwiftLLM/Sources/Models/Qwen3_5VL.swift:428-437).  The inputs they add are set here before the call.
+  ScaledDotProductAttention& withSinks(const void* sinks_hq) { sinks_ = sinks_hq; return *this; }
+  ScaledDotProductAttention& withSlidingWindow(int window) { window_ = window; return *this; }
+  ScaledDotProductAttention& withSequenceOffsets(const int32_t* q_offsets, const int32_t* kv_offsets, int n_seq,
+                                                 int max_q, int max_kv) {
+    off_q_ = q_offsets; off_k_ = kv_offsets; n_seq_ = n_seq; max_q_ = max_q; max_k_ = max_kv;
+    return *this;
+  }
+
   // op(queries, keys, values[, mask]) -> out, enqueued on `stream`.
   void operator()(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out,
                   void* workspace, size_t workspace_bytes, void* stream, const TensorView* mask = nullptr) const {
@@ -102,9 +113,18 @@ class ScaledDotProductAttention {
       p.mask_stride_h = mask->S > 1 ? mask->stride_s : 0;
       p.mask_stride_q = mask->stride_h;
     }
+    p.sinks = sinks_;
+    p.sliding_window = window_;
+    p.seq_offsets_q = off_q_; p.seq_offsets_k = off_k_;
+    p.n_seq = n_seq_; p.max_seq_q = max_q_; p.max_seq_k = max_k_;
     return p;
   }
   float scale_;
+  const void* sinks_ = nullptr;
+  int window_ = 0;
+  const int32_t* off_q_ = nullptr;
+  const int32_t* off_k_ = nullptr;
+  int n_seq_ = 0, max_q_ = 0, max_k_ = 0;
   bool causal_, has_mask_;
   unsigned flags_;
   std::string name_;

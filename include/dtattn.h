@@ -70,6 +70,23 @@ typedef struct {
   int64_t mask_stride_b, mask_stride_h, mask_stride_q;
   /* optional fp32 log-sum-exp output [B, Hq, Sq] (natural log of sum_j exp(scale*s_ij)), NULL = none   */
   float* lse;
+  /* Operator variants (ScaledDotProductAttention(... hasAttentionSinks:, slidingWindow:, isVariableLength:,
+     maxSequenceLength:)); all zero / NULL = the plain operator.
+     sinks: one logit per query head, [Hq] in the tensors' dtype (the reference passes a [1,1,Hq,1] tensor cast to
+       the queries' type, SwiftLLM/Sources/Models/DeepSeek4.swift:482-493): an extra score column without a value
+       row, so row i's weights are exp(s_ij - m) / (sum_j exp(s_ij - m) + exp(sink_h - m)).  The scale is not
+       applied to it.  lse, when asked for, includes the sink term.
+     sliding_window W > 0: key j is visible to query i only if j > i + (Sk - Sq) - W (the last W keys up to and
+       including the query's own position), on top of the causal rule when is_causal is set.
+     seq_offsets_q / seq_offsets_k (device, int32, n_seq + 1 entries, first 0, non-decreasing): variable-length
+       batches (SwiftLLM/Sources/Models/Qwen3_5VL.swift:428-437).  B must be 1; q and o hold sum(Sq_s) rows and
+       k, v sum(Sk_s) rows; sequence s attends rows [off_q[s], off_q[s+1]) to rows [off_k[s], off_k[s+1]).  Sq and
+       Sk are the packed row counts, max_seq_q / max_seq_k upper bounds of one sequence's rows.               */
+  const void* sinks;
+  int32_t sliding_window;
+  int32_t n_seq, max_seq_q, max_seq_k;
+  const int32_t* seq_offsets_q;
+  const int32_t* seq_offsets_k;
 } dt_sdpa_params;
 
 /* Library / device ------------------------------------------------------------------------------ */

@@ -39,7 +39,7 @@ MASK_FILL = -torch.finfo(torch.float32).max  # the reference fills with -greates
 
 
 def sdpa_explicit(q, k, v, scale, is_causal=False, mask=None, *, compute_dtype=torch.float32,
-                  p_dtype=None, return_lse=False):
+                  p_dtype=None, return_lse=False, sinks=None, sliding_window=0):
     """softmax(scale * Q K^T [+ mask]) V written the way the reference's explicit graphs write it.
 
     q [B,Sq,Hq,D], k/v [B,Sk,Hkv,D] (BSHD).  Steps, with the reference line each follows:
@@ -54,6 +54,10 @@ def sdpa_explicit(q, k, v, scale, is_causal=False, mask=None, *, compute_dtype=t
       8. optional cast of P to V's dtype (upcastAttention)          UNet.swift:257-259
       9. P * V, transposed back to BSHD                             UNet.swift:261-262
     compute_dtype float64 gives the high-precision variant used to bound the fp32 oracle's own error.
+    Operator variants (DeepSeek4.swift:482-493 builds the node with hasAttentionSinks and slidingWindow; their
+    arithmetic is in the absent back end, so the usual definitions are restated): `sinks` [Hq] is one extra
+    unscaled score column per head that takes part in the softmax and has no value row; `sliding_window` W hides
+    keys j <= i + (Sk - Sq) - W.
     """
     B, Sq, Hq, D = q.shape
     _, Sk, Hkv, _ = k.shape
@@ -73,10 +77,19 @@ def sdpa_explicit(q, k, v, scale, is_causal=False, mask=None, *, compute_dtype=t
         j = torch.arange(Sk).view(1, Sk)
         hidden = j > i + (Sk - Sq)
         s = s.masked_fill(hidden, float("-inf"))
+    if sliding_window > 0:
+        i = torch.arange(Sq).view(Sq, 1)
+        j = torch.arange(Sk).view(1, Sk)
+        s = s.masked_fill(j <= i + (Sk - Sq) - sliding_window, float("-inf"))
     m = s.amax(dim=-1, keepdim=True)
+    if sinks is not None:
+        sk = sinks.to(compute_dtype).view(1, Hq, 1, 1)
+        m = torch.maximum(m, sk.expand_as(m))
     m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
     e = torch.exp(s - m)
     l = e.sum(dim=-1, keepdim=True)
+    if sinks is not None:
+        l = l + torch.exp(sk - m)
     p = e / torch.where(l > 0, l, torch.ones_like(l))      # a row with no visible key yields zeros
     if p_dtype is not None:
         p = p.to(p_dtype).to(compute_dtype)
@@ -85,6 +98,17 @@ def sdpa_explicit(q, k, v, scale, is_causal=False, mask=None, *, compute_dtype=t
         lse = (m + torch.log(l)).squeeze(-1)               # [B,Hq,Sq]
         return o, lse
     return o
+
+
+def sdpa_varlen_explicit(q, k, v, scale, offsets_q, offsets_k, is_causal=False, **kw):
+    """Variable-length batch (Qwen3_5VL.swift:428-437: packed rows plus sequence offsets): sequence s attends its
+    own rows only.  q [1,sum Sq,Hq,D], k/v [1,sum Sk,Hkv,D]; offsets are Python lists with n_seq + 1 entries."""
+    out = torch.zeros(q.shape, dtype=kw.get("compute_dtype", torch.float32))
+    for s in range(len(offsets_q) - 1):
+        q0, q1, k0, k1 = offsets_q[s], offsets_q[s + 1], offsets_k[s], offsets_k[s + 1]
+        if q1 > q0:
+            out[:, q0:q1] = sdpa_explicit(q[:, q0:q1], k[:, k0:k1], v[:, k0:k1], scale, is_causal, **kw)
+    return out
 
 
 def instruction_count(batch, heads, head_dim, seq_a, seq_b):

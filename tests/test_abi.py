@@ -27,10 +27,11 @@ def test_header_symbols_are_exported(dtattn):
 
 
 def test_struct_layout_matches_header(dtattn):
-    # 10 x 4-byte scalars, 4 x (ptr + 3 int64), mask ptr + 3 int64, lse ptr
+    # 10 x 4-byte scalars, 4 x (ptr + 3 int64), mask ptr + 3 int64, lse ptr, sinks ptr, 4 x int32, 2 x ptr
     assert ctypes.sizeof(dtattn.Tensor4) == 32
-    assert ctypes.sizeof(dtattn.SdpaParams) == 40 + 4 * 32 + 8 + 24 + 8
-    assert dtattn.lib().dt_abi_version() == 1
+    assert ctypes.sizeof(dtattn.SdpaParams) == 40 + 4 * 32 + 8 + 24 + 8 + 8 + 16 + 16
+    assert dtattn.SdpaParams.sinks.offset == 208 and dtattn.SdpaParams.seq_offsets_q.offset == 232
+    assert dtattn.lib().dt_abi_version() == 2
 
 
 def test_status_strings(dtattn):
@@ -56,7 +57,8 @@ def test_bad_arguments_are_rejected(dtattn):
     lib = dtattn.lib()
     n = ctypes.c_size_t()
     assert lib.dt_sdpa_workspace_size(None, ctypes.byref(n)) == dtattn.DT_BAD_ARG
-    for over in (dict(Hkv=3), dict(B=0), dict(Sq=-1), dict(D=0), dict(dtype=7), dict(scale=float("nan"))):
+    for over in (dict(Hkv=3), dict(B=0), dict(Sq=-1), dict(D=0), dict(dtype=7), dict(scale=float("nan")),
+                 dict(sliding_window=-1), dict(seq_offsets_q=8), dict(seq_offsets_q=8, seq_offsets_k=8, n_seq=0)):
         p, keep = _params(dtattn, **over)
         assert lib.dt_sdpa_workspace_size(ctypes.byref(p), ctypes.byref(n)) == dtattn.DT_BAD_ARG, over
         assert lib.dt_sdpa_forward(ctypes.byref(p), None, 0, None) == dtattn.DT_BAD_ARG, over
