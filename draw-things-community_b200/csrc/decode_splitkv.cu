@@ -65,6 +65,9 @@ struct DecodeArgs {
   int64_t kn_sb, kn_ss, kn_sh, vn_sb, vn_ss, vn_sh, rot_sb, rot_ss, kc_sb, kc_ss, kc_sh, vc_sb, vc_ss, vc_sh;
   int Sq, Sk, Hq, Hkv, G, M;
   int stream_keys;  // cache rows streamed through the ring: Sk, or Sk - Tn with the step fusion
+  int unit_first;   // first 16-key unit that any row can see (sliding window), 0 otherwise
+  int window;       // sliding window W (0 = off): row i sees keys j > i + (Sk - Sq) - W
+  const void* sinks;  // [Hq] attention sinks, or null
   int Tn;           // new rows appended by the step fusion (<= 16), 0 otherwise
   int nsplit, units_per_split, total_units;
   float scale_log2;
@@ -99,6 +102,17 @@ __device__ __forceinline__ uint32_t cmul_pair(uint32_t x, uint32_t cs) {
                !std::is_same<T, __half>::value);
 }
 
+// Attention sink: one more score (natural-log domain logit `sink`) without a value row joins a finished row whose
+// running max is `m` (log2 domain), denominator `l` and un-normalised output `o`.
+__device__ __forceinline__ void sink_merge(float sink, float& m, float& l, float& o) {
+  const float sl = sink * kLog2e;
+  const float m2 = fmaxf(m, sl);
+  const float down = m == -INFINITY ? 0.f : fast_exp2(m - m2);
+  l = l * down + fast_exp2(sl - m2);
+  o *= down;
+  m = m2;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -118,7 +132,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   unsigned long long* dbg = a.dbg ? a.dbg + ((size_t)(b * gridDim.y + kvh) * gridDim.x + split) * 8 : nullptr;
   if (dbg && threadIdx.x == 0) dbg[0] = ptx::globaltimer_ns();
-  const int unit_begin = split * a.units_per_split;
+  const int unit_begin = a.unit_first + split * a.units_per_split;
   const int unit_end = min(a.total_units, unit_begin + a.units_per_split);
   const int n_units = max(0, unit_end - unit_begin);
   const int n_stages = (n_units + C::kUnitsPerStage - 1) / C::kUnitsPerStage;
@@ -190,6 +204,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int off = a.Sk - a.Sq;
   const int vis_lo = a.is_causal ? min(a.Sk - 1, r_lo / a.G + off) : a.Sk - 1;
   const int vis_hi = a.is_causal ? min(a.Sk - 1, r_hi / a.G + off) : a.Sk - 1;
+  // first visible key per row (sliding window)
+  const int lo_lo = a.window > 0 ? r_lo / a.G + off - a.window + 1 : 0;
+  const int lo_hi = a.window > 0 ? r_hi / a.G + off - a.window + 1 : 0;
 
   // one 16-key unit: scores, online softmax, P V.  kbase / vbase: swizzled K and V tiles in shared memory.
   // Keys beyond `last_key` are masked on top of the causal rule (rows past the streamed range are TMA zero fill).
@@ -217,8 +234,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         const int j = key0 + nt * 8 + cq + e;
         float s0 = sacc[nt][e] * a.scale_log2;
         float s1 = sacc[nt][2 + e] * a.scale_log2;
-        if (j > vl_lo) s0 = -INFINITY;
-        if (j > vl_hi) s1 = -INFINITY;
+        if (j > vl_lo || j < lo_lo) s0 = -INFINITY;
+        if (j > vl_hi || j < lo_hi) s1 = -INFINITY;
         sacc[nt][e] = s0;
         sacc[nt][2 + e] = s1;
         mx_lo = fmaxf(mx_lo, s0);
@@ -419,6 +436,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
     if (a.nsplit == 1) {
       const int sq = r / a.G, h = kvh * a.G + r % a.G;
+      if (a.sinks) sink_merge(to_float(reinterpret_cast<const T*>(a.sinks)[h]), mstar, lt, ot);
       o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
       if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
     } else {
@@ -468,6 +486,15 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         const float wgt = mstar == -INFINITY ? 0.f : fast_exp2(wbuf[sp * a.M + r] - mstar);
         wbuf[sp * a.M + r] = wgt;
         lt += wgt * lsm[sp * a.M + r];
+      }
+      if (a.sinks) {
+        // the sink is one more partial: weight 1 for it, every split's weight rescaled to the common max
+        const float sl = to_float(reinterpret_cast<const T*>(a.sinks)[kvh * a.G + r % a.G]) * kLog2e;
+        const float m2 = fmaxf(mstar, sl);
+        const float down = mstar == -INFINITY ? 0.f : fast_exp2(mstar - m2);
+        for (int sp = 0; sp < a.nsplit; ++sp) wbuf[sp * a.M + r] *= down;
+        lt = lt * down + fast_exp2(sl - m2);
+        mstar = m2;
       }
       rowinfo[2 * r] = mstar;
       rowinfo[2 * r + 1] = lt;
@@ -530,9 +557,16 @@ struct Plan {
 // ticket, combine), so use as few CTAs as keep every SM streaming: the largest power of two with
 // pairs * splits <= 2 CTAs per SM, and at least four 16-key units per split.  (Measured on B200: B=16
 // runs at 99% of the copy peak with 2 splits and at 57% with 37.)
+// first 16-key unit any row of the call can see: row 0's window bound
+int first_unit(const dt_sdpa_params& p) {
+  if (p.sliding_window <= 0) return 0;
+  const long long lo = (long long)(p.Sk - p.Sq) - p.sliding_window + 1;
+  return lo <= 0 ? 0 : (int)(lo / kUnitKeys);
+}
+
 Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
   Plan pl;
-  pl.total_units = (stream_keys + kUnitKeys - 1) / kUnitKeys;
+  pl.total_units = (stream_keys + kUnitKeys - 1) / kUnitKeys - min((stream_keys + kUnitKeys - 1) / kUnitKeys, first_unit(p));
   if (pl.total_units == 0) {  // empty cache (first step of a sequence): one CTA per pair, nothing streamed
     pl.nsplit = 1;
     pl.units_per_split = 0;
@@ -605,7 +639,11 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
     a.kc_sb = p.k.stride_b; a.kc_ss = p.k.stride_s; a.kc_sh = p.k.stride_h;
     a.vc_sb = p.v.stride_b; a.vc_ss = p.v.stride_s; a.vc_sh = p.v.stride_h;
   }
-  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
+  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split;
+  a.unit_first = min(first_unit(p), (a.stream_keys + kUnitKeys - 1) / kUnitKeys);
+  a.total_units = a.unit_first + pl.total_units;  // one past the last streamed unit
+  a.window = p.sliding_window;
+  a.sinks = p.sinks;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
   auto kern = decode_splitkv_kernel<T, D>;
@@ -624,7 +662,6 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
 
 bool decode_supported(const dt_sdpa_params& p) {
   if (p.seq_offsets_q) return false;  // variable-length batches: generic kernel
-  if (p.sinks || p.sliding_window > 0) return false;
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D != 64 && p.D != 128 && p.D != 256) return false;  // 256: the reference's Qwen3.5 configs (Qwen3_5.swift:59-82)
   if (p.mask) return false;
@@ -761,7 +798,11 @@ int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, c
   a.status = dev->status;
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
   a.stream_keys = p.Sk;
-  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split; a.total_units = pl.total_units;
+  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split;
+  a.unit_first = min(first_unit(p), (a.stream_keys + kUnitKeys - 1) / kUnitKeys);
+  a.total_units = a.unit_first + pl.total_units;  // one past the last streamed unit
+  a.window = p.sliding_window;
+  a.sinks = p.sinks;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
   auto kern = decode_splitkv_kernel<T, D>;

@@ -65,6 +65,8 @@ struct PrefillArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int is_causal;
+  int window;         // sliding window W (0 = off): row i sees keys j > i + (Sk - Sq) - W
+  const void* sinks;  // [Hq] attention sinks in the tensors' type, or null
   int options;  // bit 1: timeline probe of CTA 0 into dbg (bring-up only)
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
   // head-sharded mode: the same O tile is also stored into these views (other GPUs' output buffers, same
@@ -154,7 +156,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // Work items (batch, head, pair of query tiles), q-tile pair fastest so that CTAs running at the same
   // time share one head's K/V in L2.  The CTA is persistent: it takes items blockIdx.x, + gridDim.x, ...
   struct Item {
-    int b, h, kvh, q0, nkv;
+    int b, h, kvh, q0, nkv, j0;  // K/V blocks j0 .. j0 + nkv - 1
     bool two;
   };
   auto decode_item = [&](int item) {
@@ -173,7 +175,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int need = (int)((max(0LL, min((long long)a.Sk, lim)) + kBN - 1) / kBN);
       nkv = max(1, min(nkv, need));
     }
-    it.nkv = nkv;
+    it.j0 = 0;
+    if (a.window > 0) {  // blocks entirely below the first row's window are never visited
+      const long long lo = (long long)it.q0 + off - a.window + 1;
+      it.j0 = (int)min((long long)(nkv - 1), max(0LL, lo) / kBN);
+    }
+    it.nkv = nkv - it.j0;
     return it;
   };
 
@@ -230,7 +237,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int hf = 0; hf < C::kHalves; ++hf)
             ptx::tma_load_4d(base_ptr + C::kQBytes + slot * C::kTileBytes + hf * kHalfBytes, is_v ? &map_v : &map_k,
-                             &bars->kv_full[slot], hf * 64, w.kvh, j * kBN, w.b);
+                             &bars->kv_full[slot], hf * 64, w.kvh, (w.j0 + j) * kBN, w.b);
           ++ring_it;
           return true;
         };
@@ -319,7 +326,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int slot_k = slot, par_k = par;
             const bool more = j + 1 < w.nkv;
             if (more) advance();
-            const int valid = min(kBN, a.Sk - j * kBN);
+            const int valid = min(kBN, a.Sk - (w.j0 + j) * kBN);
             const int ksteps = (valid + 15) >> 4;
             const int k_mid = min(ksteps, 4);
             if (!ptx::mbar_wait(&bars->kv_full[slot_v], par_v, abort_flag) ||
@@ -387,6 +394,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (t == 1 && !w.two) continue;  // this item has no second tile: neither side touches tile 1's barriers
       const int row = w.q0 + t * kBM + row_in_tile;
       const long long vis = a.is_causal ? (long long)row + off : (long long)a.Sk;  // last visible key
+      const long long lo = a.window > 0 ? (long long)row + off - a.window + 1 : 0;  // first visible key
       float m_used = -INFINITY, l = 0.f;
 
       for (int j = 0; j < w.nkv; ++j) {
@@ -415,15 +423,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         first_dump = false;
 
-        const int key0 = j * kBN;
-        const bool need_mask = (key0 + kBN > a.Sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis);
+        const int key0 = (w.j0 + j) * kBN;
+        const bool need_mask = (key0 + kBN > a.Sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis) || (long long)key0 < lo;
         if (need_mask) {
           const long long lim = min((long long)a.Sk - 1, vis);  // keys <= lim visible
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if ((long long)(key0 + c * 32 + i) > lim) s[c][i] = 0xff800000u;  // -inf
+              if ((long long)(key0 + c * 32 + i) > lim || (long long)(key0 + c * 32 + i) < lo) s[c][i] = 0xff800000u;  // -inf
         }
         // chunks of 32 keys that lie entirely beyond Sk are skipped (short K/V such as 77 text tokens)
         const int nch = (min(kBN, a.Sk - key0) + 31) >> 5;
@@ -518,6 +526,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       oph ^= 1;
       if (probe) stamp(a, 16 * n_item + 10);
       ptx::tc_fence_after();
+      if (a.sinks && row < a.Sq) {
+        // attention sink: one more score without a value row joins the denominator (l and O are relative to m_used)
+        const float sl = to_float(reinterpret_cast<const T*>(a.sinks)[w.h]) * kLog2e;
+        if (m_used == -INFINITY) {
+          m_used = sl;
+          l = 1.f;
+        } else {
+          l += fast_exp2(sl - m_used);
+        }
+      }
       const float inv = l > 0.f ? 1.f / l : 0.f;
       // O goes out through shared memory and a TMA store per warp (32 rows x 64 columns): whole 128-byte
       // row pieces reach L2, instead of 16-byte pieces scattered over 32 rows per instruction.
@@ -611,6 +629,8 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
+  a.window = p.sliding_window;
+  a.sinks = p.sinks;
   a.options = g_options;
   if (n_extra < 0 || n_extra > kMaxExtraOutputs) return DT_BAD_ARG;
   a.n_extra = n_extra;
@@ -636,7 +656,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
 
 bool prefill_supported(const dt_sdpa_params& p) {
   if (p.seq_offsets_q) return false;  // variable-length batches: generic kernel
-  if (p.sinks || p.sliding_window > 0) return false;
+  if (p.sliding_window > 0 && p.Sq > p.Sk) return false;  // rows that may see no key: generic kernel
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)
   if (p.mask) return false;

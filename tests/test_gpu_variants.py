@@ -32,6 +32,8 @@ SINK_WINDOW = [
     (1, 4, 777, 8, 2, 64, torch.bfloat16, True, 300, True, False),      # 4 new tokens x group of 4
     (1, 300, 300, 4, 4, 128, torch.bfloat16, True, 128, True, True),    # same through the CUDA-core kernel
     (1, 20, 20, 2, 2, 40, torch.float32, True, 7, True, False),
+    (1, 1500, 1500, 4, 2, 128, torch.bfloat16, True, 512, True, False),  # leading K/V blocks skipped per query tile
+    (2, 700, 900, 4, 4, 64, torch.float16, True, 200, True, False),
 ]
 
 
@@ -47,6 +49,16 @@ def test_sinks_and_sliding_window(dtattn, case):
               flags=dtattn.DT_FLAG_FORCE_GENERIC if generic else 0)
     check(out, ref.float(), dtype, str(case))
     assert torch.allclose(lse.cpu(), lse_ref.float(), atol=2e-3, rtol=1e-3), "log-sum-exp"
+
+
+def test_variants_stay_on_the_fast_kernels(dtattn):
+    """Sinks and sliding window are handled inside the tensor-core and split-KV kernels, not by falling back."""
+    for shape, want in (((1, 1500, 1500, 4, 2, 128), "prefill_tcgen05"), ((1, 1, 4096, 32, 8, 128), "decode_splitkv")):
+        B, Sq, Sk, Hq, Hkv, D = shape
+        q, k, v = [t.to(DEV) for t in inputs(B, Sq, Sk, Hq, Hkv, D, torch.float16, 951)]
+        sinks = torch.zeros(Hq, dtype=torch.float16, device=DEV)
+        p = dtattn.make_params(q, k, v, torch.empty_like(q), D ** -0.5, True, sinks=sinks, sliding_window=100)
+        assert dtattn.kernel_name(p) == want
 
 
 def test_sink_dominates_row(dtattn):
