@@ -28,11 +28,22 @@ public final class ScaledDotProductAttention {
   let isCausal: Bool
   let hasAttentionMask: Bool
   let flags: GEMMFlag
+  let hasAttentionSinks: Bool
+  let slidingWindow: Int
+  let isVariableLength: Bool
+  let maxSequenceLength: (query: Int, keyValue: Int)?
 
+  /// Labels as at the reference's call sites, including hasAttentionSinks / slidingWindow
+  /// (DeepSeek4.swift:482-493) and isVariableLength / maxSequenceLength (Qwen3_5VL.swift:428-437).
   public init(
     scale: Float, isCausal: Bool = false, hasAttentionMask: Bool = false, flags: GEMMFlag = [],
-    multiHeadOutputProjectionFused: Bool = false, name: String = ""
+    multiHeadOutputProjectionFused: Bool = false, hasAttentionSinks: Bool = false, slidingWindow: Int = 0,
+    isVariableLength: Bool = false, maxSequenceLength: (query: Int, keyValue: Int)? = nil, name: String = ""
   ) {
+    self.hasAttentionSinks = hasAttentionSinks
+    self.slidingWindow = slidingWindow
+    self.isVariableLength = isVariableLength
+    self.maxSequenceLength = maxSequenceLength
     precondition(!multiHeadOutputProjectionFused, "fused output projection is not provided by libdtattn")
     precondition(!flags.contains(.Int8), "quantised attention is a Metal-only level")
     self.scale = scale
@@ -44,6 +55,7 @@ public final class ScaledDotProductAttention {
   /// out = softmax(scale * Q K^T [+ mask]) V on `stream`; traps on misuse like the reference's operator.
   public func callAsFunction(
     _ queries: DeviceView, _ keys: DeviceView, _ values: DeviceView, mask: DeviceView? = nil,
+    sinks: UnsafeRawPointer? = nil, sequenceOffsets: (query: UnsafePointer<Int32>, keyValue: UnsafePointer<Int32>, count: Int32)? = nil,
     out: DeviceView, workspace: UnsafeMutableRawPointer?, workspaceBytes: Int, stream: UnsafeMutableRawPointer?
   ) {
     precondition(hasAttentionMask == (mask != nil))
@@ -60,6 +72,13 @@ public final class ScaledDotProductAttention {
       p.mask_stride_b = m.shape.b > 1 ? m.strides.b : 0
       p.mask_stride_h = m.shape.s > 1 ? m.strides.s : 0
       p.mask_stride_q = m.strides.h
+    }
+    precondition(hasAttentionSinks == (sinks != nil) && isVariableLength == (sequenceOffsets != nil))
+    p.sinks = sinks
+    p.sliding_window = Int32(slidingWindow)
+    if let o = sequenceOffsets {
+      p.seq_offsets_q = o.query; p.seq_offsets_k = o.keyValue; p.n_seq = o.count
+      p.max_seq_q = Int32(maxSequenceLength?.query ?? Int(p.Sq)); p.max_seq_k = Int32(maxSequenceLength?.keyValue ?? Int(p.Sk))
     }
     let status = dt_sdpa_forward(&p, workspace, workspaceBytes, stream)
     precondition(status == DT_OK.rawValue, String(cString: dt_status_string(status)))
