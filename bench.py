@@ -207,6 +207,36 @@ def side_measurements(dtattn, device, peaks):
         torch.cuda.empty_cache()
     out.update(decode_step_measurements(dtattn, device))
     out.update(prologue_measurements(dtattn, device, peaks))
+    out.update(out_proj_measurements(dtattn, device, peaks))
+    return out
+
+
+def out_proj_measurements(dtattn, device, peaks):
+    """Attention with the output projection folded in (dt_sdpa_forward_projected) beside attention alone on the same
+    inputs: the difference is the time of the TMA + tcgen05 GEMM, reported against the bf16 GEMM peak."""
+    out = {}
+    for name, (B, S, H, D, C, dt) in {"sdxl_self_1280": (2, 4096, 20, 64, 1280, torch.float16),
+                                      "flux_joint_3072": (1, 4608, 24, 128, 3072, torch.bfloat16)}.items():
+        g = torch.Generator(device=device).manual_seed(17)
+        rnd = lambda *shape: torch.randn(*shape, generator=g, device=device, dtype=torch.float32).to(dt)
+        n_sets = 3
+        sets = [(rnd(B, S, H, D), rnd(B, S, H, D), rnd(B, S, H, D), torch.empty(B, S, H, D, device=device, dtype=dt),
+                 torch.empty(B, S, C, device=device, dtype=dt)) for _ in range(n_sets)]
+        w = (rnd(C, H * D) * (H * D) ** -0.5)
+        bias = rnd(C)
+        scale = D ** -0.5
+        plain = [(lambda s=s: dtattn.sdpa_forward(s[0], s[1], s[2], scale, out=s[3])) for s in sets]
+        fused = [(lambda s=s: dtattn.sdpa_forward_projected(s[0], s[1], s[2], scale, w, bias, out=s[4])) for s in sets]
+        ms_plain = time_graph(plain, reps=5)
+        ms_fused = time_graph(fused, reps=5)
+        gemm_ms = max(ms_fused - ms_plain, 1e-6)
+        gflop = 2.0 * B * S * H * D * C / 1e9
+        out["out_proj_" + name] = {"us_attention": round(ms_plain * 1e3, 1), "us_attention_plus_projection": round(ms_fused * 1e3, 1),
+                                   "us_projection": round(gemm_ms * 1e3, 1), "projection_gflop": round(gflop, 2),
+                                   "projection_tflops": round(gflop / gemm_ms, 1),
+                                   "frac_bf16_peak": round(gflop / gemm_ms / peaks["bf16_tflops"], 4)}
+        del sets, plain, fused
+        torch.cuda.empty_cache()
     return out
 
 
@@ -553,7 +583,7 @@ def main():
     ap.add_argument("--no-t1", action="store_true", help="skip the single-GPU run of the sharded workload")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
-    ap.add_argument("--only", default=None, choices=["prologue", "decode_step"],
+    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj"],
                     help="run one group of side measurements alone and print it (for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
@@ -571,7 +601,8 @@ def main():
     torch.cuda.set_device(device)
     if args.only:
         fn = {"prologue": lambda: prologue_measurements(dtattn, device, peaks),
-              "decode_step": lambda: decode_step_measurements(dtattn, device)}[args.only]
+              "decode_step": lambda: decode_step_measurements(dtattn, device),
+              "out_proj": lambda: out_proj_measurements(dtattn, device, peaks)}[args.only]
         print(json.dumps({"only": args.only, "also": fn()}))
         return
     if world > 1:

@@ -212,6 +212,73 @@ int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_b
   }
 }
 
+// ---- attention + output projection (multiHeadOutputProjectionFused) -------------------------------------
+
+// The attention output of the projected call lives in the workspace: p->o may be null.
+static dt_sdpa_params with_placeholder_o(const dt_sdpa_params* p) {
+  dt_sdpa_params t = *p;
+  t.o = t.q;
+  return t;
+}
+
+static int validate_proj(const dt_sdpa_params* p_in, const dt_out_proj* proj) {
+  if (!p_in) return DT_BAD_ARG;
+  const dt_sdpa_params t = with_placeholder_o(p_in);
+  const dt_sdpa_params* p = &t;
+  int st = validate(p);
+  if (st != DT_OK) return st;
+  if (!proj || !proj->weight || !proj->out.ptr || proj->C <= 0) return DT_BAD_ARG;
+  if (p->dtype != DT_F16 && p->dtype != DT_BF16) return DT_UNSUPPORTED;
+  if (p->seq_offsets_q) return DT_UNSUPPORTED;
+  const int64_t K = (int64_t)p->Hq * p->D;
+  if (K % 8 || proj->C % 8) return DT_UNSUPPORTED;  // 16-byte rows for TMA
+  auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  if (!al(proj->weight) || !al(proj->out.ptr) || proj->out.stride_b % 8 || proj->out.stride_s % 8) return DT_UNSUPPORTED;
+  if (proj->bias && reinterpret_cast<uintptr_t>(proj->bias) % 2) return DT_BAD_ARG;
+  return DT_OK;
+}
+
+static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+// Where the attention output starts inside the workspace: behind the attention kernel's own scratch, and never
+// inside the first 4 KB, which hold the split-KV ticket counters that every call must leave zeroed.
+static size_t proj_o_offset(size_t inner) { return align256(inner) < 4096 ? 4096 : align256(inner); }
+
+int dt_sdpa_projected_workspace_size(const dt_sdpa_params* p, const dt_out_proj* proj, size_t* bytes) {
+  int st = validate_proj(p, proj);
+  if (st != DT_OK) return st;
+  if (!bytes) return DT_BAD_ARG;
+  size_t inner = 0;
+  const dt_sdpa_params t = with_placeholder_o(p);
+  st = dt_sdpa_workspace_size(&t, &inner);
+  if (st != DT_OK) return st;
+  *bytes = proj_o_offset(inner) + align256((size_t)p->B * p->Sq * p->Hq * p->D * 2);
+  return DT_OK;
+}
+
+int dt_sdpa_forward_projected(const dt_sdpa_params* p, const dt_out_proj* proj, void* workspace, size_t workspace_bytes,
+                              void* cuda_stream) {
+  int st = validate_proj(p, proj);
+  if (st != DT_OK) return st;
+  size_t need = 0, inner = 0;
+  dt_sdpa_params q = with_placeholder_o(p);
+  dt_sdpa_projected_workspace_size(p, proj, &need);
+  dt_sdpa_workspace_size(&q, &inner);
+  if (!workspace || workspace_bytes < need) return DT_WORKSPACE;
+  // attention output, head-major rows [B, Sq, Hq*D], kept in the workspace: the GEMM reads it back from L2
+  const int64_t K = (int64_t)p->Hq * p->D;
+  q.o.ptr = static_cast<uint8_t*>(workspace) + proj_o_offset(inner);
+  q.o.stride_h = p->D;
+  q.o.stride_s = K;
+  q.o.stride_b = K * p->Sq;
+  st = dt_sdpa_forward(&q, workspace, proj_o_offset(inner), cuda_stream);
+  if (st != DT_OK) return st;
+  dt_tensor4 a_view{q.o.ptr, q.o.stride_b, q.o.stride_s, K};
+  dt_tensor4 out = proj->out;
+  out.stride_h = proj->C;
+  return launch_out_proj(a_view, p->B, p->Sq, (int)K, proj->weight, proj->bias, proj->C, out, p->dtype,
+                         (cudaStream_t)cuda_stream);
+}
+
 int dt_device_status(void* cuda_stream, int* code) {
   if (!code) return DT_BAD_ARG;
   unsigned int* w = device_status_word();

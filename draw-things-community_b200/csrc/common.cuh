@@ -42,6 +42,10 @@ bool prefill_supported(const dt_sdpa_params& p);
 // head-sharded mode) that receive a copy of every O tile.
 int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs = nullptr, int n_extra = 0);
 
+// C[B,S,N] = A[B,S,K] . W[N,K]^T + bias: the output projection behind the attention kernel (TMA + tcgen05 GEMM).
+int launch_out_proj(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
+                    const dt_tensor4& out, int dtype, cudaStream_t stream);
+
 // [world][rows][Hl][D] -> [B,Sq,world*Hl,D]
 int launch_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D,
                             int dtype, cudaStream_t stream);

@@ -1,0 +1,225 @@
+// The step immediately after the attention node when the reference builds it with
+// multiHeadOutputProjectionFused: true (Libraries/SwiftDiffusion/Sources/Models/UNet.swift:122-130, weights loaded
+// at UNet.swift:865-874): out[b, s, :] = concat_h(O[b, s, h, :]) . W^T + bias, i.e. the "unify heads" Dense folded
+// into the operator.  Here it is a TMA + tcgen05 GEMM that runs right behind the attention kernel on the same
+// stream, reading the attention output from the workspace while it is still in L2.
+//
+//   C[M, N] = A[M, K] . B[N, K]^T + bias[N]      A = attention output rows (K = Hq * D, contiguous),
+//                                                B = Dense weight, [out, in] row-major, both K-major operands
+//   CTA   = one 128 x 256 tile of C (N = 256 halves the A traffic per FLOP: the loop is bound by L2 -> shared
+//           memory bandwidth, not by the tensor pipe); 8 warps: TMA producer, MMA issuer, TMEM allocator, (idle), 4 epilogue warps.
+//   loop  = K in steps of 64 (one 128-byte swizzle atom): an A box of 128 rows and a B box of 256 rows land in a
+//           4-stage ring; one thread issues four tcgen05.mma (M128 N256 K16) per stage into a 256-column fp32 accumulator in
+//           TMEM and commits the stage back to the producer.
+//   out   = accumulator rows -> + bias -> 16-bit -> swizzled staging rows -> one TMA store per warp and half
+//           (clipped by the tensor map at the edges of M and N).
+// Every wait is bounded and reports through the device status word (code 6).
+#include "sm100_ptx.cuh"
+
+namespace dt {
+namespace {
+
+constexpr int kTile = 128;           // rows of A per tile (M)
+constexpr int kTileN = 256;          // rows of B per tile (N)
+constexpr int kKStep = 64;           // K elements per stage: 128 bytes
+constexpr int kStages = 4;
+constexpr int kBoxBytesP = kTile * 128;  // the A box: 128 rows x 128 bytes
+constexpr int kStageBytesP = kBoxBytesP + kTileN * 128;
+constexpr int kStagingBytes = 4 * 32 * 128;  // four epilogue warps x 32 rows x 128 bytes
+constexpr int kProjThreads = 256;
+constexpr int kProjSmem = kStages * kStageBytesP + kStagingBytes + 1024 + 256;
+
+struct ProjBarriers {
+  uint64_t full[kStages], empty[kStages], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct ProjArgs {
+  const void* bias;  // [N] or null
+  unsigned int* status;
+  int S, N, K, tiles_per_batch;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair_t(float a, float b) {
+  if constexpr (std::is_same<T, __half>::value) return ptx::cvt_pack_f16(a, b);
+  else return ptx::cvt_pack_bf16(a, b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kProjThreads)
+out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const ProjArgs a) {
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t staging = base + kStages * kStageBytesP;
+  ProjBarriers* bars = reinterpret_cast<ProjBarriers*>(base_ptr + kStages * kStageBytesP + kStagingBytes);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kTileN;
+  const int b = blockIdx.y / a.tiles_per_batch;
+  const int s0 = (blockIdx.y - b * a.tiles_per_batch) * kTile;
+  const int nk = (a.K + kKStep - 1) / kKStep;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&bars->full[i], 1);
+      ptx::mbar_init(&bars->empty[i], 1);
+    }
+    ptx::mbar_init(&bars->acc_full, 1);
+    bars->abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(&bars->tmem_base, kTileN);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_a);
+      ptx::prefetch_tensormap(&map_b);
+      ptx::prefetch_tensormap(&map_c);
+      for (int kb = 0; kb < nk; ++kb) {
+        const int st = kb % kStages, use = kb / kStages;
+        if (use > 0 && !ptx::mbar_wait(&bars->empty[st], (use - 1) & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 6u);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::mbar_arrive_expect_tx(&bars->full[st], (uint32_t)kStageBytesP);
+        uint8_t* dst = base_ptr + st * kStageBytesP;
+        ptx::tma_load_4d(dst, &map_a, &bars->full[st], kb * kKStep, 0, s0, b);
+        ptx::tma_load_4d(dst + kBoxBytesP, &map_b, &bars->full[st], kb * kKStep, 0, n0, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(kBf16, kTile, kTileN, 0, 0);
+      const uint64_t desc = ptx::make_smem_desc_sw128(0, 16, 1024);
+      bool ok = true;
+      for (int kb = 0; kb < nk; ++kb) {
+        const int st = kb % kStages;
+        if (!ptx::mbar_wait(&bars->full[st], (kb / kStages) & 1, abort_flag)) {
+          atomicCAS(a.status, 0u, 6u);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t sa = base + st * kStageBytesP, sb = sa + kBoxBytesP;
+        const uint64_t da = desc | (uint64_t)((sa & 0x3FFFFu) >> 4), db = desc | (uint64_t)((sb & 0x3FFFFu) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < kKStep / 16; ++kk)
+          ptx::mma_ss(tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+        ptx::tc_commit(&bars->empty[st]);  // the stage may be refilled once these MMAs have read it
+      }
+      if (ok) ptx::tc_commit(&bars->acc_full);
+    }
+  } else if (warp >= 4) {
+    // =========================== epilogue ===========================
+    const int ew = warp - 4;  // TMEM lanes 32*ew .. 32*ew + 31 = tile rows
+    if (__all_sync(0xffffffffu, ptx::mbar_wait(&bars->acc_full, 0, abort_flag))) {
+      ptx::tc_fence_after();
+      const uint32_t t_acc = tmem + ((uint32_t)(ew * 32) << 16);
+      const uint32_t my_stage = staging + (uint32_t)ew * (32 * 128);
+      const T* bias = reinterpret_cast<const T*>(a.bias);
+      const int row0 = s0 + ew * 32;
+#pragma unroll
+      for (int hf = 0; hf < kTileN / 64; ++hf) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          ptx::tmem_ld32(t_acc + hf * 64 + c * 32, acc);
+          ptx::tc_wait_ld();
+          const int col0 = n0 + hf * 64 + c * 32;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int col = col0 + v * 8 + i;
+              f[i] = __uint_as_float(acc[v * 8 + i]) + ((bias && col < a.N) ? to_float(bias[col]) : 0.f);
+            }
+            uint4 pk;
+            pk.x = pack_pair_t<T>(f[0], f[1]);
+            pk.y = pack_pair_t<T>(f[2], f[3]);
+            pk.z = pack_pair_t<T>(f[4], f[5]);
+            pk.w = pack_pair_t<T>(f[6], f[7]);
+            // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
+            const uint32_t q = (uint32_t)(c * 4 + v);
+            const uint32_t addr = my_stage + (uint32_t)lane * 128 + ((q ^ ((uint32_t)lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                         : "memory");
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < a.S && n0 + hf * 64 < a.N) {
+          ptx::tma_store_4d(&map_c, my_stage, n0 + hf * 64, 0, row0, b);
+          ptx::bulk_commit_group();
+          ptx::bulk_wait_read_all();  // the staging rows are rewritten for the second half
+        }
+        __syncwarp();
+      }
+      if (lane == 0) ptx::bulk_wait_all();
+    } else {
+      atomicCAS(a.status, 0u, 6u);
+    }
+  }
+
+  // =========================== teardown ===========================
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTileN);
+  }
+}
+
+template <typename T>
+int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
+                  const dt_tensor4& out, int dtype, cudaStream_t stream) {
+  CUtensorMap ma, mb, mc;
+  dt_tensor4 w_view{const_cast<void*>(weight), (int64_t)N * K, (int64_t)K, (int64_t)K};
+  if (!make_bshd_tensor_map(&ma, a_view, B, S, 1, K, dtype, kTile)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mb, w_view, 1, N, 1, K, dtype, kTileN)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mc, out, B, S, 1, N, dtype, 32)) return DT_UNSUPPORTED;
+  ProjArgs a{};
+  a.bias = bias;
+  a.status = device_status_word();
+  if (!a.status) return DT_CUDA;
+  a.S = S; a.N = N; a.K = K;
+  a.tiles_per_batch = (S + kTile - 1) / kTile;
+  auto kern = out_proj_kernel<T>;
+  DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kProjSmem));
+  const int64_t gy = (int64_t)a.tiles_per_batch * B;
+  if (gy > 65535) return DT_UNSUPPORTED;
+  dim3 grid((N + kTileN - 1) / kTileN, (unsigned)gy);
+  kern<<<grid, kProjThreads, kProjSmem, stream>>>(ma, mb, mc, a);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace
+
+// a_view: [B, S, 1, K] rows of the attention output; out: [B, S, 1, N]
+int launch_out_proj(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
+                    const dt_tensor4& out, int dtype, cudaStream_t stream) {
+  if (dtype == DT_F16) return launch_proj_t<__half>(a_view, B, S, K, weight, bias, N, out, dtype, stream);
+  if (dtype == DT_BF16) return launch_proj_t<__nv_bfloat16>(a_view, B, S, K, weight, bias, N, out, dtype, stream);
+  return DT_UNSUPPORTED;
+}
+
+}  // namespace dt

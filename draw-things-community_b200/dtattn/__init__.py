@@ -61,6 +61,10 @@ class QkPrologueParams(ctypes.Structure):
                 ("rotary_stride_h", ctypes.c_int64), ("post_scale", ctypes.c_float)]
 
 
+class OutProj(ctypes.Structure):
+    _fields_ = [("weight", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("C", ctypes.c_int32), ("out", Tensor4)]
+
+
 class DtError(RuntimeError):
     def __init__(self, status, what):
         self.status = status
@@ -85,6 +89,9 @@ SYMBOLS = [
     ("dt_sdpa_decode_step_workspace_size", ctypes.c_int, [_P(DecodeStepParams), _P(ctypes.c_size_t)]),
     ("dt_sdpa_decode_step", ctypes.c_int, [_P(DecodeStepParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_sdpa_decode_noalloc", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p]),
+    ("dt_sdpa_projected_workspace_size", ctypes.c_int, [_P(SdpaParams), _P(OutProj), _P(ctypes.c_size_t)]),
+    ("dt_sdpa_forward_projected", ctypes.c_int,
+     [_P(SdpaParams), _P(OutProj), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_qk_prologue", ctypes.c_int, [_P(QkPrologueParams), _P(QkPrologueParams), ctypes.c_void_p]),
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
@@ -306,6 +313,35 @@ def qk_prologue(q, k=None, *, q_out=None, k_out=None, q_weight=None, k_weight=No
     return q_out, k_out
 
 
+def sdpa_forward_projected(q, k, v, scale, weight, bias=None, is_causal=False, out=None, workspace=None, stream=None):
+    """Attention followed by the "unify heads" Dense in one call (multiHeadOutputProjectionFused,
+    UNet.swift:122-130): returns [B, Sq, C] = concat_heads(attention) @ weight.T + bias, weight [C, Hq*D]."""
+    assert q.is_cuda, "the projected call takes device tensors"
+    B, Sq, Hq, D = q.shape
+    C = weight.shape[0]
+    assert weight.dtype == q.dtype and weight.is_contiguous() and weight.shape[1] == Hq * D
+    if out is None:
+        out = torch.empty((B, Sq, C), dtype=q.dtype, device=q.device)
+    assert out.stride(2) == 1
+    p = make_params(q, k, v, q, scale, is_causal)  # o is a placeholder: the attention output stays in the workspace
+    pr = OutProj()
+    pr.weight = weight.data_ptr()
+    if bias is not None:
+        assert bias.dtype == q.dtype and bias.is_contiguous() and bias.numel() == C
+        pr.bias = bias.data_ptr()
+    pr.C = C
+    pr.out = Tensor4(out.data_ptr(), out.stride(0), out.stride(1), C)
+    need = ctypes.c_size_t(0)
+    _check(lib().dt_sdpa_projected_workspace_size(ctypes.byref(p), ctypes.byref(pr), ctypes.byref(need)),
+           "dt_sdpa_projected_workspace_size")
+    s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    ws = workspace if workspace is not None else _default_workspace(q.device)
+    ptr, nbytes = ws.ensure(need.value, s)
+    _check(lib().dt_sdpa_forward_projected(ctypes.byref(p), ctypes.byref(pr), ctypes.c_void_p(ptr), nbytes,
+                                           ctypes.c_void_p(s)), "dt_sdpa_forward_projected")
+    return out
+
+
 _workspaces = {}
 
 
@@ -341,8 +377,8 @@ class ScaledDotProductAttention:
       is_variable_length    packed rows; two more inputs hold the int32 sequence offsets (n_seq + 1 entries each);
                             max_sequence_length = (query, keyValue) bounds of one sequence
       multi_head_output_projection_fused
-                            the reference fuses the output Dense into the op (UNet.swift:122-130); not built
-                            here -> the constructor raises, as the reference would on an unsupported back end
+                            the output Dense is part of the op (UNet.swift:122-130): the result is
+                            [B, Sq, C] = concat_heads(attention) @ weight.T + bias
     Like the reference, misuse is a hard error (the reference traps with precondition/fatalError).
     """
 
@@ -355,8 +391,10 @@ class ScaledDotProductAttention:
         self.sliding_window = int(sliding_window or 0)
         self.is_variable_length = bool(is_variable_length)
         self.max_sequence_length = max_sequence_length
-        if multi_head_output_projection_fused:
-            raise NotImplementedError("multiHeadOutputProjectionFused is outside this library's scope")
+        # multiHeadOutputProjectionFused: the operator owns the unify-heads Dense; its parameters are set with
+        # set_output_projection (the reference copies them into the model's .weight / .bias, UNet.swift:865-874)
+        self.multi_head_output_projection_fused = bool(multi_head_output_projection_fused)
+        self.weight = self.bias = None
         self.scale = float(scale)
         self.is_causal = bool(is_causal)
         self.has_attention_mask = bool(has_attention_mask)
@@ -367,6 +405,9 @@ class ScaledDotProductAttention:
         self.flags = f
         if GEMMFlag.Int8 in f:
             raise NotImplementedError("quantised attention ([.Int8, .Float16]) is never selected off Metal")
+
+    def set_output_projection(self, weight, bias=None):
+        self.weight, self.bias = weight, bias
 
     def __call__(self, queries, keys, values, *extra, mask=None, out=None, lse=None):
         """Extra positional inputs follow the reference's order: the mask (hasAttentionMask), or the sinks tensor
@@ -389,6 +430,12 @@ class ScaledDotProductAttention:
         if self.has_attention_mask != (mask is not None):
             raise ValueError("hasAttentionMask and the number of inputs disagree")
         abi_flags = DT_FLAG_FP16_ACCUM_HINT if GEMMFlag.Float16 in self.flags else 0
+        if self.multi_head_output_projection_fused:
+            if self.weight is None:
+                raise ValueError("multiHeadOutputProjectionFused: set_output_projection(weight, bias) first")
+            if mask is not None or sinks is not None or offs_q is not None or self.sliding_window or lse is not None:
+                raise NotImplementedError("the fused output projection takes the plain operator only")
+            return sdpa_forward_projected(queries, keys, values, self.scale, self.weight, self.bias, self.is_causal, out=out)
         mq, mk = self.max_sequence_length if self.max_sequence_length else (0, 0)
         return sdpa_forward(queries, keys, values, self.scale, self.is_causal, mask, out=out, lse=lse, flags=abi_flags,
                             sinks=sinks, sliding_window=self.sliding_window, seq_offsets_q=offs_q, seq_offsets_k=offs_k,

@@ -59,9 +59,8 @@ class ScaledDotProductAttention {
   ScaledDotProductAttention(float scale, bool isCausal = false, bool hasAttentionMask = false,
                             unsigned flags = kNone, bool multiHeadOutputProjectionFused = false,
                             std::string name = "")
-      : scale_(scale), causal_(isCausal), has_mask_(hasAttentionMask), flags_(flags), name_(std::move(name)) {
-    if (multiHeadOutputProjectionFused)
-      throw Error(DT_UNSUPPORTED, "multiHeadOutputProjectionFused (UNet.swift:122-130) is outside this library");
+      : scale_(scale), causal_(isCausal), has_mask_(hasAttentionMask), flags_(flags), name_(std::move(name)),
+        fused_projection_(multiHeadOutputProjectionFused) {
     if (flags & kInt8) throw Error(DT_UNSUPPORTED, "quantised attention is only selected on Metal in the reference");
   }
 
@@ -86,16 +85,46 @@ class ScaledDotProductAttention {
     return *this;
   }
 
+  // multiHeadOutputProjectionFused (UNet.swift:122-130): the operator owns the unify-heads Dense.  Its
+  // parameters ([C, Hq*D] weight, [C] bias or null, device memory) are set here, as the reference copies them
+  // into the model at UNet.swift:865-874; out of operator() is then [B, Sq, 1, C].
+  ScaledDotProductAttention& withOutputProjection(const void* weight, const void* bias, int C) {
+    proj_weight_ = weight; proj_bias_ = bias; proj_c_ = C;
+    return *this;
+  }
+  size_t projectedWorkspaceSize(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out) const {
+    dt_sdpa_params p = params(q, k, v, q, nullptr);
+    dt_out_proj pr = projection(out);
+    size_t n = 0;
+    int st = dt_sdpa_projected_workspace_size(&p, &pr, &n);
+    if (st != DT_OK) throw Error(st, "dt_sdpa_projected_workspace_size");
+    return n;
+  }
+
   // op(queries, keys, values[, mask]) -> out, enqueued on `stream`.
   void operator()(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& out,
                   void* workspace, size_t workspace_bytes, void* stream, const TensorView* mask = nullptr) const {
     if (has_mask_ != (mask != nullptr)) throw Error(DT_BAD_ARG, "hasAttentionMask and the inputs disagree");
+    if (fused_projection_) {
+      if (!proj_weight_) throw Error(DT_BAD_ARG, "multiHeadOutputProjectionFused: withOutputProjection() first");
+      dt_sdpa_params pp = params(q, k, v, q, mask);
+      dt_out_proj pr = projection(out);
+      int stp = dt_sdpa_forward_projected(&pp, &pr, workspace, workspace_bytes, stream);
+      if (stp != DT_OK) throw Error(stp, "dt_sdpa_forward_projected(" + name_ + ")");
+      return;
+    }
     dt_sdpa_params p = params(q, k, v, out, mask);
     int st = dt_sdpa_forward(&p, workspace, workspace_bytes, stream);
     if (st != DT_OK) throw Error(st, "dt_sdpa_forward(" + name_ + ")");
   }
 
  private:
+  dt_out_proj projection(const TensorView& out) const {
+    dt_out_proj pr{};
+    pr.weight = proj_weight_; pr.bias = proj_bias_; pr.C = proj_c_;
+    pr.out = out.abi();
+    return pr;
+  }
   dt_sdpa_params params(const TensorView& q, const TensorView& k, const TensorView& v, const TensorView& o,
                         const TensorView* mask) const {
     if (q.dtype != k.dtype || q.dtype != v.dtype || q.dtype != o.dtype) throw Error(DT_BAD_ARG, "dtype mismatch");
@@ -120,6 +149,9 @@ class ScaledDotProductAttention {
     return p;
   }
   float scale_;
+  const void* proj_weight_ = nullptr;
+  const void* proj_bias_ = nullptr;
+  int proj_c_ = 0;
   const void* sinks_ = nullptr;
   int window_ = 0;
   const int32_t* off_q_ = nullptr;
@@ -128,6 +160,7 @@ class ScaledDotProductAttention {
   bool causal_, has_mask_;
   unsigned flags_;
   std::string name_;
+  bool fused_projection_ = false;
 };
 
 }  // namespace dt

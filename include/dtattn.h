@@ -152,6 +152,25 @@ int dt_sdpa_decode_step_workspace_size(const dt_decode_step_params* s, size_t* b
 int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspace, size_t workspace_bytes,
                         void* cuda_stream);
 
+/* Attention with the output projection folded in ---------------------------------------------------------
+ * ScaledDotProductAttention(..., multiHeadOutputProjectionFused: true) (Libraries/SwiftDiffusion/Sources/Models/
+ * UNet.swift:122-130; the operator then owns the "unify heads" Dense whose weight and bias are loaded at
+ * UNet.swift:865-874): out[b, s, :] = concat_h(O[b, s, h, :]) . weight^T + bias.  weight is [C, Hq*D] row-major
+ * (a Dense weight: outputs x inputs) and bias [C] (or NULL), both in the tensors' 16-bit dtype; out is a
+ * [B, Sq, C] view given as dt_tensor4 (stride_b, stride_s; stride_h unused).  p->o is not written: the attention
+ * output stays in the workspace (rounded to the 16-bit dtype, as the unfused graph's tensor would be) and the
+ * projection, a TMA + tcgen05 GEMM on the same stream, reads it from there.  Hq*D and C must be multiples of 8.
+ */
+typedef struct {
+  const void* weight;
+  const void* bias;
+  int32_t C;
+  dt_tensor4 out;
+} dt_out_proj;
+int dt_sdpa_projected_workspace_size(const dt_sdpa_params* p, const dt_out_proj* proj, size_t* bytes);
+int dt_sdpa_forward_projected(const dt_sdpa_params* p, const dt_out_proj* proj, void* workspace,
+                              size_t workspace_bytes, void* cuda_stream);
+
 /* Q/K prologue -----------------------------------------------------------------------------------------
  * The steps the reference runs on queries and keys immediately before the attention node, as one pass over HBM
  * instead of one graph node (a full read and write of the tensor) per step:

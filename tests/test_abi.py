@@ -98,8 +98,9 @@ def test_kernel_selection(dtattn):
 def test_operator_mirror_validates_like_the_reference(dtattn):
     op = dtattn.ScaledDotProductAttention(scale=0.125, is_causal=True, flags=[dtattn.GEMMFlag.Float16])
     assert op.scale == 0.125 and op.is_causal
-    with pytest.raises(NotImplementedError):
-        dtattn.ScaledDotProductAttention(scale=1.0, multi_head_output_projection_fused=True)
+    fused = dtattn.ScaledDotProductAttention(scale=1.0, multi_head_output_projection_fused=True)
+    with pytest.raises(ValueError):  # the operator owns the unify-heads Dense: its parameters must be set first
+        fused(torch.zeros(1, 4, 2, 64, dtype=torch.float16), None, None)
     with pytest.raises(NotImplementedError):
         dtattn.ScaledDotProductAttention(scale=1.0, flags=[dtattn.GEMMFlag.Int8, dtattn.GEMMFlag.Float16])
     q = torch.zeros(1, 4, 2, 64, dtype=torch.float16)

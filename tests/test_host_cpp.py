@@ -14,8 +14,13 @@ int main() {
   using namespace dt;
   int fails = 0;
   ScaledDotProductAttention op(0.125f, /*isCausal=*/true, /*hasAttentionMask=*/false, kFloat16);
-  try { ScaledDotProductAttention bad(1.f, false, false, kNone, /*multiHeadOutputProjectionFused=*/true); ++fails; }
-  catch (const Error& e) { if (e.status != DT_UNSUPPORTED) ++fails; }
+  ScaledDotProductAttention fused(1.f, false, false, kNone, /*multiHeadOutputProjectionFused=*/true);
+  alignas(16) static char qb[1 << 12];
+  TensorView fq = TensorView::contiguous(qb, 1, 1, 4, 64, DT_F16);
+  try { fused(fq, fq, fq, fq, nullptr, 0, nullptr); ++fails; }  // the Dense parameters were never set
+  catch (const Error& e) { if (e.status != DT_BAD_ARG) ++fails; }
+  fused.withOutputProjection(qb, nullptr, 64);
+  if (fused.projectedWorkspaceSize(fq, fq, fq, fq) < 4 * 64 * 2) ++fails;  // room for the attention output
   try { ScaledDotProductAttention bad(1.f, false, false, kInt8 | kFloat16); ++fails; }
   catch (const Error& e) { if (e.status != DT_UNSUPPORTED) ++fails; }
   alignas(16) static char buf[1 << 16];
