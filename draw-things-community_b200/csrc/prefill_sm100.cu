@@ -69,6 +69,10 @@ struct PrefillArgs {
   const void* sinks;  // [Hq] attention sinks in the tensors' type, or null
   int options;  // bit 1: timeline probe of CTA 0 into dbg (bring-up only)
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
+  // variable-length batch (both null otherwise): packed rows, sequence s owns query rows [off_q[s], off_q[s+1])
+  // and key rows [off_k[s], off_k[s+1]); the item's batch index is then the sequence
+  const int32_t* off_q;
+  const int32_t* off_k;
   // head-sharded mode: the same O tile is also stored into these views (other GPUs' output buffers, same
   // strides as o) with ordinary 16-byte stores
   void* extra_o[kMaxExtraOutputs];
@@ -150,13 +154,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int off = a.Sk - a.Sq;  // causal: key j visible to query i iff j <= i + off
   const int G = a.Hq / a.Hkv;
 
   // Work items (batch, head, pair of query tiles), q-tile pair fastest so that CTAs running at the same
   // time share one head's K/V in L2.  The CTA is persistent: it takes items blockIdx.x, + gridDim.x, ...
   struct Item {
-    int b, h, kvh, q0, nkv, j0;  // K/V blocks j0 .. j0 + nkv - 1
+    int b, h, kvh, q0, nkv, j0;  // K/V blocks j0 .. j0 + nkv - 1; nkv == 0: nothing to do (q0 beyond the sequence)
+    int sq, sk, off;             // rows of this (batch item | sequence); causal: key j visible to query i iff j <= i + off
+    int qrow, krow;              // first packed row of the sequence (0 unless variable-length)
     bool two;
   };
   auto decode_item = [&](int item) {
@@ -167,17 +172,32 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     it.b = bh / a.Hq;
     it.kvh = it.h / G;
     it.q0 = qt * (2 * kBM);
-    it.two = it.q0 + kBM < a.Sq;
-    int nkv = (a.Sk + kBN - 1) / kBN;
+    it.sq = a.Sq;
+    it.sk = a.Sk;
+    it.qrow = it.krow = 0;
+    if (a.off_q) {
+      it.qrow = a.off_q[it.b];
+      it.krow = a.off_k[it.b];
+      it.sq = a.off_q[it.b + 1] - it.qrow;
+      it.sk = a.off_k[it.b + 1] - it.krow;
+      it.b = 0;
+    }
+    it.off = it.sk - it.sq;
+    it.two = it.q0 + kBM < it.sq;
+    it.j0 = 0;
+    if (it.q0 >= it.sq) {  // only with variable lengths: this sequence is shorter than the longest one
+      it.nkv = 0;
+      return it;
+    }
+    int nkv = max(1, (it.sk + kBN - 1) / kBN);  // a sequence without keys still runs one (fully masked) block
     if (a.is_causal) {
-      const int last_row = min(a.Sq, it.q0 + 2 * kBM) - 1;
-      const long long lim = (long long)last_row + off + 1;  // keys [0, lim) can be visible
-      const int need = (int)((max(0LL, min((long long)a.Sk, lim)) + kBN - 1) / kBN);
+      const int last_row = min(it.sq, it.q0 + 2 * kBM) - 1;
+      const long long lim = (long long)last_row + it.off + 1;  // keys [0, lim) can be visible
+      const int need = (int)((max(0LL, min((long long)it.sk, lim)) + kBN - 1) / kBN);
       nkv = max(1, min(nkv, need));
     }
-    it.j0 = 0;
     if (a.window > 0) {  // blocks entirely below the first row's window are never visited
-      const long long lo = (long long)it.q0 + off - a.window + 1;
+      const long long lo = (long long)it.q0 + it.off - a.window + 1;
       it.j0 = (int)min((long long)(nkv - 1), max(0LL, lo) / kBN);
     }
     it.nkv = nkv - it.j0;
@@ -237,12 +257,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int hf = 0; hf < C::kHalves; ++hf)
             ptx::tma_load_4d(base_ptr + C::kQBytes + slot * C::kTileBytes + hf * kHalfBytes, is_v ? &map_v : &map_k,
-                             &bars->kv_full[slot], hf * 64, w.kvh, (w.j0 + j) * kBN, w.b);
+                             &bars->kv_full[slot], hf * 64, w.kvh, w.krow + (w.j0 + j) * kBN, w.b);
           ++ring_it;
           return true;
         };
         for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
+          if (w.nkv == 0) {  // empty item: not counted (the loop header increments n_item)
+            --n_item;
+            continue;
+          }
           // The Q tiles of the NEXT item are pulled into L2 now: their rows are 256-byte pieces a whole
           // token stride apart (slow to gather from HBM), and the real load sits on the critical path
           // between two items.
@@ -250,7 +274,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const Item nx = decode_item(item + gridDim.x);
             for (int t = 0; t < (nx.two ? 2 : 1); ++t)
 #pragma unroll
-              for (int hf = 0; hf < C::kHalves; ++hf) ptx::tma_prefetch_l2_4d(&map_q, hf * 64, nx.h, nx.q0 + t * kBM, nx.b);
+              for (int hf = 0; hf < C::kHalves; ++hf)
+                if (nx.nkv > 0) ptx::tma_prefetch_l2_4d(&map_q, hf * 64, nx.h, nx.qrow + nx.q0 + t * kBM, nx.b);
           }
           // first K/V block of this item may be fetched while the previous item still owns the Q buffers
           ok = load_kv(w, 0, false) && load_kv(w, 0, true);
@@ -267,7 +292,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
               ptx::tma_load_4d(base_ptr + (qb * 2 + t) * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full[qb], hf * 64,
-                               w.h, w.q0 + t * kBM, w.b);
+                               w.h, w.qrow + w.q0 + t * kBM, w.b);
           for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
         }
       }
@@ -297,6 +322,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         };
         for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
+          if (w.nkv == 0) {  // empty item: not counted (the loop header increments n_item)
+            --n_item;
+            continue;
+          }
           const int ntile = w.two ? 2 : 1;
           const int qb = n_item % C::kQBufs;
           const uint64_t qd0 = qd_base + (uint64_t)(qb * 2 * (C::kTileBytes >> 4));
@@ -326,7 +355,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int slot_k = slot, par_k = par;
             const bool more = j + 1 < w.nkv;
             if (more) advance();
-            const int valid = min(kBN, a.Sk - (w.j0 + j) * kBN);
+            const int valid = max(16, min(kBN, w.sk - (w.j0 + j) * kBN));  // at least one 16-key step (P = 0 there if sk = 0)
             const int ksteps = (valid + 15) >> 4;
             const int k_mid = min(ksteps, 4);
             if (!ptx::mbar_wait(&bars->kv_full[slot_v], par_v, abort_flag) ||
@@ -391,10 +420,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
       const Item w = decode_item(item);
+      if (w.nkv == 0) continue;
       if (t == 1 && !w.two) continue;  // this item has no second tile: neither side touches tile 1's barriers
       const int row = w.q0 + t * kBM + row_in_tile;
-      const long long vis = a.is_causal ? (long long)row + off : (long long)a.Sk;  // last visible key
-      const long long lo = a.window > 0 ? (long long)row + off - a.window + 1 : 0;  // first visible key
+      const long long vis = a.is_causal ? (long long)row + w.off : (long long)w.sk;  // last visible key
+      const long long lo = a.window > 0 ? (long long)row + w.off - a.window + 1 : 0;  // first visible key
       float m_used = -INFINITY, l = 0.f;
 
       for (int j = 0; j < w.nkv; ++j) {
@@ -424,9 +454,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         first_dump = false;
 
         const int key0 = (w.j0 + j) * kBN;
-        const bool need_mask = (key0 + kBN > a.Sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis) || (long long)key0 < lo;
+        const bool need_mask = (key0 + kBN > w.sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis) || (long long)key0 < lo;
         if (need_mask) {
-          const long long lim = min((long long)a.Sk - 1, vis);  // keys <= lim visible
+          const long long lim = min((long long)w.sk - 1, vis);  // keys <= lim visible
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -434,7 +464,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               if ((long long)(key0 + c * 32 + i) > lim || (long long)(key0 + c * 32 + i) < lo) s[c][i] = 0xff800000u;  // -inf
         }
         // chunks of 32 keys that lie entirely beyond Sk are skipped (short K/V such as 77 text tokens)
-        const int nch = (min(kBN, a.Sk - key0) + 31) >> 5;
+        const int nch = max(1, (min(kBN, w.sk - key0) + 31) >> 5);  // at least the chunk the MMA warp always reads
         // row max: four independent chains of 3-input max (one per 32-column chunk)
         float mxc[4];
 #pragma unroll
@@ -526,7 +556,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       oph ^= 1;
       if (probe) stamp(a, 16 * n_item + 10);
       ptx::tc_fence_after();
-      if (a.sinks && row < a.Sq) {
+      if (a.sinks && row < w.sq) {
         // attention sink: one more score without a value row joins the denominator (l and O are relative to m_used)
         const float sl = to_float(reinterpret_cast<const T*>(a.sinks)[w.h]) * kLog2e;
         if (m_used == -INFINITY) {
@@ -536,12 +566,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           l += fast_exp2(sl - m_used);
         }
       }
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // a row that never saw a visible key (m_used still -inf) yields zeros, whatever the masked entries summed to
+      const float inv = (l > 0.f && m_used != -INFINITY) ? 1.f / l : 0.f;
       // O goes out through shared memory and a TMA store per warp (32 rows x 64 columns): whole 128-byte
       // row pieces reach L2, instead of 16-byte pieces scattered over 32 rows per instruction.
       {
         const uint32_t my_stage = stage_smem + (uint32_t)(warp - 4) * (32 * 128);
         const int wrow0 = w.q0 + t * kBM + ((warp & 3) << 5);
+        // The tensor map clips at the end of the tensor, not at the end of a packed sequence: with variable
+        // lengths a warp whose 32 rows reach past its sequence stores row by row instead.
+        const bool tma_ok = a.off_q ? (wrow0 + 32 <= w.sq) : (wrow0 < w.sq);
+        const bool guarded_main = a.off_q != nullptr && wrow0 < w.sq && !tma_ok;
 #pragma unroll
         for (int hf = 0; hf < D / 64; ++hf) {
 #pragma unroll
@@ -565,32 +600,34 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && wrow0 < a.Sq) {
-            ptx::tma_store_4d(&map_o, my_stage, hf * 64, w.h, wrow0, w.b);
+          if (lane == 0 && tma_ok) {
+            ptx::tma_store_4d(&map_o, my_stage, hf * 64, w.h, w.qrow + wrow0, w.b);
             ptx::bulk_commit_group();
           }
-          if (a.n_extra > 0) {
-            // copies of the tile for the other GPUs: 8 lanes write one row's 128 bytes, 4 rows per instruction
-            const int64_t row_off = (int64_t)w.b * a.o_sb + (int64_t)w.h * a.o_sh + hf * 64;
+          if (a.n_extra > 0 || guarded_main) {
+            // copies of the tile for the other GPUs (and the row-guarded store of a sequence's last rows):
+            // 8 lanes write one row's 128 bytes, 4 rows per instruction
+            const int64_t row_off = (int64_t)w.b * a.o_sb + (int64_t)w.h * a.o_sh + hf * 64 + (int64_t)w.qrow * a.o_ss;
 #pragma unroll 1
-            for (int e = 0; e < a.n_extra; ++e) {
-              T* dst = reinterpret_cast<T*>(a.extra_o[e]) + row_off;
+            for (int e = guarded_main ? -1 : 0; e < a.n_extra; ++e) {
+              T* dst = reinterpret_cast<T*>(e < 0 ? a.o : a.extra_o[e]) + row_off;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int r = i * 4 + (lane >> 3), ch = lane & 7;
                 uint4 val;
                 const uint32_t addr = my_stage + (uint32_t)r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
-                if (wrow0 + r < a.Sq && hf * 64 + ch * 8 < a.d_real) *reinterpret_cast<uint4*>(dst + (int64_t)(wrow0 + r) * a.o_ss + ch * 8) = val;
+                if (wrow0 + r < w.sq && hf * 64 + ch * 8 < a.d_real) *reinterpret_cast<uint4*>(dst + (int64_t)(wrow0 + r) * a.o_ss + ch * 8) = val;
               }
             }
           }
-          if (lane == 0 && wrow0 < a.Sq) ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
+          if (lane == 0 && tma_ok) ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
           __syncwarp();
         }
       }
-      if (a.lse && row < a.Sq)
-        a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m_used * kLn2 + logf(l) : -INFINITY;
+      if (a.lse && row < w.sq)
+        a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + w.qrow + row] =
+            (l > 0.f && m_used != -INFINITY) ? m_used * kLn2 + logf(l) : -INFINITY;
       // the next item's first P*V overwrites O: order this thread's TMEM reads before its later arrivals
       ptx::tc_fence_before();
       if (probe) stamp(a, 16 * n_item + 11);
@@ -636,8 +673,11 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   a.n_extra = n_extra;
   a.d_real = p.D;
   for (int i = 0; i < n_extra; ++i) a.extra_o[i] = extra[i];
-  a.n_qpairs = (p.Sq + 2 * kBM - 1) / (2 * kBM);
-  a.n_items = a.n_qpairs * p.Hq * p.B;
+  const bool varlen = p.seq_offsets_q != nullptr;
+  a.off_q = p.seq_offsets_q;
+  a.off_k = p.seq_offsets_k;
+  a.n_qpairs = ((varlen ? p.max_seq_q : p.Sq) + 2 * kBM - 1) / (2 * kBM);
+  a.n_items = a.n_qpairs * p.Hq * (varlen ? p.n_seq : p.B);
   auto kern = prefill_tcgen05_kernel<T, D>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   static int n_sm = 0;
@@ -655,7 +695,9 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
 }  // namespace
 
 bool prefill_supported(const dt_sdpa_params& p) {
-  if (p.seq_offsets_q) return false;  // variable-length batches: generic kernel
+  // variable-length batches: the plain operator only (per-sequence lengths are on the device, so the causal and
+  // window cases, which need sq <= sk per sequence, stay on the generic kernel)
+  if (p.seq_offsets_q && (p.is_causal || p.sliding_window > 0 || p.n_seq > 65535)) return false;
   if (p.sliding_window > 0 && p.Sq > p.Sk) return false;  // rows that may see no key: generic kernel
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)

@@ -95,6 +95,45 @@ def test_variable_length_batch(dtattn, causal):
     check(out, ref, dtype, f"varlen causal={causal}")
 
 
+@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.float16), (80, torch.float16)])
+def test_variable_length_batch_on_the_tensor_core_kernel(dtattn, D, dtype):
+    """Packed vision-encoder style batch (Qwen3_5VL.swift:428-437, non-causal): sequences that end inside a 32-row
+    store group, exactly on a tile edge, one row past it, an empty one, and one with queries but no keys."""
+    Hq, Hkv = 4, 2
+    len_q = [5, 0, 130, 64, 1, 300, 256, 257, 33, 7]
+    len_k = [7, 3, 130, 100, 300, 300, 256, 513, 0, 129]
+    off_q, off_k = [0], [0]
+    for a, b in zip(len_q, len_k):
+        off_q.append(off_q[-1] + a)
+        off_k.append(off_k[-1] + b)
+    q = so.seeded_normal((1, off_q[-1], Hq, D), 925).to(dtype)
+    k = so.seeded_normal((1, off_k[-1], Hkv, D), 926).to(dtype)
+    v = so.seeded_normal((1, off_k[-1], Hkv, D), 927).to(dtype)
+    ref, lse_ref = torch.zeros(q.shape), torch.full((1, Hq, off_q[-1]), float("-inf"))
+    for s_ in range(len(len_q)):
+        q0, q1, k0, k1 = off_q[s_], off_q[s_ + 1], off_k[s_], off_k[s_ + 1]
+        if q1 > q0 and k1 > k0:
+            o_, l_ = so.sdpa_explicit(q[:, q0:q1], k[:, k0:k1], v[:, k0:k1], D ** -0.5, compute_dtype=torch.float64,
+                                      return_lse=True)
+            ref[:, q0:q1], lse_ref[:, :, q0:q1] = o_.float(), l_.float()
+    oq = torch.tensor(off_q, dtype=torch.int32, device=DEV)
+    ok = torch.tensor(off_k, dtype=torch.int32, device=DEV)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.full(q.shape, float("nan"), dtype=dtype, device=DEV)
+    lse = torch.zeros(1, Hq, off_q[-1], dtype=torch.float32, device=DEV)
+    p = dtattn.make_params(qd, kd, vd, out, D ** -0.5, False, seq_offsets_q=oq, seq_offsets_k=ok,
+                           max_seq_q=max(len_q), max_seq_k=max(len_k))
+    assert dtattn.kernel_name(p) == "prefill_tcgen05"
+    dtattn.sdpa_forward(qd, kd, vd, D ** -0.5, False, out=out, lse=lse, seq_offsets_q=oq, seq_offsets_k=ok,
+                        max_seq_q=max(len_q), max_seq_k=max(len_k))
+    torch.cuda.synchronize()
+    assert dtattn.device_status() == 0
+    check(out, ref, dtype, f"varlen tensor-core D={D}")
+    finite = torch.isfinite(lse_ref)
+    assert torch.allclose(lse.cpu()[finite], lse_ref[finite], atol=2e-3, rtol=1e-3)
+    assert bool((lse.cpu()[~finite] == float("-inf")).all())
+
+
 def test_operator_mirror_takes_sinks_input(dtattn):
     q, k, v = inputs(1, 12, 12, 4, 1, 64, torch.float16, 931)
     sinks = so.seeded_normal((1, 1, 4, 1), 934).to(torch.float16)
