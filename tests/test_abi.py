@@ -116,3 +116,52 @@ def test_no_cpu_fallback(dtattn):
     with pytest.raises(dtattn.DtError) as e:
         dtattn.ScaledDotProductAttention(scale=1.0)(q, q, q)
     assert e.value.status in (dtattn.DT_CUDA, dtattn.DT_NO_DEVICE, dtattn.DT_UNSUPPORTED)
+
+
+def test_new_entry_points_validate_without_a_gpu(dtattn):
+    """Host-side checks of the decode-step, prologue and projected calls: sizes and refusals are decided before
+    anything touches a device."""
+    lib = dtattn.lib()
+    f16 = torch.float16
+    q = torch.zeros(1, 1, 8, 128, dtype=f16)
+    cache = torch.zeros(1, 4096, 2, 128, dtype=f16)
+    new = torch.zeros(1, 1, 2, 128, dtype=f16)
+    rot = torch.zeros(1, 1, 128, dtype=f16)
+    sp = dtattn.make_step_params(q, cache, cache, new, new, rot, q, 0.1, 3000)
+    need = ctypes.c_size_t(0)
+    assert lib.dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)) == dtattn.DT_OK
+    assert need.value > 4096                       # split over the cached rows: ticket area plus partials
+    sp.T_new = 0
+    assert lib.dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)) == dtattn.DT_BAD_ARG
+    sp = dtattn.make_step_params(q, cache, cache, new, new, rot, q, 0.1, 1)   # empty cache: nothing to split
+    assert lib.dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)) == dtattn.DT_OK
+    assert need.value == 0
+
+    x = torch.zeros(1, 16, 4, 64, dtype=f16)
+    pp = dtattn.make_prologue_params(x, x)
+    pp.D = 260
+    assert lib.dt_qk_prologue(ctypes.byref(pp), None, None) == dtattn.DT_UNSUPPORTED
+    pp = dtattn.make_prologue_params(x, x)
+    pp.x.stride_s = 250                             # rows that are not 16-byte aligned
+    assert lib.dt_qk_prologue(ctypes.byref(pp), None, None) == dtattn.DT_UNSUPPORTED
+
+    p = dtattn.make_params(x, x, x, x, 0.125)
+    pr = dtattn.OutProj()
+    w = torch.zeros(512, 256, dtype=f16)
+    out = torch.zeros(1, 16, 512, dtype=f16)
+    pr.weight, pr.C = w.data_ptr(), 512
+    pr.out = dtattn.Tensor4(out.data_ptr(), out.stride(0), out.stride(1), 512)
+    assert lib.dt_sdpa_projected_workspace_size(ctypes.byref(p), ctypes.byref(pr), ctypes.byref(need)) == dtattn.DT_OK
+    assert need.value == 4096 + 16 * 256 * 2        # ticket area kept clear, then the attention output
+    p.dtype = dtattn.DT_F32
+    assert lib.dt_sdpa_projected_workspace_size(ctypes.byref(p), ctypes.byref(pr), ctypes.byref(need)) == dtattn.DT_UNSUPPORTED
+
+    # sinks / window / variable length on the plain call: kernel choice is made on the host
+    qd = torch.zeros(1, 300, 4, 128, dtype=f16)
+    offs = torch.zeros(3, dtype=torch.int32)
+    p = dtattn.make_params(qd, qd, qd, qd, 0.1, False, seq_offsets_q=offs, seq_offsets_k=offs, max_seq_q=200, max_seq_k=200)
+    assert dtattn.kernel_name(p) == "prefill_tcgen05"
+    p = dtattn.make_params(qd, qd, qd, qd, 0.1, True, seq_offsets_q=offs, seq_offsets_k=offs, max_seq_q=200, max_seq_k=200)
+    assert dtattn.kernel_name(p) == "generic"
+    p = dtattn.make_params(qd, qd, qd, qd, 0.1, True, sliding_window=64, sinks=torch.zeros(4, dtype=f16))
+    assert dtattn.kernel_name(p) == "prefill_tcgen05"
