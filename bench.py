@@ -542,6 +542,38 @@ def run_sharded(args, dtattn, device, peaks):
         t1 = time_device(f, 2, 1) / 2
         del full
     dist.barrier()
+    also = {}
+    if 24 % world == 0 and not args.no_side:
+        # side measurement: Flux joint attention + output projection with the heads spread over the ranks
+        # (row-parallel GEMM, fp32 partial tiles stored to the row owner over NVLink, rendezvous, reduction)
+        try:
+            fw = WORKLOADS["flux_joint"]
+            hl2, D2, S2, C2 = fw["Hq"] // world, fw["D"], fw["Sq"], fw["Hq"] * fw["D"]
+            g2 = torch.Generator(device=device).manual_seed(23 + rank)
+            rnd = lambda *shape: torch.randn(*shape, generator=g2, device=device, dtype=torch.float32).to(torch.bfloat16)
+            q2, k2, v2 = rnd(1, S2, hl2, D2), rnd(1, S2, hl2, D2), rnd(1, S2, hl2, D2)
+            w2 = rnd(C2, hl2 * D2) * (C2 ** -0.5)
+            b2 = rnd(C2)
+            _, rb, rpr = comm.projected_sizes(q2, k2, v2, D2 ** -0.5, C2)
+            recv = torch.zeros(rb // 4, dtype=torch.float32, device=device)
+            comm.register_output(recv)
+            rows = torch.empty(rpr, C2, dtype=torch.bfloat16, device=device)
+            fn = lambda i: comm.forward_projected(q2, k2, v2, D2 ** -0.5, w2, b2, recv, rows)
+            for _ in range(3):
+                fn(0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms = time_device(fn, 10, 0) / 10
+            tm = torch.tensor([ms], device=device)
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+            flp = flops_of(fw) + 2.0 * S2 * C2 * C2
+            also["flux_attention_plus_projection_headsharded"] = {
+                "ms_per_call": round(float(tm.item()), 4), "tflops_all_gpus": round(flp / (float(tm.item()) * 1e-3) / 1e12, 1),
+                "rows_per_rank": rpr, "nvlink_bytes_sent_per_rank": int((world - 1) * rpr * C2 * 4)}
+            del recv
+        except Exception as e:  # a side measurement must not take the main line down
+            also["flux_attention_plus_projection_headsharded_error"] = str(e)[:160]
+    dist.barrier()
     if rank == 0:
         peak = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
         line = {"metric": METRIC, "value": round(tflops, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -563,7 +595,8 @@ def run_sharded(args, dtattn, device, peaks):
                         "d2h_bytes_per_step": 2 * ho.numel(), "ms_per_step": round(e2e_s * 1e3, 3)},
                 "gpu_launches": launches, "device_status": status,
                 "t1_same_workload_ms": round(t1, 3) if t1 else None,
-                "strong_scaling_efficiency_same_run": round(t1 / (world * ms_step), 4) if t1 else None}
+                "strong_scaling_efficiency_same_run": round(t1 / (world * ms_step), 4) if t1 else None,
+                "also": also}
         print(json.dumps(line))
     comm.close()
     dist.destroy_process_group()

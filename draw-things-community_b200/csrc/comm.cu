@@ -67,7 +67,7 @@ struct Comm {
   cudaEvent_t chunk_done[kMaxChunks];
   cudaEvent_t all_done = nullptr;
   // output buffers registered for the fused mode: every rank's buffer mapped into this process
-  static constexpr int kMaxRegs = 4;
+  static constexpr int kMaxRegs = 8;
   struct Reg {
     void* local = nullptr;
     size_t bytes = 0;
@@ -76,6 +76,7 @@ struct Comm {
   } regs[kMaxRegs];
   int n_regs = 0;
   int* flag = nullptr;               // 4 bytes for the in-stream rendezvous after a fused step
+  unsigned long long proj_calls = 0; // projected head-sharded calls so far: picks the half of the receive buffer
   void* xchg = nullptr;              // small device buffer for exchanging handles
 };
 
@@ -373,6 +374,92 @@ int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tens
   DT_CUDA_TRY(cudaEventRecord(c->all_done, c->side));
   DT_CUDA_TRY(cudaStreamWaitEvent(s, c->all_done, 0));
   return DT_OK;
+}
+
+// ---- head-sharded attention + output projection: row-parallel GEMM + reduce-scatter -----------------------
+
+static int proj_rows_per_rank(int64_t M, int world) {
+  const int64_t per = (M + world - 1) / world;
+  return (int)((per + 127) / 128 * 128);  // whole 128-row tiles, so that a tile has one owner
+}
+
+int dt_sdpa_projected_headsharded_sizes(const dt_sdpa_params* local, int world, int C, size_t* workspace_bytes,
+                                        size_t* recv_bytes, int* rows_per_rank) {
+  if (!local || world <= 0 || world > 8 || C <= 0) return DT_BAD_ARG;
+  if (local->dtype != DT_F16 && local->dtype != DT_BF16) return DT_UNSUPPORTED;
+  if (C % 8 || ((int64_t)local->Hq * local->D) % 8) return DT_UNSUPPORTED;
+  dt_sdpa_params t = *local;
+  t.o = t.q;
+  size_t inner = 0;
+  int st = dt_sdpa_workspace_size(&t, &inner);
+  if (st != DT_OK) return st;
+  const int64_t M = (int64_t)local->B * local->Sq;
+  const int rpr = proj_rows_per_rank(M, world);
+  const size_t o_off = al256(inner) < 4096 ? 4096 : al256(inner);  // the ticket area stays clear
+  if (workspace_bytes) *workspace_bytes = o_off + al256((size_t)M * local->Hq * local->D * 2) + al256((size_t)128 * C * 2);
+  // two halves used alternately: a fast rank's next call must not overwrite slabs a slower rank is still summing
+  if (recv_bytes) *recv_bytes = 2 * (size_t)world * rpr * C * sizeof(float);
+  if (rows_per_rank) *rows_per_rank = rpr;
+  return DT_OK;
+}
+
+int dt_sdpa_forward_projected_headsharded(void* comm, const dt_sdpa_params* local, const void* weight_local,
+                                          const void* bias, int C, void* recv, dt_tensor4 out_rows, void* workspace,
+                                          size_t workspace_bytes, void* cuda_stream) {
+  if (!comm || !local || !weight_local || !recv || !out_rows.ptr) return DT_BAD_ARG;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  NcclApi& api = nccl();
+  if (!api.ok) return DT_NCCL;
+  size_t need = 0, recv_bytes = 0;
+  int rpr = 0;
+  int st = dt_sdpa_projected_headsharded_sizes(local, c->world, C, &need, &recv_bytes, &rpr);
+  if (st != DT_OK) return st;
+  if (!workspace || workspace_bytes < need) return DT_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(weight_local) % 16 || reinterpret_cast<uintptr_t>(recv) % 16 ||
+      reinterpret_cast<uintptr_t>(out_rows.ptr) % 16 || out_rows.stride_s % 8)
+    return DT_UNSUPPORTED;
+  const Comm::Reg* reg = nullptr;
+  for (int i = 0; i < c->n_regs; ++i)
+    if (c->regs[i].local == recv) reg = &c->regs[i];
+  if (!reg || reg->bytes < recv_bytes) return DT_BAD_ARG;  // recv must be registered on every rank (dt_comm_register_output)
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  // 1. local head slice -> [M, Kl] rows in the workspace
+  dt_sdpa_params p = *local;
+  dt_sdpa_params t = *local;
+  t.o = t.q;
+  size_t inner = 0;
+  dt_sdpa_workspace_size(&t, &inner);
+  const size_t o_off = al256(inner) < 4096 ? 4096 : al256(inner);
+  const int64_t Kl = (int64_t)local->Hq * local->D;
+  const int64_t M = (int64_t)local->B * local->Sq;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  p.o.ptr = w + o_off;
+  p.o.stride_h = local->D;
+  p.o.stride_s = Kl;
+  p.o.stride_b = Kl * local->Sq;
+  st = dt_sdpa_forward(&p, workspace, o_off, s);
+  if (st != DT_OK) return st;
+  // 2. partial C = O_local . W_local^T, each 128-row tile stored (fp32) into slab [rank] of its owner's buffer
+  const size_t half = (size_t)(c->proj_calls++ & 1) * ((size_t)c->world * rpr * C);  // floats
+  float* slabs[8];
+  for (int q = 0; q < c->world; ++q) slabs[q] = static_cast<float*>(reg->peer[q]) + half;
+  dt_tensor4 a_view{p.o.ptr, Kl * M, Kl, Kl};
+  dt_tensor4 scratch{w + o_off + al256((size_t)M * Kl * 2), (int64_t)C * 128, (int64_t)C, (int64_t)C};
+  st = launch_out_proj_rowparallel(a_view, (int)M, (int)Kl, weight_local, C, scratch, local->dtype, slabs, c->world, c->rank,
+                                   rpr, s);
+  if (st != DT_OK) return st;
+  // 3. rendezvous: kernel completion makes this rank's peer stores visible; after it every rank's have landed
+  if (c->world > 1) {
+    if (!c->flag) return DT_BAD_ARG;
+    ncclResult_t r = api.AllReduce(c->flag, c->flag, 1, ncclInt, ncclSum, c->comm, s);
+    st = wait_nccl(c, r, c->timeout_ms);
+    if (st != DT_OK) return st;
+  }
+  // 4. this rank's rows: bias + sum of the slabs, rounded to the 16-bit type
+  const int64_t row0 = (int64_t)c->rank * rpr;
+  const int rows = (int)(M - row0 < 0 ? 0 : (M - row0 < rpr ? M - row0 : rpr));
+  return launch_slab_reduce(static_cast<const float*>(recv) + half, bias, out_rows.ptr, out_rows.stride_s, c->world, rows, rpr, C,
+                            local->dtype, s);
 }
 
 }  // extern "C"

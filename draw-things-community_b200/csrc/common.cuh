@@ -46,6 +46,11 @@ int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* ex
 int launch_out_proj(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
                     const dt_tensor4& out, int dtype, cudaStream_t stream);
 
+int launch_out_proj_rowparallel(const dt_tensor4& a_view, int M, int K, const void* weight, int N, const dt_tensor4& scratch_out,
+                                int dtype, float* const* slabs, int world, int rank, int rows_per_rank, cudaStream_t stream);
+int launch_slab_reduce(const float* recv, const void* bias, void* out, int64_t out_stride, int world, int rows,
+                       int rows_per_rank, int N, int dtype, cudaStream_t stream);
+
 // [world][rows][Hl][D] -> [B,Sq,world*Hl,D]
 int launch_permute_gathered(const void* src, dt_tensor4 dst, int world, int B, int Sq, int Hl, int D,
                             int dtype, cudaStream_t stream);

@@ -39,6 +39,11 @@ struct ProjArgs {
   const void* bias;  // [N] or null
   unsigned int* status;
   int S, N, K, tiles_per_batch;
+  // Row-parallel mode (head-sharded ranks each hold a K-slice): the fp32 partial tile goes to the rank that owns
+  // its rows, into slab [this rank] of that rank's receive buffer [world][rows_per_rank][N] (ordinary stores, peer
+  // memory over NVLink for other ranks); the owner sums the slabs afterwards.  slab[0] == nullptr: plain mode.
+  float* slab[8];
+  int rank, rows_per_rank;
 };
 
 template <typename T>
@@ -136,6 +141,40 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t my_stage = staging + (uint32_t)ew * (32 * 128);
       const T* bias = reinterpret_cast<const T*>(a.bias);
       const int row0 = s0 + ew * 32;
+      if (a.slab[0] != nullptr) {
+        // ---- row-parallel mode: fp32 partials to the owner of these rows ----
+        const int owner = s0 / a.rows_per_rank;  // a tile never straddles two owners (rows_per_rank % 128 == 0)
+        float* slab = a.slab[0];  // selected without indexing the parameter array dynamically
+#pragma unroll
+        for (int i = 1; i < 8; ++i)
+          if (owner == i) slab = a.slab[i];
+        float* dst = slab + ((size_t)a.rank * a.rows_per_rank + (size_t)(row0 - owner * a.rows_per_rank)) * a.N;
+#pragma unroll 1
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t acc[32];
+          ptx::tmem_ld32(t_acc + c * 32, acc);
+          ptx::tc_wait_ld();
+          // stage 32 rows x 128 bytes (16-byte chunk q of row r at q ^ (r & 7)), then 8 lanes write one row
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint32_t addr = my_stage + (uint32_t)lane * 128 + (((uint32_t)v ^ ((uint32_t)lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(acc[v * 4 + 0]), "r"(acc[v * 4 + 1]),
+                         "r"(acc[v * 4 + 2]), "r"(acc[v * 4 + 3])
+                         : "memory");
+          }
+          __syncwarp();
+          const int col = n0 + c * 32 + (lane & 7) * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), ch = lane & 7;
+            uint4 val;
+            const uint32_t addr = my_stage + (uint32_t)r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+            if (row0 + r < a.S && col < a.N) *reinterpret_cast<uint4*>(dst + (size_t)r * a.N + col) = val;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll
       for (int hf = 0; hf < kTileN / 64; ++hf) {
 #pragma unroll
@@ -173,6 +212,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         __syncwarp();
       }
+      }
       if (lane == 0) ptx::bulk_wait_all();
     } else {
       atomicCAS(a.status, 0u, 6u);
@@ -190,7 +230,8 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 template <typename T>
 int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
-                  const dt_tensor4& out, int dtype, cudaStream_t stream) {
+                  const dt_tensor4& out, int dtype, cudaStream_t stream, float* const* slabs = nullptr, int world = 0,
+                  int rank = 0, int rows_per_rank = 0) {
   CUtensorMap ma, mb, mc;
   dt_tensor4 w_view{const_cast<void*>(weight), (int64_t)N * K, (int64_t)K, (int64_t)K};
   if (!make_bshd_tensor_map(&ma, a_view, B, S, 1, K, dtype, kTile)) return DT_UNSUPPORTED;
@@ -202,6 +243,12 @@ int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* wei
   if (!a.status) return DT_CUDA;
   a.S = S; a.N = N; a.K = K;
   a.tiles_per_batch = (S + kTile - 1) / kTile;
+  if (slabs) {
+    if (world < 1 || world > 8 || rows_per_rank % kTile || B != 1) return DT_BAD_ARG;
+    for (int i = 0; i < world; ++i) a.slab[i] = slabs[i];
+    a.rank = rank;
+    a.rows_per_rank = rows_per_rank;
+  }
   auto kern = out_proj_kernel<T>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kProjSmem));
   const int64_t gy = (int64_t)a.tiles_per_batch * B;
@@ -220,6 +267,62 @@ int launch_out_proj(const dt_tensor4& a_view, int B, int S, int K, const void* w
   if (dtype == DT_F16) return launch_proj_t<__half>(a_view, B, S, K, weight, bias, N, out, dtype, stream);
   if (dtype == DT_BF16) return launch_proj_t<__nv_bfloat16>(a_view, B, S, K, weight, bias, N, out, dtype, stream);
   return DT_UNSUPPORTED;
+}
+
+// Row-parallel form: A [M, K_local] (this rank's heads), W_local [N, K_local]; fp32 partial tiles are stored into
+// slab `rank` of the receive buffer of the rank that owns the tile's rows.  `scratch_out` is a valid [M, N] 16-bit
+// view only used to build the (unused) store map.
+int launch_out_proj_rowparallel(const dt_tensor4& a_view, int M, int K, const void* weight, int N, const dt_tensor4& scratch_out,
+                                int dtype, float* const* slabs, int world, int rank, int rows_per_rank, cudaStream_t stream) {
+  if (dtype == DT_F16)
+    return launch_proj_t<__half>(a_view, 1, M, K, weight, nullptr, N, scratch_out, dtype, stream, slabs, world, rank, rows_per_rank);
+  if (dtype == DT_BF16)
+    return launch_proj_t<__nv_bfloat16>(a_view, 1, M, K, weight, nullptr, N, scratch_out, dtype, stream, slabs, world, rank,
+                                        rows_per_rank);
+  return DT_UNSUPPORTED;
+}
+
+namespace {
+// out[i, :] = bias + sum over ranks of slab[r][i, :], rounded to T: the owner's half of the reduce-scatter.
+template <typename T>
+__global__ void __launch_bounds__(256) slab_reduce_kernel(const float* __restrict__ recv, const T* __restrict__ bias,
+                                                          T* __restrict__ out, int64_t out_stride, int world, int rows,
+                                                          int rows_per_rank, int N) {
+  const int vec_per_row = N / 4;
+  const int64_t total = (int64_t)rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / vec_per_row), c4 = (int)(i - (int64_t)row * vec_per_row);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias) {
+      acc.x = to_float(bias[c4 * 4 + 0]); acc.y = to_float(bias[c4 * 4 + 1]);
+      acc.z = to_float(bias[c4 * 4 + 2]); acc.w = to_float(bias[c4 * 4 + 3]);
+    }
+    for (int r = 0; r < world; ++r) {  // fixed order: the sum does not depend on arrival order
+      const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)r * rows_per_rank + row) * N + c4 * 4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    T* o = out + (int64_t)row * out_stride + c4 * 4;
+    o[0] = from_float<T>(acc.x); o[1] = from_float<T>(acc.y); o[2] = from_float<T>(acc.z); o[3] = from_float<T>(acc.w);
+  }
+}
+}  // namespace
+
+int launch_slab_reduce(const float* recv, const void* bias, void* out, int64_t out_stride, int world, int rows,
+                       int rows_per_rank, int N, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return DT_OK;
+  const int64_t total = (int64_t)rows * (N / 4);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (dtype == DT_F16)
+    slab_reduce_kernel<__half><<<(int)blocks, 256, 0, stream>>>(recv, (const __half*)bias, (__half*)out, out_stride, world, rows,
+                                                                rows_per_rank, N);
+  else if (dtype == DT_BF16)
+    slab_reduce_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(recv, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out,
+                                                                       out_stride, world, rows, rows_per_rank, N);
+  else
+    return DT_UNSUPPORTED;
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
 }
 
 }  // namespace dt

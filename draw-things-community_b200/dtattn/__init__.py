@@ -100,6 +100,11 @@ SYMBOLS = [
     ("dt_sdpa_headsharded_workspace_size", ctypes.c_int, [_P(SdpaParams), ctypes.c_int, ctypes.c_int, _P(ctypes.c_size_t)]),
     ("dt_sdpa_forward_headsharded", ctypes.c_int,
      [ctypes.c_void_p, _P(SdpaParams), Tensor4, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    ("dt_sdpa_projected_headsharded_sizes", ctypes.c_int,
+     [_P(SdpaParams), ctypes.c_int, ctypes.c_int, _P(ctypes.c_size_t), _P(ctypes.c_size_t), _P(ctypes.c_int)]),
+    ("dt_sdpa_forward_projected_headsharded", ctypes.c_int,
+     [ctypes.c_void_p, _P(SdpaParams), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, Tensor4,
+      ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_permute_gathered", ctypes.c_int,
      [ctypes.c_void_p, Tensor4, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
       ctypes.c_void_p]),
@@ -483,6 +488,33 @@ class HeadShardedComm:
                                                  ctypes.c_void_p(self.ws.data_ptr()), self.ws.numel(),
                                                  ctypes.c_void_p(s)), "dt_sdpa_forward_headsharded")
         return o_full
+
+    def projected_sizes(self, q_local, k_local, v_local, scale, C, is_causal=False):
+        """(workspace bytes, receive-buffer bytes, rows per rank) of forward_projected for these shapes."""
+        p = make_params(q_local, k_local, v_local, q_local, scale, is_causal)
+        ws, rb, rpr = ctypes.c_size_t(0), ctypes.c_size_t(0), ctypes.c_int(0)
+        _check(lib().dt_sdpa_projected_headsharded_sizes(ctypes.byref(p), self.world, C, ctypes.byref(ws), ctypes.byref(rb),
+                                                         ctypes.byref(rpr)), "dt_sdpa_projected_headsharded_sizes")
+        return ws.value, rb.value, rpr.value
+
+    def forward_projected(self, q_local, k_local, v_local, scale, weight_local, bias, recv, out_rows, is_causal=False,
+                          stream=None):
+        """Local head slice, row-parallel output projection and reduce-scatter in one call: this rank's rows
+        [rank * rows_per_rank, ...) of the flattened [B*Sq, C] output land in out_rows ([rows_per_rank, C]).  recv is
+        the fp32 receive buffer registered on every rank with register_output."""
+        C = weight_local.shape[0]
+        p = make_params(q_local, k_local, v_local, q_local, scale, is_causal)
+        need, _, _ = self.projected_sizes(q_local, k_local, v_local, scale, C, is_causal)
+        s = stream if stream is not None else torch.cuda.current_stream(q_local.device).cuda_stream
+        if getattr(self, "proj_ws", None) is None:
+            self.proj_ws = Workspace(q_local.device)
+        ptr, nbytes = self.proj_ws.ensure(need, s)
+        rows = Tensor4(out_rows.data_ptr(), 0, out_rows.stride(0), C)
+        _check(lib().dt_sdpa_forward_projected_headsharded(
+            self.handle, ctypes.byref(p), ctypes.c_void_p(weight_local.data_ptr()),
+            ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, C, ctypes.c_void_p(recv.data_ptr()), rows,
+            ctypes.c_void_p(ptr), nbytes, ctypes.c_void_p(s)), "dt_sdpa_forward_projected_headsharded")
+        return out_rows
 
     def close(self):
         if self.handle:

@@ -42,3 +42,18 @@ def chunk_rows(Sq: int, chunks: int, items_per_row_block: int = 1, sms: int = 14
     per = -(-Sq // chunks)
     per = min(Sq, -(-per // unit) * unit)
     return [(r0, min(Sq, r0 + per)) for r0 in range(0, Sq, per)]
+
+
+def projection_rows(M: int, world: int, tile: int = 128):
+    """Row ownership of the head-sharded output projection (dt_sdpa_forward_projected_headsharded): the M = B*Sq
+    flattened output rows are dealt out in blocks of rows_per_rank, a multiple of the GEMM's 128-row tile so that a
+    tile has one owner.  Returns (rows_per_rank, [(row_begin, row_end) per rank]); trailing ranks may own nothing."""
+    per = -(-M // world)
+    rpr = -(-per // tile) * tile
+    return rpr, [(min(M, r * rpr), min(M, (r + 1) * rpr)) for r in range(world)]
+
+
+def weight_slice(weight, rank: int, world: int, Hq: int, D: int):
+    """The K-slice of the unify-heads Dense weight [C, Hq*D] that multiplies rank r's heads."""
+    per = Hq // world
+    return weight[:, rank * per * D:(rank + 1) * per * D]

@@ -244,7 +244,7 @@ int dt_comm_destroy(void* comm);
  * dt_sdpa_forward_headsharded whose o_full.ptr is a registered buffer stores each output tile straight into
  * all ranks' buffers from the attention kernel's epilogue (ordinary peer stores over NVLink, overlapped with
  * the tensor-core work) and ends with one small in-stream rendezvous, instead of all-gather + permute.
- * Up to 4 buffers per communicator, up to 8 ranks. */
+ * Up to 8 buffers per communicator, up to 8 ranks. */
 int dt_comm_register_output(void* comm, void* o_full, size_t bytes);
 /* Run the local head slice (`local`: Hq and Hkv are the per-rank counts, o is ignored) and gather the
  * full output into o_full ([B, Sq, Hq*world, D], contiguous rows) on every rank.  `chunks` >= 1 splits
@@ -254,6 +254,23 @@ int dt_comm_register_output(void* comm, void* o_full, size_t bytes);
 int dt_sdpa_headsharded_workspace_size(const dt_sdpa_params* local, int world, int chunks, size_t* bytes);
 int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tensor4 o_full, int chunks,
                                 void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Head-sharded attention + output projection: row-parallel GEMM + reduce-scatter in one call (no counterpart in
+ * the reference; this is what multiHeadOutputProjectionFused becomes when the heads are spread over GPUs).  Rank r
+ * holds its head slice of q, k, v and the matching K-slice of the Dense weight, weight_local [C, Hq_local*D]
+ * row-major.  The flattened output rows [B*Sq, C] are dealt out in blocks of *rows_per_rank (a multiple of 128):
+ * rank r ends with rows [r*rows_per_rank, (r+1)*rows_per_rank) in out_rows ([rows, C], row stride
+ * out_rows.stride_s), bias included.  recv is an fp32 buffer of *recv_bytes that every rank registered with
+ * dt_comm_register_output: the GEMM epilogue stores each fp32 partial tile straight into slab [rank] of the owning
+ * rank's recv buffer (ordinary stores, over NVLink for other ranks), one small in-stream rendezvous follows, and
+ * the owner sums the slabs in rank order (the result does not depend on arrival order).  recv holds two sets of
+ * slabs used by alternate calls, so a rank that runs ahead never overwrites what a slower rank is still summing;
+ * all ranks must make the same sequence of calls. */
+int dt_sdpa_projected_headsharded_sizes(const dt_sdpa_params* local, int world, int C, size_t* workspace_bytes,
+                                        size_t* recv_bytes, int* rows_per_rank);
+int dt_sdpa_forward_projected_headsharded(void* comm, const dt_sdpa_params* local, const void* weight_local,
+                                          const void* bias, int C, void* recv, dt_tensor4 out_rows, void* workspace,
+                                          size_t workspace_bytes, void* cuda_stream);
 
 /* Layout helper used by the head-sharded path: src [world][B*Sq][Hl][D] (rank-major gather order)
  * -> dst view [B, Sq, world*Hl, D].  Exposed because a caller that gathers by other means needs it. */

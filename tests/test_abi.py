@@ -165,3 +165,19 @@ def test_new_entry_points_validate_without_a_gpu(dtattn):
     assert dtattn.kernel_name(p) == "generic"
     p = dtattn.make_params(qd, qd, qd, qd, 0.1, True, sliding_window=64, sinks=torch.zeros(4, dtype=f16))
     assert dtattn.kernel_name(p) == "prefill_tcgen05"
+
+
+def test_projected_headsharded_sizes(dtattn):
+    lib = dtattn.lib()
+    q = torch.zeros(1, 4608, 3, 128, dtype=torch.bfloat16)
+    p = dtattn.make_params(q, q, q, q, 0.1)
+    ws, rb, rpr = ctypes.c_size_t(0), ctypes.c_size_t(0), ctypes.c_int(0)
+    assert lib.dt_sdpa_projected_headsharded_sizes(ctypes.byref(p), 8, 3072, ctypes.byref(ws), ctypes.byref(rb),
+                                                   ctypes.byref(rpr)) == dtattn.DT_OK
+    assert rpr.value == 640                                 # ceil(4608 / 8) = 576 rows, rounded up to whole 128-row tiles
+    assert rb.value == 2 * 8 * 640 * 3072 * 4               # two sets of fp32 slabs, one per sending rank
+    assert ws.value >= 4096 + 4608 * 384 * 2
+    assert lib.dt_sdpa_projected_headsharded_sizes(ctypes.byref(p), 9, 3072, None, None, None) == dtattn.DT_BAD_ARG
+    assert lib.dt_sdpa_projected_headsharded_sizes(ctypes.byref(p), 8, 3070, None, None, None) == dtattn.DT_UNSUPPORTED
+    from dtattn import sharding
+    assert sharding.projection_rows(4608, 8)[0] == 640

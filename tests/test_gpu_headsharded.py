@@ -57,6 +57,28 @@ def _worker(rank, world, port, q):
             errs.append(so.error_stats(o_fused.float().cpu(), ref))
             assert torch.equal(o_fused, o_full), "fused and gathered results must be bitwise equal"
             keep.append(o_fused)
+            # attention + output projection, row-parallel over the head slices, reduce-scattered over the rows
+            C = 512 if D == 128 else 200
+            w_full = (so.seeded_normal((C, H * D), 77) * (H * D) ** -0.5 * 2.0).to(torch.bfloat16)
+            bias = so.seeded_normal((C,), 78).to(torch.bfloat16)
+            w_local = w_full[:, q0 * D:q1 * D].contiguous().to(dev)
+            _, recv_bytes, rpr = comm.projected_sizes(ql.to(dev), kl.to(dev), vl.to(dev), cfg.scale, C)
+            recv = torch.zeros(recv_bytes // 4, dtype=torch.float32, device=dev)
+            comm.register_output(recv)
+            rows = torch.full((rpr, C), float("nan"), dtype=torch.bfloat16, device=dev)
+            for _ in range(3):  # both halves of the receive buffer, and the first one again
+                comm.forward_projected(ql.to(dev), kl.to(dev), vl.to(dev), cfg.scale, w_local, bias.to(dev), recv, rows)
+            torch.cuda.synchronize()
+            dist.barrier()
+            attn = ref.to(torch.bfloat16).reshape(B * S, H * D).double()
+            want = (attn @ w_full.double().t() + bias.double()).float()[rank * rpr:(rank + 1) * rpr]
+            got = rows[:want.shape[0]].float().cpu()
+            assert torch.isfinite(got).all()
+            mx, mean = so.error_stats(got, want)
+            # stated tolerance plus the bf16 rounding of an output of this magnitude (bias makes |out| ~ 1..4)
+            assert mx <= 2e-3 + 2 * 2.0 ** -8 * float(want.abs().max()), ("projected max-abs", rank, mx)
+            assert mean <= 2e-4 + 2.0 ** -8 * float(want.abs().mean()), ("projected mean-abs", rank, mean)
+            keep.append(recv)
         comm.close()
         q.put((rank, errs, dtattn.device_status()))
     finally:
@@ -72,7 +94,7 @@ def test_head_sharded_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = sorted(q.get(timeout=300) for _ in range(2))
+    res = sorted(q.get(timeout=120) for _ in range(2))
     for p in procs:
         p.join(60)
         assert p.exitcode == 0

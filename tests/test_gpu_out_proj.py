@@ -81,3 +81,26 @@ def test_projected_argument_checks(dtattn):
     assert lib.dt_sdpa_projected_workspace_size(ctypes.byref(p), ctypes.byref(pr), ctypes.byref(need)) == dtattn.DT_UNSUPPORTED
     pr.C, pr.weight = 128, None
     assert lib.dt_sdpa_projected_workspace_size(ctypes.byref(p), ctypes.byref(pr), ctypes.byref(need)) == dtattn.DT_BAD_ARG
+
+
+def test_row_parallel_form_on_one_rank(dtattn):
+    """The head-sharded projected call with a world of one: the GEMM epilogue writes fp32 slabs, the reduction adds
+    the bias and rounds.  (Two ranks are covered by tests/test_gpu_headsharded.py on a 2-GPU box.)"""
+    dtype, B, S, H, D, C = torch.bfloat16, 2, 333, 4, 64, 200
+    q, k, v = inputs(B, S, S, H, H, D, dtype, 991)
+    w = (so.seeded_normal((C, H * D), 994) * (H * D) ** -0.5 * 2.0).to(dtype)
+    bias = so.seeded_normal((C,), 995).to(dtype)
+    comm = dtattn.HeadShardedComm(0, 1, lambda b: b)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    _, recv_bytes, rpr = comm.projected_sizes(qd, kd, vd, D ** -0.5, C)
+    assert rpr % 128 == 0 and rpr >= B * S
+    recv = torch.zeros(recv_bytes // 4, dtype=torch.float32, device=DEV)
+    comm.register_output(recv)
+    rows = torch.full((rpr, C), float("nan"), dtype=dtype, device=DEV)
+    for _ in range(2):
+        comm.forward_projected(qd, kd, vd, D ** -0.5, w.to(DEV), bias.to(DEV), recv, rows)
+    torch.cuda.synchronize()
+    assert dtattn.device_status() == 0
+    ref = reference(q, k, v, D ** -0.5, w, bias, False, dtype).reshape(B * S, C)
+    check(rows[:B * S], ref, dtype, "row-parallel, one rank")
+    comm.close()
