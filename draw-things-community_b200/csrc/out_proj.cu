@@ -6,11 +6,13 @@
 //
 //   C[M, N] = A[M, K] . B[N, K]^T + bias[N]      A = attention output rows (K = Hq * D, contiguous),
 //                                                B = Dense weight, [out, in] row-major, both K-major operands
-//   CTA   = one 128 x 256 tile of C (N = 256 halves the A traffic per FLOP: the loop is bound by L2 -> shared
-//           memory bandwidth, not by the tensor pipe); 8 warps: TMA producer, MMA issuer, TMEM allocator, (idle), 4 epilogue warps.
+//   CTA   = persistent, one per SM, looping over 128 x 256 tiles of C, column tile fastest (CTAs that run together
+//           share A row blocks and W column blocks in L2; N = 256 halves the A traffic per FLOP: the loop is bound by
+//           L2 -> shared memory bandwidth, not by the tensor pipe); 8 warps: TMA producer, MMA issuer, TMEM allocator, (idle), 4 epilogue warps.
 //   loop  = K in steps of 64 (one 128-byte swizzle atom): an A box of 128 rows and a B box of 256 rows land in a
-//           4-stage ring; one thread issues four tcgen05.mma (M128 N256 K16) per stage into a 256-column fp32 accumulator in
-//           TMEM and commits the stage back to the producer.
+//           4-stage ring; one thread issues four tcgen05.mma (M128 N256 K16) per stage into one of two 256-column fp32
+//           accumulators in TMEM (the epilogue of tile i overlaps the main loop of tile i + 1) and commits the stage
+//           back to the producer; the ring keeps running across tiles.
 //   out   = accumulator rows -> + bias -> 16-bit -> swizzled staging rows -> one TMA store per warp and half
 //           (clipped by the tensor map at the edges of M and N).
 // Every wait is bounded and reports through the device status word (code 6).
@@ -30,7 +32,7 @@ constexpr int kProjThreads = 256;
 constexpr int kProjSmem = kStages * kStageBytesP + kStagingBytes + 1024 + 256;
 
 struct ProjBarriers {
-  uint64_t full[kStages], empty[kStages], acc_full;
+  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -39,6 +41,7 @@ struct ProjArgs {
   const void* bias;  // [N] or null
   unsigned int* status;
   int S, N, K, tiles_per_batch;
+  int n_tiles_n, n_tiles;  // column tiles, all tiles (column tile fastest)
   // Row-parallel mode (head-sharded ranks each hold a K-slice): the fp32 partial tile goes to the rank that owns
   // its rows, into slab [this rank] of that rank's receive buffer [world][rows_per_rank][N] (ordinary stores, peer
   // memory over NVLink for other ranks); the owner sums the slabs afterwards.  slab[0] == nullptr: plain mode.
@@ -66,22 +69,26 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kTileN;
-  const int b = blockIdx.y / a.tiles_per_batch;
-  const int s0 = (blockIdx.y - b * a.tiles_per_batch) * kTile;
   const int nk = (a.K + kKStep - 1) / kKStep;
+  // tile -> (column offset, batch item, row offset)
+  auto tile_n0 = [&](int t) { return (t % a.n_tiles_n) * kTileN; };
+  auto tile_b = [&](int t) { return (t / a.n_tiles_n) / a.tiles_per_batch; };
+  auto tile_s0 = [&](int t) { return ((t / a.n_tiles_n) % a.tiles_per_batch) * kTile; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       ptx::mbar_init(&bars->full[i], 1);
       ptx::mbar_init(&bars->empty[i], 1);
     }
-    ptx::mbar_init(&bars->acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&bars->acc_full[i], 1);
+      ptx::mbar_init(&bars->acc_empty[i], 4);  // one arrival per epilogue warp
+    }
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
   if (warp == 2) {
-    ptx::tmem_alloc(&bars->tmem_base, kTileN);
+    ptx::tmem_alloc(&bars->tmem_base, 2 * kTileN);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -95,17 +102,23 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
       ptx::prefetch_tensormap(&map_c);
-      for (int kb = 0; kb < nk; ++kb) {
-        const int st = kb % kStages, use = kb / kStages;
-        if (use > 0 && !ptx::mbar_wait(&bars->empty[st], (use - 1) & 1, abort_flag)) {
-          atomicCAS(a.status, 0u, 6u);
-          *abort_flag = 1;
-          break;
+      int it = 0;  // ring position, continues across tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x) {
+        const int n0 = tile_n0(t), b = tile_b(t), s0 = tile_s0(t);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int st = it % kStages, use = it / kStages;
+          if (use > 0 && !ptx::mbar_wait(&bars->empty[st], (use - 1) & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 6u);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&bars->full[st], (uint32_t)kStageBytesP);
+          uint8_t* dst = base_ptr + st * kStageBytesP;
+          ptx::tma_load_4d(dst, &map_a, &bars->full[st], kb * kKStep, 0, s0, b);
+          ptx::tma_load_4d(dst + kBoxBytesP, &map_b, &bars->full[st], kb * kKStep, 0, n0, 0);
         }
-        ptx::mbar_arrive_expect_tx(&bars->full[st], (uint32_t)kStageBytesP);
-        uint8_t* dst = base_ptr + st * kStageBytesP;
-        ptx::tma_load_4d(dst, &map_a, &bars->full[st], kb * kKStep, 0, s0, b);
-        ptx::tma_load_4d(dst + kBoxBytesP, &map_b, &bars->full[st], kb * kKStep, 0, n0, 0);
       }
     }
   } else if (warp == 1) {
@@ -114,30 +127,50 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       constexpr uint32_t idesc = ptx::make_idesc_f16(kBf16, kTile, kTileN, 0, 0);
       const uint64_t desc = ptx::make_smem_desc_sw128(0, 16, 1024);
       bool ok = true;
-      for (int kb = 0; kb < nk; ++kb) {
-        const int st = kb % kStages;
-        if (!ptx::mbar_wait(&bars->full[st], (kb / kStages) & 1, abort_flag)) {
+      int it = 0, n_tile = 0;
+      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x, ++n_tile) {
+        const int buf = n_tile & 1, use = n_tile >> 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        if (use > 0 && !ptx::mbar_wait(&bars->acc_empty[buf], (use - 1) & 1, abort_flag)) {
           atomicCAS(a.status, 0u, 6u);
           *abort_flag = 1;
-          ok = false;
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t sa = base + st * kStageBytesP, sb = sa + kBoxBytesP;
-        const uint64_t da = desc | (uint64_t)((sa & 0x3FFFFu) >> 4), db = desc | (uint64_t)((sb & 0x3FFFFu) >> 4);
+        const uint32_t acc = tmem + (uint32_t)(buf * kTileN);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int st = it % kStages;
+          if (!ptx::mbar_wait(&bars->full[st], (it / kStages) & 1, abort_flag)) {
+            atomicCAS(a.status, 0u, 6u);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = base + st * kStageBytesP, sb = sa + kBoxBytesP;
+          const uint64_t da = desc | (uint64_t)((sa & 0x3FFFFu) >> 4), db = desc | (uint64_t)((sb & 0x3FFFFu) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kKStep / 16; ++kk)
-          ptx::mma_ss(tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-        ptx::tc_commit(&bars->empty[st]);  // the stage may be refilled once these MMAs have read it
+          for (int kk = 0; kk < kKStep / 16; ++kk)
+            ptx::mma_ss(acc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          ptx::tc_commit(&bars->empty[st]);  // the stage may be refilled once these MMAs have read it
+        }
+        if (ok) ptx::tc_commit(&bars->acc_full[buf]);
       }
-      if (ok) ptx::tc_commit(&bars->acc_full);
     }
   } else if (warp >= 4) {
     // =========================== epilogue ===========================
     const int ew = warp - 4;  // TMEM lanes 32*ew .. 32*ew + 31 = tile rows
-    if (__all_sync(0xffffffffu, ptx::mbar_wait(&bars->acc_full, 0, abort_flag))) {
+    int n_tile = 0;
+    for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++n_tile) {
+      const int buf = n_tile & 1;
+      const int n0 = tile_n0(t), b = tile_b(t), s0 = tile_s0(t);
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->acc_full[buf], (n_tile >> 1) & 1, abort_flag))) {
+        atomicCAS(a.status, 0u, 6u);
+        *abort_flag = 1;
+        break;
+      }
       ptx::tc_fence_after();
-      const uint32_t t_acc = tmem + ((uint32_t)(ew * 32) << 16);
+      const uint32_t t_acc = tmem + (uint32_t)(buf * kTileN) + ((uint32_t)(ew * 32) << 16);
       const uint32_t my_stage = staging + (uint32_t)ew * (32 * 128);
       const T* bias = reinterpret_cast<const T*>(a.bias);
       const int row0 = s0 + ew * 32;
@@ -213,10 +246,12 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
       }
       }
-      if (lane == 0) ptx::bulk_wait_all();
-    } else {
-      atomicCAS(a.status, 0u, 6u);
+      // every TMEM load of this tile has completed: hand the accumulator back to the MMA warp
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[buf]);
     }
+    if (lane == 0) ptx::bulk_wait_all();
   }
 
   // =========================== teardown ===========================
@@ -224,7 +259,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   if (warp == 2) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, kTileN);
+    ptx::tmem_dealloc(tmem, 2 * kTileN);
   }
 }
 
@@ -251,9 +286,14 @@ int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* wei
   }
   auto kern = out_proj_kernel<T>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kProjSmem));
-  const int64_t gy = (int64_t)a.tiles_per_batch * B;
-  if (gy > 65535) return DT_UNSUPPORTED;
-  dim3 grid((N + kTileN - 1) / kTileN, (unsigned)gy);
+  a.n_tiles_n = (N + kTileN - 1) / kTileN;
+  const int64_t tiles = (int64_t)a.n_tiles_n * a.tiles_per_batch * B;
+  if (tiles > (1 << 30)) return DT_UNSUPPORTED;
+  a.n_tiles = (int)tiles;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));  // one persistent CTA per SM
   kern<<<grid, kProjThreads, kProjSmem, stream>>>(ma, mb, mc, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;

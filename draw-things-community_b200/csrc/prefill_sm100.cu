@@ -443,6 +443,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ptx::tmem_ld32(t_s + 64, s[2]);
         ptx::tmem_ld32(t_s + 96, s[3]);
         ptx::tc_wait_ld();
+        if (probe && j == 0) stamp(a, 16 * n_item + 4);
 
         if (a.dbg != nullptr && first_dump && j == 0 && blockIdx.x == 0) {
           float* dst = a.dbg + ((size_t)t * kBM + row_in_tile) * kBN;
@@ -465,6 +466,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         // chunks of 32 keys that lie entirely beyond Sk are skipped (short K/V such as 77 text tokens)
         const int nch = max(1, (min(kBN, w.sk - key0) + 31) >> 5);  // at least the chunk the MMA warp always reads
+        if (probe && j == 0) stamp(a, 16 * n_item + 12);
         // row max: four independent chains of 3-input max (one per 32-column chunk)
         float mxc[4];
 #pragma unroll
@@ -502,6 +504,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         // p = exp2(s * scale_log2 - m): packed fp32x2 multiply-add, packed row sums in four independent
         // accumulators, packed conversion to the 16-bit P the second MMA reads from TMEM
+        if (probe && j == 0) stamp(a, 16 * n_item + 13);
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
         const uint64_t scale2 = ptx::pack_f32x2(a.scale_log2, a.scale_log2);
@@ -534,6 +537,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bars->p_half[t][c >> 1]);
+            if (probe && j == 0) stamp(a, 16 * n_item + 14 + (c >> 1));
           }
         }
         {
