@@ -555,8 +555,9 @@ struct Plan {
 
 // Split count: the path is bound by HBM, and what costs is the fixed part of a CTA (start-up, merge,
 // ticket, combine), so use as few CTAs as keep every SM streaming: the largest power of two with
-// pairs * splits <= 2 CTAs per SM, and at least four 16-key units per split.  (Measured on B200: B=16
-// runs at 99% of the copy peak with 2 splits and at 57% with 37.)
+// pairs * splits <= the CTAs that are resident at once (one wave), and at least four 16-key units per
+// split.  (Measured on B200: B=16 runs at 99% of the copy peak with 2 splits and at 57% with 37.)
+
 // first 16-key unit any row of the call can see: row 0's window bound
 int first_unit(const dt_sdpa_params& p) {
   if (p.sliding_window <= 0) return 0;
@@ -573,7 +574,8 @@ Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
     return pl;
   }
   const int pairs = p.B * p.Hkv;
-  const int slots = 2 * sm_count();
+  // resident CTAs per SM: two, except head dim 256 whose 215 registers per thread leave room for one
+  const int slots = (p.D > 128 ? 1 : 2) * sm_count();
   int ns = 1;
   while (pairs * ns * 2 <= slots && pl.total_units / (ns * 2) >= 4) ns *= 2;
   const char* env = getenv("DTATTN_DECODE_SPLITS");

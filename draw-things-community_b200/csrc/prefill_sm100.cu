@@ -331,7 +331,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint64_t qd0 = qd_base + (uint64_t)(qb * 2 * (C::kTileBytes >> 4));
           const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
           // ---- S_t(0) = Q_t K(0)^T ----
-          if (!ptx::mbar_wait(&bars->q_full[qb], (n_item / C::kQBufs) & 1, abort_flag) || !ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
+          stamp(a, 16 * n_item + 5);
+          if (!ptx::mbar_wait(&bars->q_full[qb], (n_item / C::kQBufs) & 1, abort_flag)) {
+            fail(1u);
+            break;
+          }
+          stamp(a, 16 * n_item + 6);
+          if (!ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
             fail(1u);
             break;
           }
@@ -456,16 +462,32 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
         const int key0 = (w.j0 + j) * kBN;
         const bool need_mask = (key0 + kBN > w.sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis) || (long long)key0 < lo;
-        if (need_mask) {
-          const long long lim = min((long long)w.sk - 1, vis);  // keys <= lim visible
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if ((long long)(key0 + c * 32 + i) > lim || (long long)(key0 + c * 32 + i) < lo) s[c][i] = 0xff800000u;  // -inf
-        }
         // chunks of 32 keys that lie entirely beyond Sk are skipped (short K/V such as 77 text tokens)
         const int nch = max(1, (min(kBN, w.sk - key0) + 31) >> 5);  // at least the chunk the MMA warp always reads
+        if (need_mask) {
+          // bounds relative to this block as 32-bit values, so that each element costs one compare against a
+          // constant: columns hi_rel+1 .. 127 and 0 .. lo_rel-1 are hidden
+          const long long lim = min((long long)w.sk - 1, vis);  // keys <= lim visible
+          const int hi_rel = (int)max(-1LL, min(lim - key0, (long long)(kBN - 1)));
+          const int lo_rel = (int)max(0LL, min(lo - key0, (long long)kBN));
+          if (lo_rel == 0) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              if (c >= nch || (c + 1) * 32 - 1 <= hi_rel) continue;  // chunk never read, or entirely visible
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i > hi_rel) s[c][i] = 0xff800000u;  // -inf
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              if (c >= nch) continue;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i > hi_rel || c * 32 + i < lo_rel) s[c][i] = 0xff800000u;  // -inf
+            }
+          }
+        }
         if (probe && j == 0) stamp(a, 16 * n_item + 12);
         // row max: four independent chains of 3-input max (one per 32-column chunk)
         float mxc[4];
