@@ -137,6 +137,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int n_units = max(0, unit_end - unit_begin);
   const int n_stages = (n_units + C::kUnitsPerStage - 1) / C::kUnitsPerStage;
 
+  if (threadIdx.x == kConsumerWarps * 32) {  // the producer lane: the descriptor fetch (about 1 us when cold) starts at once
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
   if (threadIdx.x == 0) {
     s_abort = 0;
     s_is_last = 0;
@@ -296,8 +300,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      ptx::prefetch_tensormap(&map_k);
-      ptx::prefetch_tensormap(&map_v);
       for (int st = 0; st < n_stages; ++st) {
         const int slot = st % C::kStages;
         if (st >= C::kStages) {
@@ -316,11 +318,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
           for (int hf = 0; hf < C::kHalves; ++hf) {
             ptx::tma_load_4d(dst + hf * kBoxBytes, &map_k, &full_bar[slot], hf * 64, kvh, key0, b);
-            if (dbg && st == 0 && w == 0 && hf == 0) dbg[6] = ptx::globaltimer_ns();
             ptx::tma_load_4d(dst + (C::kHalves + hf) * kBoxBytes, &map_v, &full_bar[slot], hf * 64, kvh, key0, b);
           }
         }
-        if (dbg && st == 0) dbg[7] = ptx::globaltimer_ns();
       }
     }
   } else {
@@ -482,6 +482,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       lsm[idx] = ml.y;
     }
     __syncthreads();
+    if (dbg && threadIdx.x == 0) dbg[6] = ptx::globaltimer_ns();
     for (int r = warp; r < a.M; r += kThreads / 32) {
       float mstar = -INFINITY;
       for (int sp = lane; sp < a.nsplit; sp += 32) mstar = fmaxf(mstar, wbuf[sp * a.M + r]);
@@ -510,6 +511,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
     }
     __syncthreads();
+    if (dbg && threadIdx.x == 0) dbg[7] = ptx::globaltimer_ns();
     for (int item = threadIdx.x; item < a.M * kVec; item += kThreads) {
       const int r = item / kVec, d4 = item - r * kVec;
       const float4* src = reinterpret_cast<const float4*>(a.part_o) + (base * a.M + r) * kVec + d4;
