@@ -50,3 +50,25 @@ def test_cpp_mirror_compiles_and_validates(tmp_path, dtattn):
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "fails=0" in r.stdout
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/dtattn.h must be usable from C (the boundary is a C ABI): compile a C translation unit that fills every
+    parameter struct and references every entry point."""
+    import re
+    header = os.path.join(ROOT, "include", "dtattn.h")
+    text = re.sub(r"/\*.*?\*/", "", open(header).read(), flags=re.S)
+    names = sorted(set(re.findall(r"\b(dt_[a-z0-9_]+)\s*\(", text)))
+    src = tmp_path / "abi.c"
+    body = ["#include \"dtattn.h\"", "#include <string.h>", "int probe(void) {",
+            "  dt_sdpa_params p; dt_decode_step_params s; dt_qk_prologue_params q; dt_out_proj o;",
+            "  memset(&p, 0, sizeof p); memset(&s, 0, sizeof s); memset(&q, 0, sizeof q); memset(&o, 0, sizeof o);",
+            "  p.sliding_window = 4; s.T_new = 1; q.post_scale = 1.0f; o.C = 8;",
+            "  typedef void (*fn_t)(void);",
+            "  fn_t fns[] = {" + ", ".join(f"(fn_t){n}" for n in names) + "};",
+            "  return (int)(sizeof fns / sizeof fns[0]) + p.sliding_window + s.T_new + o.C + (int)q.post_scale;", "}"]
+    src.write_text("\n".join(body) + "\n")
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), "-c", str(src), "-o",
+                        str(tmp_path / "abi.o")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert len(names) >= 25
