@@ -197,12 +197,25 @@ def side_measurements(dtattn, device, peaks):
         except Exception as e:  # graph capture is a convenience for the tiny shapes, not a requirement
             ms_graph = None
             out[name + "_graph_error"] = str(e)[:120]
+        ms_pdl = None
+        if name.startswith("decode"):
+            # the same calls with DT_FLAG_KV_PREFIX_STABLE (the caches are written by nothing in the stream): the next
+            # call's producer warps fill shared memory from its cache while the previous call's last CTAs combine
+            fns_pdl = [(lambda s=s: dtattn.sdpa_forward(s[0], s[1], s[2], scale, w["causal"], out=s[3],
+                                                        flags=dtattn.DT_FLAG_KV_PREFIX_STABLE)) for s in sets]
+            try:
+                ms_pdl = time_graph(fns_pdl, reps=reps)
+            except Exception as e:
+                out[name + "_pdl_error"] = str(e)[:120]
         best = min(x for x in (ms_stream, ms_graph) if x is not None)
         out[name] = {"us_per_call_stream": round(ms_stream * 1e3, 2),
                      "us_per_call_graph": round(ms_graph * 1e3, 2) if ms_graph else None,
                      "algorithmic_bytes": nbytes, "gbs": round(nbytes / (best * 1e-3) / 1e9, 1),
                      "frac_hbm": round(nbytes / (best * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                      "tflops": round(flops_of(w) / (best * 1e-3) / 1e12, 2), "rotating_sets": n_sets}
+        if ms_pdl:
+            out[name]["us_per_call_graph_dependent_launch"] = round(ms_pdl * 1e3, 2)
+            out[name]["frac_hbm_dependent_launch"] = round(nbytes / (ms_pdl * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         del sets, fns
         torch.cuda.empty_cache()
     out.update(decode_step_measurements(dtattn, device))

@@ -137,6 +137,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int n_units = max(0, unit_end - unit_begin);
   const int n_stages = (n_units + C::kUnitsPerStage - 1) / C::kUnitsPerStage;
 
+  // A kernel launched behind this one with programmatic stream serialization (the next decode call, see
+  // DT_FLAG_KV_PREFIX_STABLE) may be scheduled as soon as every CTA of this grid has got here; it takes the SM slots
+  // that this grid's CTAs free when they exit, while the last CTAs still combine.
+  if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == kConsumerWarps * 32) {  // the producer lane: the descriptor fetch (about 1 us when cold) starts at once
     ptx::prefetch_tensormap(&map_k);
     ptx::prefetch_tensormap(&map_v);
@@ -167,6 +171,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   // Q fragments (A operand, rows = (query token, group head), k = head dim)
   uint32_t qa[D / 16][4];
   if (warp < kConsumerWarps) {
+    // Programmatic dependent launch (DT_FLAG_KV_PREFIX_STABLE): this grid may have started while the kernel before
+    // it in the stream was still running.  The producer warp streams the K/V prefix at once (the caller guarantees
+    // that kernel does not write it); everything else -- Q, the new rows, the workspace, the outputs -- is
+    // touched only after the preceding grid has completed.  Without the launch attribute this returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const T* q = reinterpret_cast<const T*>(a.q);
     const T* rot = reinterpret_cast<const T*>(a.rotary);
     const T* p_lo = nullptr;
@@ -665,6 +674,20 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
     attr_set = true;
   }
   dim3 grid(pl.nsplit, p.Hkv, p.B);
+  if (p.flags & DT_FLAG_KV_PREFIX_STABLE) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mk, mv, a));
+    return DT_OK;
+  }
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mk, mv, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;

@@ -27,7 +27,7 @@ DT_OK, DT_BAD_ARG, DT_UNSUPPORTED, DT_WORKSPACE, DT_CUDA, DT_NCCL, DT_TIMEOUT, D
 DT_SCRATCH_LIMIT = -8
 NOALLOC_SCRATCH_BYTES = 8 << 20
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
-DT_FLAG_FP16_ACCUM_HINT, DT_FLAG_FORCE_GENERIC = 1, 2
+DT_FLAG_FP16_ACCUM_HINT, DT_FLAG_FORCE_GENERIC, DT_FLAG_KV_PREFIX_STABLE = 1, 2, 4
 _DTYPES = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
 
 
@@ -238,11 +238,11 @@ def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None,
 
 
 def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_len, is_causal=True,
-                     lse=None) -> DecodeStepParams:
+                     lse=None, flags=0) -> DecodeStepParams:
     """k_cache / v_cache: [B, capacity, Hkv, D]; the step attends over their first `total_len` rows, of which
     the last k_new.shape[1] are written by the call."""
     sp = DecodeStepParams()
-    sp.attn = make_params(q, k_cache[:, :total_len], v_cache[:, :total_len], o, scale, is_causal, None, lse)
+    sp.attn = make_params(q, k_cache[:, :total_len], v_cache[:, :total_len], o, scale, is_causal, None, lse, flags)
     sp.k_new, sp.v_new = _view4(k_new), _view4(v_new)
     sp.T_new = k_new.shape[1]
     if rotary is not None:
@@ -255,7 +255,7 @@ def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_
 
 
 def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, out=None, lse=None, workspace=None,
-                stream=None):
+                stream=None, flags=0):
     """One KV-cache step in one launch (Qwen3_5.swift:167-196): rotate q and k_new with `rotary`
     ([B or 1, T_new, D], interleaved cos/sin), write rotated k_new and v_new into cache rows
     [cached_len, cached_len + T_new) and return causal attention of the rotated queries over rows
@@ -264,7 +264,8 @@ def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, ou
     B, Sq, Hq, D = q.shape
     if out is None:
         out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
-    sp = make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, out, scale, cached_len + k_new.shape[1], True, lse)
+    sp = make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, out, scale, cached_len + k_new.shape[1], True, lse,
+                          flags)
     need = ctypes.c_size_t(0)
     _check(lib().dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)),
            "dt_sdpa_decode_step_workspace_size")

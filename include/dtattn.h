@@ -52,6 +52,13 @@ typedef struct {
 /* dt_sdpa_params.flags */
 #define DT_FLAG_FP16_ACCUM_HINT 1u /* reference flags:[.Float16] (UNet.swift:124); accepted, ignored: accumulation is always fp32 */
 #define DT_FLAG_FORCE_GENERIC 2u   /* route to the CUDA-core kernel (second GPU opinion in tests)        */
+#define DT_FLAG_KV_PREFIX_STABLE 4u /* decode over a KV cache: the kernel that precedes this call in the stream does
+                                      not write the K/V rows this call streams (rows [0, Sk), or the cached prefix
+                                      [0, Sk - T_new) of dt_sdpa_decode_step).  The decode kernel is then launched with
+                                      programmatic stream serialization: its producer warp starts filling shared
+                                      memory from the cache while the preceding kernel drains, and everything else
+                                      (Q, new rows, workspace, outputs) waits for that kernel to complete.  Ignored by
+                                      the other kernels. */
 
 typedef struct {
   int32_t B, Sq, Sk, Hq, Hkv, D; /* Hq % Hkv == 0; query head h reads KV head h / (Hq/Hkv)

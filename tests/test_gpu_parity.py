@@ -369,3 +369,44 @@ def test_permute_gathered(dtattn):
     torch.cuda.synchronize()
     want = src.permute(1, 2, 0, 3, 4).reshape(B, S, world * Hl, D)
     assert torch.equal(dst, want)
+
+
+def test_decode_with_programmatic_dependent_launch(dtattn):
+    """DT_FLAG_KV_PREFIX_STABLE: back-to-back decode calls that share one workspace and one stream may overlap (the
+    next call streams its cache while the previous one combines); every call must still be right.  The caches are
+    not written by anything in the stream, which is what the flag promises."""
+    dtype = torch.float16
+    sets = []
+    for i, (B, Sk, Hq, Hkv, D) in enumerate([(1, 8192, 32, 8, 128), (2, 3000, 16, 4, 256), (1, 5000, 8, 8, 64)]):
+        q, k, v = inputs(B, 1, Sk, Hq, Hkv, D, dtype, 1001 + 10 * i)
+        ref = oracle(q, k, v, D ** -0.5, True)
+        sets.append((q.to(DEV), k.to(DEV), v.to(DEV), ref, D))
+    outs = []
+    for rep in range(20):
+        for q, k, v, ref, D in sets:
+            outs.append((dtattn.sdpa_forward(q, k, v, D ** -0.5, True, flags=dtattn.DT_FLAG_KV_PREFIX_STABLE), ref))
+    torch.cuda.synchronize()
+    assert dtattn.device_status() == 0
+    for out, ref in outs:
+        check(out, ref, dtype, "decode, dependent launch")
+    # the fused step with the flag: other kernels (here: plain decode calls on another cache) sit between two steps
+    # of one cache, as a model's other layers do
+    B, Hq, Hkv, D, start = 1, 16, 4, 128, 700
+    k_cache = so.seeded_normal((B, start + 6, Hkv, D), 1051).to(dtype)
+    v_cache = so.seeded_normal((B, start + 6, Hkv, D), 1052).to(dtype)
+    kc_ref, vc_ref = k_cache.clone(), v_cache.clone()
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    pend = []
+    for t in range(6):
+        qn = so.seeded_normal((B, 1, Hq, D), 1060 + 3 * t).to(dtype)
+        kn = so.seeded_normal((B, 1, Hkv, D), 1061 + 3 * t).to(dtype)
+        vn = so.seeded_normal((B, 1, Hkv, D), 1062 + 3 * t).to(dtype)
+        ref = so.decode_step_explicit(qn, kc_ref, vc_ref, kn, vn, None, D ** -0.5, start + t, dtype)
+        pend.append((dtattn.decode_step(qn.to(DEV), kc, vc, kn.to(DEV), vn.to(DEV), None, D ** -0.5, start + t,
+                                        flags=dtattn.DT_FLAG_KV_PREFIX_STABLE), ref))
+        q0, k0, v0, _, D0 = sets[0]
+        dtattn.sdpa_forward(q0, k0, v0, D0 ** -0.5, True, flags=dtattn.DT_FLAG_KV_PREFIX_STABLE)
+    torch.cuda.synchronize()
+    for out, ref in pend:
+        check(out, ref, dtype, "decode step, dependent launch")
+    assert torch.equal(kc.cpu().view(torch.int16), kc_ref.view(torch.int16))
