@@ -68,6 +68,9 @@ struct DecodeArgs {
   int unit_first;   // first 16-key unit that any row can see (sliding window), 0 otherwise
   int window;       // sliding window W (0 = off): row i sees keys j > i + (Sk - Sq) - W
   const void* sinks;  // [Hq] attention sinks, or null
+  const void* q_norm_w;  // [D] RMSNorm weights applied to the queries / new keys before the rotation, or null
+  const void* k_norm_w;
+  float norm_eps;
   int Tn;           // new rows appended by the step fusion (<= 16), 0 otherwise
   int nsplit, units_per_split, total_units;
   float scale_log2;
@@ -111,6 +114,37 @@ __device__ __forceinline__ void sink_merge(float sink, float& m, float& l, float
   l = l * down + fast_exp2(sl - m2);
   o *= down;
   m = m2;
+}
+
+// RMSNorm of one packed pair: (x * inv) * w in fp32 without contraction, rounded once to T (the node the reference
+// runs before the rotation, Qwen3_5.swift:164-167).
+template <typename T>
+__device__ __forceinline__ uint32_t norm_pair(uint32_t x, float inv, uint32_t w) {
+  float x0, x1, w0, w1;
+  if constexpr (std::is_same<T, __half>::value) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x));
+    const float2 g = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    x0 = a.x; x1 = a.y; w0 = g.x; w1 = g.y;
+  } else {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+    x0 = a.x; x1 = a.y; w0 = g.x; w1 = g.y;
+  }
+  return pack2(__fmul_rn(__fmul_rn(x0, inv), w0), __fmul_rn(__fmul_rn(x1, inv), w1), !std::is_same<T, __half>::value);
+}
+
+template <typename T>
+__device__ __forceinline__ float sumsq_pair(uint32_t x) {
+  float2 a;
+  if constexpr (std::is_same<T, __half>::value) a = __half22float2(*reinterpret_cast<const __half2*>(&x));
+  else a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+  return fmaf(a.x, a.x, a.y * a.y);
+}
+
+__device__ __forceinline__ float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <typename T, int D>
@@ -196,6 +230,31 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       qa[ks][1] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq) : 0u;
       qa[ks][2] = p_lo ? *reinterpret_cast<const uint32_t*>(p_lo + ks * 16 + cq + 8) : 0u;
       qa[ks][3] = p_hi ? *reinterpret_cast<const uint32_t*>(p_hi + ks * 16 + cq + 8) : 0u;
+    }
+    if (a.q_norm_w) {
+      // per-row RMSNorm: a row's D elements sit in the four lanes that share lane >> 2
+      const T* gw = reinterpret_cast<const T*>(a.q_norm_w);
+      float ss_lo = 0.f, ss_hi = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        ss_lo += sumsq_pair<T>(qa[ks][0]) + sumsq_pair<T>(qa[ks][2]);
+        ss_hi += sumsq_pair<T>(qa[ks][1]) + sumsq_pair<T>(qa[ks][3]);
+      }
+      ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 1);
+      ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 2);
+      ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 1);
+      ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 2);
+      const float inv_lo = rsqrt_approx(fmaf(ss_lo, 1.f / (float)D, a.norm_eps));
+      const float inv_hi = rsqrt_approx(fmaf(ss_hi, 1.f / (float)D, a.norm_eps));
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t g0 = *reinterpret_cast<const uint32_t*>(gw + ks * 16 + cq);
+        const uint32_t g1 = *reinterpret_cast<const uint32_t*>(gw + ks * 16 + cq + 8);
+        qa[ks][0] = norm_pair<T>(qa[ks][0], inv_lo, g0);
+        qa[ks][1] = norm_pair<T>(qa[ks][1], inv_hi, g0);
+        qa[ks][2] = norm_pair<T>(qa[ks][2], inv_lo, g1);
+        qa[ks][3] = norm_pair<T>(qa[ks][3], inv_hi, g1);
+      }
     }
     // rotation as a second pass, so that the loads above stay back to back when there is no table: a fragment
     // register holds head dims (d, d+1) with d even, exactly one (cos, sin) pair of the rotary table
@@ -367,12 +426,37 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       T* vc = reinterpret_cast<T*>(a.v_cache);
       const int t_old = a.stream_keys;
       constexpr int kChunks = D / 8;  // 16-byte chunks per row
+      // RMSNorm of the new keys: lanes l and l + 16 each sum half of row l's squares; lane l then holds 1 / rms
+      const T* kw = reinterpret_cast<const T*>(a.k_norm_w);
+      float inv_row = 1.f;
+      if (kw) {
+        const int row = lane & 15, half = lane >> 4;
+        float ss = 0.f;
+        if (row < a.Tn) {
+          const T* src = kn + b * a.kn_sb + (int64_t)row * a.kn_ss + (int64_t)kvh * a.kn_sh + half * (D / 2);
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            const uint4 x = *reinterpret_cast<const uint4*>(src + c * 8);
+            ss += sumsq_pair<T>(x.x) + sumsq_pair<T>(x.y) + sumsq_pair<T>(x.z) + sumsq_pair<T>(x.w);
+          }
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+        inv_row = rsqrt_approx(fmaf(ss, 1.f / (float)D, a.norm_eps));
+      }
       for (int it = lane; it < kUnitKeys * kChunks; it += 32) {
         const int row = it / kChunks, ch = it - row * kChunks;
+        const float inv_k = __shfl_sync(0xffffffffu, inv_row, row);  // uniform trip count: every lane takes part
         uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = make_uint4(0u, 0u, 0u, 0u);
         if (row < a.Tn) {
           kq = *reinterpret_cast<const uint4*>(kn + b * a.kn_sb + (int64_t)row * a.kn_ss + (int64_t)kvh * a.kn_sh + ch * 8);
           vq = *reinterpret_cast<const uint4*>(vn + b * a.vn_sb + (int64_t)row * a.vn_ss + (int64_t)kvh * a.vn_sh + ch * 8);
+          if (kw) {
+            const uint4 g = *reinterpret_cast<const uint4*>(kw + ch * 8);
+            kq.x = norm_pair<T>(kq.x, inv_k, g.x);
+            kq.y = norm_pair<T>(kq.y, inv_k, g.y);
+            kq.z = norm_pair<T>(kq.z, inv_k, g.z);
+            kq.w = norm_pair<T>(kq.w, inv_k, g.w);
+          }
           if (rot) {
             const uint4 rq = *reinterpret_cast<const uint4*>(rot + b * a.rot_sb + (int64_t)row * a.rot_ss + ch * 8);
             kq.x = cmul_pair<T>(kq.x, rq.x);
@@ -657,6 +741,7 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
     a.kn_sb = step->k_new.stride_b; a.kn_ss = step->k_new.stride_s; a.kn_sh = step->k_new.stride_h;
     a.vn_sb = step->v_new.stride_b; a.vn_ss = step->v_new.stride_s; a.vn_sh = step->v_new.stride_h;
     a.rot_sb = step->rotary_stride_b; a.rot_ss = step->rotary_stride_s;
+    a.q_norm_w = step->q_norm_weight; a.k_norm_w = step->k_norm_weight; a.norm_eps = step->norm_eps;
     a.kc_sb = p.k.stride_b; a.kc_ss = p.k.stride_s; a.kc_sh = p.k.stride_h;
     a.vc_sb = p.v.stride_b; a.vc_ss = p.v.stride_s; a.vc_sh = p.v.stride_h;
   }
@@ -744,6 +829,10 @@ int validate_step(const dt_decode_step_params* s) {
   if (!ok(s->k_new) || !ok(s->v_new)) return DT_UNSUPPORTED;
   if (s->rotary && (reinterpret_cast<uintptr_t>(s->rotary) % 16 || s->rotary_stride_b % 8 || s->rotary_stride_s % 8))
     return DT_UNSUPPORTED;
+  if ((s->q_norm_weight && reinterpret_cast<uintptr_t>(s->q_norm_weight) % 16) ||
+      (s->k_norm_weight && reinterpret_cast<uintptr_t>(s->k_norm_weight) % 16))
+    return DT_UNSUPPORTED;
+  if ((s->q_norm_weight || s->k_norm_weight) && !(s->norm_eps >= 0.f)) return DT_BAD_ARG;
   return DT_OK;
 }
 }  // namespace

@@ -50,7 +50,8 @@ class SdpaParams(ctypes.Structure):
 
 class DecodeStepParams(ctypes.Structure):
     _fields_ = [("attn", SdpaParams), ("k_new", Tensor4), ("v_new", Tensor4), ("T_new", ctypes.c_int32),
-                ("rotary", ctypes.c_void_p), ("rotary_stride_b", ctypes.c_int64), ("rotary_stride_s", ctypes.c_int64)]
+                ("rotary", ctypes.c_void_p), ("rotary_stride_b", ctypes.c_int64), ("rotary_stride_s", ctypes.c_int64),
+                ("q_norm_weight", ctypes.c_void_p), ("k_norm_weight", ctypes.c_void_p), ("norm_eps", ctypes.c_float)]
 
 
 class QkPrologueParams(ctypes.Structure):
@@ -238,7 +239,7 @@ def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None,
 
 
 def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_len, is_causal=True,
-                     lse=None, flags=0) -> DecodeStepParams:
+                     lse=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6) -> DecodeStepParams:
     """k_cache / v_cache: [B, capacity, Hkv, D]; the step attends over their first `total_len` rows, of which
     the last k_new.shape[1] are written by the call."""
     sp = DecodeStepParams()
@@ -251,11 +252,16 @@ def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_
         sp.rotary = rotary.data_ptr()
         sp.rotary_stride_b = rotary.stride(0) if rotary.shape[0] > 1 else 0
         sp.rotary_stride_s = rotary.stride(1)
+    for name, wt in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight)):
+        if wt is not None:
+            assert wt.dtype == q.dtype and wt.is_contiguous() and wt.numel() == q.shape[3]
+            setattr(sp, name, wt.data_ptr())
+    sp.norm_eps = float(norm_eps)
     return sp
 
 
 def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, out=None, lse=None, workspace=None,
-                stream=None, flags=0):
+                stream=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6):
     """One KV-cache step in one launch (Qwen3_5.swift:167-196): rotate q and k_new with `rotary`
     ([B or 1, T_new, D], interleaved cos/sin), write rotated k_new and v_new into cache rows
     [cached_len, cached_len + T_new) and return causal attention of the rotated queries over rows
@@ -265,7 +271,7 @@ def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, ou
     if out is None:
         out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
     sp = make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, out, scale, cached_len + k_new.shape[1], True, lse,
-                          flags)
+                          flags, q_norm_weight, k_norm_weight, norm_eps)
     need = ctypes.c_size_t(0)
     _check(lib().dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)),
            "dt_sdpa_decode_step_workspace_size")

@@ -154,6 +154,12 @@ typedef struct {
   int32_t T_new;
   const void* rotary;
   int64_t rotary_stride_b, rotary_stride_s; /* stride_b 0 = one table for the whole batch */
+  /* optional per-head RMSNorm of the queries and of the new keys before the rotation (qNorm / kNorm,
+     Qwen3_5.swift:164-167): weights [D] in the tensors' dtype, y = x / sqrt(mean(x^2) + norm_eps) * weight, rounded to
+     the dtype before the rotation as the separate node does.  NULL = that tensor is not normalised. */
+  const void* q_norm_weight;
+  const void* k_norm_weight;
+  float norm_eps;
 } dt_decode_step_params;
 int dt_sdpa_decode_step_workspace_size(const dt_decode_step_params* s, size_t* bytes);
 int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspace, size_t workspace_bytes,

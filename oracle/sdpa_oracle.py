@@ -206,16 +206,18 @@ def qk_prologue_explicit(x, weight, rotary, eps, dtype, norm_per_token=False, po
     return y
 
 
-def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, dtype):
-    """The reference's KV-cache step as separate nodes (Qwen3_5.swift:167-196), every node's output rounded to
-    `dtype` as a graph of 16-bit tensors does: cmul on the queries (rotary rows of the last Sq tokens) and on the
-    new keys, new keys / values moved into the cache at row cached_len, causal attention over rows
-    [0, cached_len + T_new).  Inputs are `dtype` tensors on the CPU; k_cache / v_cache ([B, capacity, Hkv, D])
-    are updated in place.  Returns fp32 attention output computed from the rounded operands."""
+def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, dtype, q_norm_weight=None,
+                         k_norm_weight=None, norm_eps=1e-6):
+    """The reference's KV-cache step as separate nodes (Qwen3_5.swift:164-196), every node's output rounded to
+    `dtype` as a graph of 16-bit tensors does: optional qNorm / kNorm (RMSNorm over the head dim, :164-167), cmul on
+    the queries (rotary rows of the last Sq tokens) and on the new keys, new keys / values moved into the cache at row
+    cached_len, causal attention over rows [0, cached_len + T_new).  Inputs are `dtype` tensors on the CPU; k_cache /
+    v_cache ([B, capacity, Hkv, D]) are updated in place.  Returns fp32 attention output computed from the rounded
+    operands."""
     Sq, Tn = q.shape[1], k_new.shape[1]
-    rot = None if rotary is None else rotary.float()[:, :, None, :]
-    qr = q.float() if rot is None else cmul(q.float(), rot[:, Tn - Sq:]).to(dtype).float()
-    kr = k_new if rot is None else cmul(k_new.float(), rot).to(dtype)
+    rot = None if rotary is None else rotary[:, :, None, :]
+    qr = qk_prologue_explicit(q, q_norm_weight, None if rot is None else rot[:, Tn - Sq:], norm_eps, dtype)
+    kr = qk_prologue_explicit(k_new, k_norm_weight, rot, norm_eps, dtype)
     k_cache[:, cached_len:cached_len + Tn] = kr
     v_cache[:, cached_len:cached_len + Tn] = v_new
     total = cached_len + Tn

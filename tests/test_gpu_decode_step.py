@@ -133,3 +133,39 @@ def test_decode_step_argument_checks(dtattn):
     sp = dtattn.make_step_params(q, kc, vc, kn, vn, rot, o, 0.125, 66)
     sp.k_new.ptr = None
     assert lib.dt_sdpa_decode_step(ctypes.byref(sp), None, 0, None) == dtattn.DT_BAD_ARG
+
+
+@pytest.mark.parametrize("case", [
+    # B, cached, T_new, Sq, Hq, Hkv, D, dtype, rotary_dim
+    (1, 3000, 1, 1, 16, 4, 256, torch.bfloat16, 64),   # Qwen3.5: qNorm, kNorm, partial rotary, append, attention
+    (2, 700, 3, 1, 32, 8, 128, torch.float16, None),
+    (1, 0, 5, 5, 8, 4, 64, torch.bfloat16, None),
+])
+def test_decode_step_with_qk_rmsnorm(dtattn, case):
+    """qNorm / kNorm (Qwen3_5.swift:164-167) inside the step.  The RMS sum is accumulated in another order than on the
+    CPU and uses the hardware reciprocal square root, so an appended key may land on the neighbouring 16-bit value
+    (and the rotation carries that into its pair): keys within two units in the last place of their pair on at most
+    1 % of the elements, values and every other cache row bit-identical, output within the stated tolerance."""
+    B, cached, Tn, Sq, Hq, Hkv, D, dtype, rdim = case
+    q, k_cache, v_cache, k_new, v_new, rot = make_case(B, cached, Tn, Sq, Hq, Hkv, D, dtype, 801, rdim)
+    wq = (1.0 + 0.2 * so.seeded_normal((D,), 811)).to(dtype)
+    wk = (1.0 + 0.2 * so.seeded_normal((D,), 812)).to(dtype)
+    kc_ref, vc_ref = k_cache.clone(), v_cache.clone()
+    ref = so.decode_step_explicit(q, kc_ref, vc_ref, k_new, v_new, rot, D ** -0.5, cached, dtype, wq, wk, 1e-6)
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    out = dtattn.decode_step(q.to(DEV), kc, vc, k_new.to(DEV), v_new.to(DEV), rot.to(DEV), D ** -0.5, cached,
+                             q_norm_weight=wq.to(DEV), k_norm_weight=wk.to(DEV), norm_eps=1e-6)
+    torch.cuda.synchronize()
+    assert dtattn.device_status() == 0
+    assert torch.equal(vc.cpu().view(torch.int16), vc_ref.view(torch.int16))
+    got, want = kc.cpu(), kc_ref
+    keep = torch.ones(got.shape[1], dtype=torch.bool)
+    keep[cached:cached + Tn] = False
+    assert torch.equal(got[:, keep].view(torch.int16), want[:, keep].view(torch.int16)), "rows outside the append changed"
+    g, w = got[:, cached:cached + Tn].float(), want[:, cached:cached + Tn].float()
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    pair = w.abs().reshape(*w.shape[:-1], -1, 2).amax(dim=-1, keepdim=True).expand(*w.shape[:-1], -1, 2).reshape(w.shape)
+    diff = (g - w).abs()
+    assert not bool((diff > 2 * ulp * pair + 1e-30).any()), float(diff.max())
+    assert float((diff > 0).float().mean()) <= 1e-2
+    check(out, ref, dtype, str(case))
