@@ -29,7 +29,7 @@ sys.path.insert(0, os.path.join(ROOT, "draw-things-community_b200"))
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (profiles/prefill_tcgen05_flux_joint.md, profiles/decode_splitkv_gqa_8192.md); None = not captured
-NCU_TRAFFIC_BYTES = {"flux_joint": 93.3e6, "decode_b16": 541.3e6, "decode_b1": 33.6e6, "wan_self": None, "sdxl_cross": None}
+NCU_TRAFFIC_BYTES = {"flux_joint": 91.7e6, "decode_b16": 541.3e6, "decode_b1": 33.6e6, "wan_self": None, "sdxl_cross": None}
 
 METRIC = "sdpa_fwd_tflops"
 UNIT = "TFLOP/s"
