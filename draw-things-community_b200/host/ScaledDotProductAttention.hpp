@@ -163,4 +163,53 @@ class ScaledDotProductAttention {
   bool fused_projection_ = false;
 };
 
+// ---- the steps either side of the operator, as free functions over the same views --------------------------
+
+// One KV-cache step (Qwen3_5.swift:164-196): optional qNorm / kNorm, rotary cmul on the last q.S queries and the
+// new keys, append of the new rows at row `cachedLength` of the caches, causal attention over cachedLength + T_new
+// rows.  kCache / vCache are views of the whole cache (capacity rows).
+inline void decodeStep(const TensorView& q, const TensorView& kCache, const TensorView& vCache, const TensorView& kNew,
+                       const TensorView& vNew, const void* rotary, int64_t rotaryStrideB, int64_t rotaryStrideS,
+                       float scale, int cachedLength, const TensorView& out, void* workspace, size_t workspaceBytes,
+                       void* stream, const void* qNormWeight = nullptr, const void* kNormWeight = nullptr,
+                       float normEps = 1e-6f, unsigned flags = 0) {
+  dt_decode_step_params s{};
+  dt_sdpa_params& p = s.attn;
+  p.B = q.B; p.Sq = q.S; p.Sk = cachedLength + kNew.S; p.Hq = q.H; p.Hkv = kCache.H; p.D = q.D;
+  p.dtype = q.dtype; p.scale = scale; p.is_causal = 1; p.flags = flags;
+  p.q = q.abi(); p.k = kCache.abi(); p.v = vCache.abi(); p.o = out.abi();
+  s.k_new = kNew.abi(); s.v_new = vNew.abi(); s.T_new = kNew.S;
+  s.rotary = rotary; s.rotary_stride_b = rotaryStrideB; s.rotary_stride_s = rotaryStrideS;
+  s.q_norm_weight = qNormWeight; s.k_norm_weight = kNormWeight; s.norm_eps = normEps;
+  int st = dt_sdpa_decode_step(&s, workspace, workspaceBytes, stream);
+  if (st != DT_OK) throw Error(st, "dt_sdpa_decode_step");
+}
+
+// RMSNorm + rotary + pre-scale of one tensor or of queries and keys together (Flux1.swift:164-188, Wan.swift:86-98).
+struct PrologueSpec {
+  const void* normWeight = nullptr;  // [D], or [H*D] with normPerToken
+  bool normPerToken = false;
+  float eps = 1e-6f;
+  const void* rotary = nullptr;      // [B|1, S, H|1, D], interleaved (cos, sin); a broadcast axis has stride 0
+  int64_t rotaryStrideB = 0, rotaryStrideS = 0, rotaryStrideH = 0;
+  float postScale = 1.f;
+};
+inline dt_qk_prologue_params prologueParams(const TensorView& x, const TensorView& y, const PrologueSpec& spec) {
+  dt_qk_prologue_params p{};
+  p.B = x.B; p.S = x.S; p.H = x.H; p.D = x.D; p.dtype = x.dtype;
+  p.x = x.abi(); p.y = y.abi();
+  p.norm_weight = spec.normWeight; p.norm_per_token = spec.normPerToken ? 1 : 0; p.eps = spec.eps;
+  p.rotary = spec.rotary; p.rotary_stride_b = spec.rotaryStrideB; p.rotary_stride_s = spec.rotaryStrideS;
+  p.rotary_stride_h = spec.rotaryStrideH; p.post_scale = spec.postScale;
+  return p;
+}
+inline void qkPrologue(const TensorView& q, const TensorView& qOut, const PrologueSpec& qSpec, const TensorView* k,
+                       const TensorView* kOut, const PrologueSpec* kSpec, void* stream) {
+  dt_qk_prologue_params pq = prologueParams(q, qOut, qSpec);
+  dt_qk_prologue_params pk{};
+  if (k) pk = prologueParams(*k, *kOut, kSpec ? *kSpec : qSpec);
+  int st = dt_qk_prologue(&pq, k ? &pk : nullptr, stream);
+  if (st != DT_OK) throw Error(st, "dt_qk_prologue");
+}
+
 }  // namespace dt

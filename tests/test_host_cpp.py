@@ -34,6 +34,14 @@ int main() {
   if (r.S != 100 || r.ptr != buf + 16 * 8 * 128 * 2) ++fails;
   ScaledDotProductAttention masked(1.f, false, true);
   try { masked(q, k, k, q, nullptr, 0, nullptr); ++fails; } catch (const Error& e) { if (e.status != DT_BAD_ARG) ++fails; }
+  // free functions for the steps either side of the operator: argument checks happen before any launch
+  TensorView cache = TensorView::contiguous(buf, 1, 64, 8, 128, DT_F16);
+  TensorView many = TensorView::contiguous(buf, 1, 17, 8, 128, DT_F16);
+  try { decodeStep(q, cache, cache, many, many, nullptr, 0, 0, 0.1f, 10, q, nullptr, 0, nullptr); ++fails; }
+  catch (const Error& e) { if (e.status != DT_UNSUPPORTED) ++fails; }  // more new rows than one 16-key unit
+  TensorView odd = TensorView::contiguous(buf, 1, 4, 2, 60, DT_F16);
+  try { qkPrologue(odd, odd, PrologueSpec(), nullptr, nullptr, nullptr, nullptr); ++fails; }
+  catch (const Error& e) { if (e.status != DT_UNSUPPORTED) ++fails; }
   std::printf("fails=%d ws=%zu\n", fails, ws);
   return fails;
 }
