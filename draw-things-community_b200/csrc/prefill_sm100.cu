@@ -606,6 +606,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const bool guarded_main = a.off_q != nullptr && wrow0 < w.sq && !tma_ok;
 #pragma unroll
         for (int hf = 0; hf < D / 64; ++hf) {
+          // the previous TMA store of this warp (last half, or the previous item) must have read the staging rows
+          // before they are overwritten: waited for here, as late as possible, not right after issuing it
+          if (lane == 0) ptx::bulk_wait_read_all();
+          __syncwarp();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t ov[32];
@@ -648,7 +652,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               }
             }
           }
-          if (lane == 0 && tma_ok) ptx::bulk_wait_read_all();  // the staging rows may be overwritten after this
           __syncwarp();
         }
       }
