@@ -45,6 +45,15 @@ struct Cfg {
   static constexpr int kUnitsPerStage = kConsumerWarps / kDimSplit;
   static constexpr int kDW = D / kDimSplit;  // output dims accumulated by one warp
   static constexpr int kStageBytes = kUnitsPerStage * kWarpTileBytes;
+  // A stage is filled by one TMA box per (K | V, 64-dim half) that covers all its units: [K half 0][K half 1]..[V half 0]..,
+  // each kStageBox bytes = units x 16 keys x 128 bytes; unit u sits u * kBoxBytes into every box.
+  static constexpr int kStageBox = kUnitsPerStage * kBoxBytes;
+  // Measured on B200: stage-wide boxes help head dim 256 (16.4 -> 15.2 us at B=1) and cost 3 % at D=128, B=16, where
+  // one box per unit streams more evenly; so only D=256 uses them.
+  static constexpr bool kStageBoxes = D > 128;
+  static constexpr int kHalfStride = kStageBoxes ? kStageBox : kBoxBytes;   // bytes between 64-dim halves of a tile
+  static constexpr int kUnitStride = kStageBoxes ? kBoxBytes : kWarpTileBytes;  // bytes between units of a stage
+  static constexpr int kBoxRows = kStageBoxes ? kUnitKeys * kUnitsPerStage : kUnitKeys;
   static constexpr int kStages = D == 64 ? 4 : 3;
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -282,7 +291,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   // one 16-key unit: scores, online softmax, P V.  kbase / vbase: swizzled K and V tiles in shared memory.
   // Keys beyond `last_key` are masked on top of the causal rule (rows past the streamed range are TMA zero fill).
-  auto process_unit = [&](uint32_t kbase, uint32_t vbase, int key0, int last_key) {
+  // half_stride: bytes between the 64-dim halves of a tile (a whole stage box for streamed units).
+  auto process_unit = [&](uint32_t kbase, uint32_t vbase, int key0, int last_key, uint32_t half_stride) {
     const int vl_lo = min(vis_lo, last_key), vl_hi = min(vis_hi, last_key);
     float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
@@ -290,7 +300,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const int chunk = ks * 2 + ((lane >> 3) & 1);
-        const uint32_t addr = kbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        const uint32_t addr = kbase + (chunk >> 3) * half_stride + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
         uint32_t b00, b01, b10, b11;
         ptx::ldmatrix_x4(b00, b01, b10, b11, addr);
         ptx::mma_m16n8k16<kBf16>(sacc[0], qa[ks], b00, b01);
@@ -356,7 +366,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
       for (int dp = 0; dp < C::kDW / 16; ++dp) {
         const int chunk = dhalf * (C::kDW / 8) + dp * 2 + (lane >> 4);
-        const uint32_t addr = vbase + (chunk >> 3) * kBoxBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+        const uint32_t addr = vbase + (chunk >> 3) * half_stride + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
         uint32_t v00, v01, v10, v11;
         ptx::ldmatrix_x4_trans(v00, v01, v10, v11, addr);
         ptx::mma_m16n8k16<kBf16>(oacc[2 * dp], pa, v00, v01);
@@ -378,15 +388,28 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
           }
         }
         const int u0 = unit_begin + st * C::kUnitsPerStage;
-        const int nu = min(C::kUnitsPerStage, unit_end - u0);
-        ptx::mbar_arrive_expect_tx(&full_bar[slot], (uint32_t)(nu * C::kWarpTileBytes));
-        for (int w = 0; w < nu; ++w) {
-          uint8_t* dst = ring_ptr + slot * C::kStageBytes + w * C::kWarpTileBytes;
-          const int key0 = (u0 + w) * kUnitKeys;
+        if constexpr (C::kStageBoxes) {
+          // one box per (K | V, half) covers the stage's units; rows past the streamed range are zero fill and units
+          // past this split's end are simply not consumed
+          const int key0 = u0 * kUnitKeys;
+          ptx::mbar_arrive_expect_tx(&full_bar[slot], (uint32_t)C::kStageBytes);
+          uint8_t* dst = ring_ptr + slot * C::kStageBytes;
 #pragma unroll
           for (int hf = 0; hf < C::kHalves; ++hf) {
-            ptx::tma_load_4d(dst + hf * kBoxBytes, &map_k, &full_bar[slot], hf * 64, kvh, key0, b);
-            ptx::tma_load_4d(dst + (C::kHalves + hf) * kBoxBytes, &map_v, &full_bar[slot], hf * 64, kvh, key0, b);
+            ptx::tma_load_4d(dst + hf * C::kStageBox, &map_k, &full_bar[slot], hf * 64, kvh, key0, b);
+            ptx::tma_load_4d(dst + (C::kHalves + hf) * C::kStageBox, &map_v, &full_bar[slot], hf * 64, kvh, key0, b);
+          }
+        } else {
+          const int nu = min(C::kUnitsPerStage, unit_end - u0);
+          ptx::mbar_arrive_expect_tx(&full_bar[slot], (uint32_t)(nu * C::kWarpTileBytes));
+          for (int w = 0; w < nu; ++w) {
+            uint8_t* dst = ring_ptr + slot * C::kStageBytes + w * C::kWarpTileBytes;
+            const int key0 = (u0 + w) * kUnitKeys;
+#pragma unroll
+            for (int hf = 0; hf < C::kHalves; ++hf) {
+              ptx::tma_load_4d(dst + hf * kBoxBytes, &map_k, &full_bar[slot], hf * 64, kvh, key0, b);
+              ptx::tma_load_4d(dst + (C::kHalves + hf) * kBoxBytes, &map_v, &full_bar[slot], hf * 64, kvh, key0, b);
+            }
           }
         }
       }
@@ -403,8 +426,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       if (dbg && st == 0 && threadIdx.x == 0) dbg[1] = ptx::globaltimer_ns();
       const int unit = unit_begin + st * C::kUnitsPerStage + uslot;
       if (unit < unit_end) {
-        const uint32_t kbase = ring + slot * C::kStageBytes + uslot * C::kWarpTileBytes;
-        process_unit(kbase, kbase + C::kHalves * kBoxBytes, unit * kUnitKeys, a.stream_keys - 1);
+        const uint32_t kbase = ring + slot * C::kStageBytes + uslot * C::kUnitStride;
+        process_unit(kbase, kbase + C::kHalves * C::kHalfStride, unit * kUnitKeys, a.stream_keys - 1, (uint32_t)C::kHalfStride);
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
@@ -476,7 +499,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                      : "memory");
       }
       __syncwarp();
-      process_unit(tile, tile + C::kHalves * kBoxBytes, t_old, a.Sk - 1);
+      process_unit(tile, tile + C::kHalves * kBoxBytes, t_old, a.Sk - 1, (uint32_t)kBoxBytes);
     }
   }
   if (warp < kConsumerWarps) {
@@ -724,8 +747,8 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
   // another CTA of this launch is appending.  (An empty cache still needs a valid map; it is never read.)
   CUtensorMap mk, mv;
   const int map_rows = stream_keys > 0 ? stream_keys : 1;
-  if (!make_bshd_tensor_map(&mk, p.k, p.B, map_rows, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mv, p.v, p.B, map_rows, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, map_rows, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, map_rows, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
   a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
   a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
@@ -914,8 +937,8 @@ int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, c
     DT_CUDA_TRY(cudaMemsetAsync(a.counters, 0, pairs * sizeof(unsigned int), stream));
   }
   CUtensorMap mk, mv;
-  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, kUnitKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
   a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
   a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
