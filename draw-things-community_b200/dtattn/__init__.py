@@ -239,11 +239,13 @@ def sdpa_forward(q, k, v, scale, is_causal=False, mask=None, out=None, lse=None,
 
 
 def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_len, is_causal=True,
-                     lse=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6) -> DecodeStepParams:
+                     lse=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6, sinks=None,
+                     sliding_window=0) -> DecodeStepParams:
     """k_cache / v_cache: [B, capacity, Hkv, D]; the step attends over their first `total_len` rows, of which
     the last k_new.shape[1] are written by the call."""
     sp = DecodeStepParams()
-    sp.attn = make_params(q, k_cache[:, :total_len], v_cache[:, :total_len], o, scale, is_causal, None, lse, flags)
+    sp.attn = make_params(q, k_cache[:, :total_len], v_cache[:, :total_len], o, scale, is_causal, None, lse, flags, sinks,
+                          sliding_window)
     sp.k_new, sp.v_new = _view4(k_new), _view4(v_new)
     sp.T_new = k_new.shape[1]
     if rotary is not None:
@@ -261,7 +263,7 @@ def make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, o, scale, total_
 
 
 def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, out=None, lse=None, workspace=None,
-                stream=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6):
+                stream=None, flags=0, q_norm_weight=None, k_norm_weight=None, norm_eps=1e-6, sinks=None, sliding_window=0):
     """One KV-cache step in one launch (Qwen3_5.swift:167-196): rotate q and k_new with `rotary`
     ([B or 1, T_new, D], interleaved cos/sin), write rotated k_new and v_new into cache rows
     [cached_len, cached_len + T_new) and return causal attention of the rotated queries over rows
@@ -271,7 +273,7 @@ def decode_step(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, ou
     if out is None:
         out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
     sp = make_step_params(q, k_cache, v_cache, k_new, v_new, rotary, out, scale, cached_len + k_new.shape[1], True, lse,
-                          flags, q_norm_weight, k_norm_weight, norm_eps)
+                          flags, q_norm_weight, k_norm_weight, norm_eps, sinks, sliding_window)
     need = ctypes.c_size_t(0)
     _check(lib().dt_sdpa_decode_step_workspace_size(ctypes.byref(sp), ctypes.byref(need)),
            "dt_sdpa_decode_step_workspace_size")

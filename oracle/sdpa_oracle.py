@@ -207,7 +207,7 @@ def qk_prologue_explicit(x, weight, rotary, eps, dtype, norm_per_token=False, po
 
 
 def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cached_len, dtype, q_norm_weight=None,
-                         k_norm_weight=None, norm_eps=1e-6):
+                         k_norm_weight=None, norm_eps=1e-6, sinks=None, sliding_window=0):
     """The reference's KV-cache step as separate nodes (Qwen3_5.swift:164-196), every node's output rounded to
     `dtype` as a graph of 16-bit tensors does: optional qNorm / kNorm (RMSNorm over the head dim, :164-167), cmul on
     the queries (rotary rows of the last Sq tokens) and on the new keys, new keys / values moved into the cache at row
@@ -221,7 +221,8 @@ def decode_step_explicit(q, k_cache, v_cache, k_new, v_new, rotary, scale, cache
     k_cache[:, cached_len:cached_len + Tn] = kr
     v_cache[:, cached_len:cached_len + Tn] = v_new
     total = cached_len + Tn
-    return sdpa_explicit(qr.to(dtype), k_cache[:, :total], v_cache[:, :total], scale, True)
+    return sdpa_explicit(qr.to(dtype), k_cache[:, :total], v_cache[:, :total], scale, True, sinks=sinks,
+                         sliding_window=sliding_window)
 
 
 # --------------------------------------------------------------------------------------------------

@@ -169,3 +169,28 @@ def test_decode_step_with_qk_rmsnorm(dtattn, case):
     assert not bool((diff > 2 * ulp * pair + 1e-30).any()), float(diff.max())
     assert float((diff > 0).float().mean()) <= 1e-2
     check(out, ref, dtype, str(case))
+
+
+@pytest.mark.parametrize("case", [
+    # B, cached, T_new, Sq, Hq, Hkv, D, window
+    (1, 3000, 1, 1, 32, 8, 128, 128),    # only the last 128 rows are streamed
+    (2, 100, 4, 4, 8, 2, 64, 50),        # the window starts inside the cache and ends among the new rows
+    (1, 20, 3, 3, 8, 8, 128, 2),         # a window narrower than the new rows: nothing of the cache is visible
+])
+def test_decode_step_with_sinks_and_sliding_window(dtattn, case):
+    """The fused step with the operator variants of DeepSeek4.swift:482-493 (a cache, a window, sinks)."""
+    B, cached, Tn, Sq, Hq, Hkv, D, window = case
+    dtype = torch.bfloat16
+    q, k_cache, v_cache, k_new, v_new, rot = make_case(B, cached, Tn, Sq, Hq, Hkv, D, dtype, 901)
+    sinks = (so.seeded_normal((Hq,), 911) * 2.0).to(dtype)
+    kc_ref, vc_ref = k_cache.clone(), v_cache.clone()
+    ref = so.decode_step_explicit(q, kc_ref, vc_ref, k_new, v_new, rot, D ** -0.5, cached, dtype, sinks=sinks,
+                                  sliding_window=window)
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    out = dtattn.decode_step(q.to(DEV), kc, vc, k_new.to(DEV), v_new.to(DEV), rot.to(DEV), D ** -0.5, cached,
+                             sinks=sinks.to(DEV), sliding_window=window)
+    torch.cuda.synchronize()
+    assert dtattn.device_status() == 0
+    assert torch.equal(kc.cpu().view(torch.int16), kc_ref.view(torch.int16))
+    assert torch.equal(vc.cpu().view(torch.int16), vc_ref.view(torch.int16))
+    check(out, ref, dtype, str(case))
