@@ -4,6 +4,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "sm100_ptx.cuh"
@@ -333,14 +334,16 @@ int dt_host_release(void) {
 int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
   int st = validate(ph);
   if (st != DT_OK) return st;
-  if (ph->mask) return DT_UNSUPPORTED;  // masks are served by the device-tensor entry point only
+  // masks and variable-length offsets are served by the device-tensor entry point only
+  if (ph->mask || ph->n_seq || ph->seq_offsets_q || ph->seq_offsets_k) return DT_UNSUPPORTED;
   dt_sdpa_params p = *ph;
   const size_t es = dtype_size(p.dtype);
   const size_t nq = view_span(p.q, p.B, p.Sq, p.Hq, p.D) * es, nk = view_span(p.k, p.B, p.Sk, p.Hkv, p.D) * es;
   const size_t nv = view_span(p.v, p.B, p.Sk, p.Hkv, p.D) * es, no = view_span(p.o, p.B, p.Sq, p.Hq, p.D) * es;
   auto al = [](size_t x) { return (x + 255) / 256 * 256; };
   const size_t nl = p.lse ? al((size_t)p.B * p.Hq * p.Sq * 4) : 0;
-  const size_t total = al(nq) + al(nk) + al(nv) + al(no) + nl;
+  const size_t nsink = p.sinks ? (size_t)p.Hq * es : 0;
+  const size_t total = al(nq) + al(nk) + al(nv) + al(no) + nl + al(nsink);
   if (!g_hs.stream) DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.stream, cudaStreamNonBlocking));
   if (g_hs.dev_bytes < total) {
     if (g_hs.dev) cudaFree(g_hs.dev);
@@ -355,6 +358,8 @@ int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
   p.v.ptr = d; d += al(nv);
   p.o.ptr = d; d += al(no);
   if (p.lse) p.lse = reinterpret_cast<float*>(d);
+  d += nl;
+  if (p.sinks) p.sinks = d;
   size_t wsb = 0;
   st = dt_sdpa_workspace_size(&p, &wsb);
   if (st != DT_OK) return st;
@@ -367,6 +372,7 @@ int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
     DT_CUDA_TRY(cudaMemsetAsync(g_hs.ws, 0, wsb, g_hs.stream));
   }
   cudaStream_t s = g_hs.stream;
+  if (nsink) DT_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(p.sinks), ph->sinks, nsink, cudaMemcpyHostToDevice, s));
   // Pipelined path for the large tensor-core shapes: heads are independent, so the host->device copy of one
   // group of heads overlaps the attention of the previous group and the device->host copy of the one before
   // (three streams, both copy engines busy).  Needs heads contiguous inside a token row and regular rows.
@@ -379,16 +385,72 @@ int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
       return t.stride_h == p.D && t.stride_s >= (int64_t)H * p.D && (p.B == 1 || t.stride_b == (int64_t)S * t.stride_s);
     };
     const bool big = nq + nk + nv >= (size_t)(16u << 20);
-    if (groups >= 2 && big && !p.lse && choose(p) == kPrefill && regular(p.q, p.Sq, p.Hq) && regular(p.k, p.Sk, p.Hkv) &&
-        regular(p.v, p.Sk, p.Hkv) && regular(p.o, p.Sq, p.Hq)) {
-      if (!g_hs.s_in) {
-        DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_in, cudaStreamNonBlocking));
-        DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_out, cudaStreamNonBlocking));
-        for (int i = 0; i < 8; ++i) {
-          DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_in[i], cudaEventDisableTiming));
-          DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_done[i], cudaEventDisableTiming));
-        }
+    const bool pipelined = big && !p.lse && choose(p) == kPrefill && regular(p.q, p.Sq, p.Hq) &&
+                           regular(p.k, p.Sk, p.Hkv) && regular(p.v, p.Sk, p.Hkv) && regular(p.o, p.Sq, p.Hq);
+    if (pipelined && !g_hs.s_in) {
+      DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_in, cudaStreamNonBlocking));
+      DT_CUDA_TRY(cudaStreamCreateWithFlags(&g_hs.s_out, cudaStreamNonBlocking));
+      for (int i = 0; i < 8; ++i) {
+        DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_in[i], cudaEventDisableTiming));
+        DT_CUDA_TRY(cudaEventCreateWithFlags(&g_hs.ev_done[i], cudaEventDisableTiming));
       }
+    }
+    // One image, every query row sees every key (the diffusion shapes): K and V go up whole as two linear copies,
+    // then the queries in runs of whole 256-row work items, each run attended and sent back while the next one is
+    // on the bus.  Linear copies of full token rows move faster than the per-head-group 2-D copies below, and the
+    // runs shrink towards the end so that little work is left once the last query row has arrived.
+    constexpr int kItemRows = 256;
+    const int items = p.Sq / kItemRows;  // a ragged tail stays with the last run
+    if (pipelined && p.B == 1 && !p.is_causal && p.sliding_window == 0 && items >= 4 &&
+        p.q.stride_s == (int64_t)p.Hq * p.D && p.o.stride_s == (int64_t)p.Hq * p.D) {
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+      int per = std::max(1, sms / p.Hq);  // items of one run: one wave of the persistent kernel
+      if ((items + per - 1) / per > 6) per = (items + 5) / 6;
+      int runs[8], n_runs = 0, left = items;
+      while (left > per + per / 2) { runs[n_runs++] = per; left -= per; }
+      if (left >= 3) { runs[n_runs++] = (2 * left + 2) / 3; left -= runs[n_runs - 1]; }
+      runs[n_runs++] = left;
+      bool same_kernel = true;  // every run must take the tensor-core kernel within the workspace sized for the whole
+      for (int c = 0, r = 0; c < n_runs; ++c) {
+        dt_sdpa_params pc = p;
+        pc.Sq = c + 1 < n_runs ? runs[c] * kItemRows : p.Sq - r;
+        r += pc.Sq;
+        size_t w = 0;
+        same_kernel = same_kernel && choose(pc) == kPrefill && dt_sdpa_workspace_size(&pc, &w) == DT_OK && w <= g_hs.ws_bytes;
+      }
+      if (same_kernel) {
+      DT_CUDA_TRY(cudaMemcpyAsync(p.k.ptr, ph->k.ptr, nk, cudaMemcpyHostToDevice, g_hs.s_in));
+      DT_CUDA_TRY(cudaMemcpyAsync(p.v.ptr, ph->v.ptr, nv, cudaMemcpyHostToDevice, g_hs.s_in));
+      const size_t row_bytes = (size_t)p.Hq * p.D * es;
+      int r0 = 0;
+      for (int c = 0; c < n_runs; ++c) {
+        const int rows = c + 1 < n_runs ? runs[c] * kItemRows : p.Sq - r0;
+        DT_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(p.q.ptr) + r0 * row_bytes,
+                                    static_cast<const char*>(ph->q.ptr) + r0 * row_bytes, rows * row_bytes,
+                                    cudaMemcpyHostToDevice, g_hs.s_in));
+        DT_CUDA_TRY(cudaEventRecord(g_hs.ev_in[c], g_hs.s_in));
+        DT_CUDA_TRY(cudaStreamWaitEvent(s, g_hs.ev_in[c], 0));
+        dt_sdpa_params pc = p;
+        pc.Sq = rows;
+        pc.q.ptr = static_cast<char*>(p.q.ptr) + r0 * row_bytes;
+        pc.o.ptr = static_cast<char*>(p.o.ptr) + r0 * row_bytes;
+        st = dt_sdpa_forward(&pc, g_hs.ws, g_hs.ws_bytes, s);
+        if (st != DT_OK) return st;
+        DT_CUDA_TRY(cudaEventRecord(g_hs.ev_done[c], s));
+        DT_CUDA_TRY(cudaStreamWaitEvent(g_hs.s_out, g_hs.ev_done[c], 0));
+        DT_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(ph->o.ptr) + r0 * row_bytes,
+                                    static_cast<const char*>(p.o.ptr) + r0 * row_bytes, rows * row_bytes,
+                                    cudaMemcpyDeviceToHost, g_hs.s_out));
+        r0 += rows;
+      }
+      DT_CUDA_TRY(cudaStreamSynchronize(g_hs.s_out));
+      DT_CUDA_TRY(cudaStreamSynchronize(s));
+      return DT_OK;
+      }
+    }
+    if (groups >= 2 && pipelined) {
       const int hk = p.Hkv / groups, hq = hk * G;
       auto copy2d = [&](void* dst, const void* src, const dt_tensor4& t, int S, int heads, int h0, cudaMemcpyKind kind,
                         cudaStream_t cs) {
@@ -410,6 +472,7 @@ int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
         pg.k.ptr = static_cast<char*>(p.k.ptr) + (size_t)g * hk * p.D * es;
         pg.v.ptr = static_cast<char*>(p.v.ptr) + (size_t)g * hk * p.D * es;
         pg.o.ptr = static_cast<char*>(p.o.ptr) + (size_t)g * hq * p.D * es;
+        if (p.sinks) pg.sinks = static_cast<const char*>(p.sinks) + (size_t)g * hq * es;
         st = dt_sdpa_forward(&pg, g_hs.ws, g_hs.ws_bytes, s);
         if (st != DT_OK) return st;
         DT_CUDA_TRY(cudaEventRecord(g_hs.ev_done[g], s));

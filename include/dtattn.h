@@ -124,8 +124,9 @@ int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_b
    "decode_splitkv", "generic") to *name. */
 int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name);
 
-/* Same operator with HOST tensors: copies q, k, v (and mask) to device scratch it owns, runs
- * dt_sdpa_forward, copies o (and lse) back and synchronises.  This is the call a host program makes
+/* Same operator with HOST tensors: copies q, k, v (and sinks) to device scratch it owns, runs
+ * dt_sdpa_forward, copies o (and lse) back and synchronises.  Masks and variable-length offsets
+ * are refused with DT_UNSUPPORTED: they are served by the device-tensor entry point.  This is the call a host program makes
  * when its tensors live in host memory; it is the end-to-end path the benchmark times.  The scratch
  * is cached per host thread and released by dt_host_release().
  */

@@ -349,13 +349,28 @@ def test_host_entry_point(dtattn):
         out = dtattn.sdpa_forward(q, k, v, D ** -0.5, causal)
         assert not out.is_cuda
         check(out, oracle(q, k, v, D ** -0.5, causal), dtype, "host path")
-    # a large tensor-core shape takes the pipelined path (copies of one head group overlap the attention of another)
-    q, k, v = inputs(1, 2304, 2304, 16, 8, 128, torch.bfloat16, 97)
-    out = dtattn.sdpa_forward(q, k, v, 128 ** -0.5)
-    rows = torch.arange(0, 2304, 11)
-    check(out[:, rows], oracle(q[:, rows].contiguous(), k, v, 128 ** -0.5), torch.bfloat16, "host path, pipelined")
-    out2 = dtattn.sdpa_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5).cpu()
-    assert torch.equal(out, out2), "host path and device path must agree bitwise"
+    # a large tensor-core shape takes a pipelined path: one image without a causal rule sends K and V whole and the
+    # queries in runs of rows (2300 rows: the last run is ragged); a batch of two goes by head groups (copies of one
+    # group overlap the attention of another); sinks travel with both
+    for (B, S, causal, with_sinks) in [(1, 2300, False, False), (1, 2304, False, True), (2, 1152, False, True),
+                                       (1, 2304, True, False)]:
+        q, k, v = inputs(B, S, S, 16, 8, 128, torch.bfloat16, 97 + S + B)
+        sinks = (so.seeded_normal((16,), 99) * 2.0).to(torch.bfloat16) if with_sinks else None
+        out = dtattn.sdpa_forward(q, k, v, 128 ** -0.5, causal, sinks=sinks)
+        if not with_sinks:
+            rows = torch.arange(0, S, 11)
+            want = oracle(q, k, v, 128 ** -0.5, causal)[:, rows] if causal else \
+                oracle(q[:, rows].contiguous(), k, v, 128 ** -0.5)
+            check(out[:, rows], want, torch.bfloat16, "host path, pipelined")
+        out2 = dtattn.sdpa_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, causal,
+                                   sinks=None if sinks is None else sinks.cuda()).cpu()
+        assert torch.equal(out, out2), "host path and device path must agree bitwise"
+    # sinks on the plain (single-stream) host path
+    q, k, v = inputs(1, 300, 300, 4, 2, 64, torch.float16, 93)
+    sinks = (so.seeded_normal((4,), 94) * 2.0).to(torch.float16)
+    out = dtattn.sdpa_forward(q, k, v, 0.125, True, sinks=sinks)
+    ref = so.sdpa_explicit(q, k, v, 0.125, True, compute_dtype=torch.float64, sinks=sinks).float()
+    check(out, ref, torch.float16, "host path, sinks")
     assert dtattn.lib().dt_host_release() == 0
 
 
