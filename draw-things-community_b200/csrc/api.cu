@@ -21,7 +21,11 @@ int record_cuda_error(cudaError_t e) {
 }
 
 // ---- per-device status word --------------------------------------------------------------------------
+// The word lives in the library image (one copy per device that loads the library), so no entry point has to
+// allocate it.  In host code the array's name is a host-side stand-in: the device address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
 
+static __device__ __align__(256) unsigned int g_status_storage[64];
 static std::mutex g_status_mu;
 static unsigned int* g_status_words[64] = {nullptr};
 
@@ -30,12 +34,27 @@ unsigned int* device_status_word() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lk(g_status_mu);
   if (!g_status_words[dev]) {
-    unsigned int* p = nullptr;
-    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
-    if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
-    g_status_words[dev] = p;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_storage) != cudaSuccess) return nullptr;
+    g_status_words[dev] = reinterpret_cast<unsigned int*>(p);  // zero-initialised when the module is loaded
   }
   return g_status_words[dev];
+}
+
+int device_sm_count() {
+  static int counts[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return 148;
+  }
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (counts[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    counts[dev] = n;
+  }
+  return counts[dev];
 }
 
 // ---- tensor maps -------------------------------------------------------------------------------------
@@ -121,7 +140,7 @@ bool make_bshd_tensor_map(CUtensorMap* map, const dt_tensor4& t, int B, int S, i
 
 // ---- validation and dispatch -------------------------------------------------------------------------
 
-static int validate(const dt_sdpa_params* p) {
+int validate_params(const dt_sdpa_params* p) {
   if (!p) return DT_BAD_ARG;
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->D <= 0) return DT_BAD_ARG;
   if (p->Hq % p->Hkv) return DT_BAD_ARG;
@@ -135,6 +154,8 @@ static int validate(const dt_sdpa_params* p) {
   if (p->D > 256) return DT_UNSUPPORTED;
   if (p->sliding_window < 0) return DT_BAD_ARG;
   if (p->sinks && reinterpret_cast<uintptr_t>(p->sinks) % es) return DT_BAD_ARG;
+  if (p->mask && reinterpret_cast<uintptr_t>(p->mask) % es) return DT_BAD_ARG;
+  if (p->lse && reinterpret_cast<uintptr_t>(p->lse) % sizeof(float)) return DT_BAD_ARG;
   if ((p->seq_offsets_q != nullptr) != (p->seq_offsets_k != nullptr)) return DT_BAD_ARG;
   if (p->seq_offsets_q) {
     if (p->B != 1 || p->n_seq <= 0 || p->max_seq_q <= 0 || p->max_seq_k <= 0) return DT_BAD_ARG;
@@ -180,7 +201,7 @@ int dt_last_cuda_error(void) { return g_last_cuda_error; }
 int dt_abi_version(void) { return 2; }
 
 int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name) {
-  int st = validate(p);
+  int st = validate_params(p);
   if (st != DT_OK) return st;
   if (!name) return DT_BAD_ARG;
   static const char* names[3] = {"generic", "decode_splitkv", "prefill_tcgen05"};
@@ -189,7 +210,7 @@ int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name) {
 }
 
 int dt_sdpa_workspace_size(const dt_sdpa_params* p, size_t* bytes) {
-  int st = validate(p);
+  int st = validate_params(p);
   if (st != DT_OK) return st;
   if (!bytes) return DT_BAD_ARG;
   *bytes = choose(*p) == kDecode ? decode_workspace_bytes(*p) : 0;
@@ -203,7 +224,7 @@ int dt_sdpa_workspace_init(void* workspace, size_t bytes, void* cuda_stream) {
 }
 
 int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_bytes, void* cuda_stream) {
-  int st = validate(p);
+  int st = validate_params(p);
   if (st != DT_OK) return st;
   cudaStream_t stream = (cudaStream_t)cuda_stream;
   switch (choose(*p)) {
@@ -226,7 +247,7 @@ static int validate_proj(const dt_sdpa_params* p_in, const dt_out_proj* proj) {
   if (!p_in) return DT_BAD_ARG;
   const dt_sdpa_params t = with_placeholder_o(p_in);
   const dt_sdpa_params* p = &t;
-  int st = validate(p);
+  int st = validate_params(p);
   if (st != DT_OK) return st;
   if (!proj || !proj->weight || !proj->out.ptr || proj->C <= 0) return DT_BAD_ARG;
   if (p->dtype != DT_F16 && p->dtype != DT_BF16) return DT_UNSUPPORTED;
@@ -332,7 +353,7 @@ int dt_host_release(void) {
 }
 
 int dt_sdpa_forward_host(const dt_sdpa_params* ph) {
-  int st = validate(ph);
+  int st = validate_params(ph);
   if (st != DT_OK) return st;
   // masks and variable-length offsets are served by the device-tensor entry point only
   if (ph->mask || ph->n_seq || ph->seq_offsets_q || ph->seq_offsets_k) return DT_UNSUPPORTED;

@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <stdlib.h>
 #include <string.h>
 
 #include <chrono>
@@ -37,8 +38,11 @@ NcclApi& nccl() {
   static bool tried = false;
   if (tried) return api;
   tried = true;
-  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  // DTATTN_NCCL_LIB names the NCCL build to load (a deployment with several NCCLs; the failure-path tests point it
+  // at a stand-in whose communicator never becomes ready); otherwise the one already in the process or on the path.
+  const char* names[] = {getenv("DTATTN_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
   for (const char* n : names) {
+    if (!n || !*n) continue;
     api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
     if (api.handle) break;
   }
@@ -76,6 +80,7 @@ struct Comm {
   } regs[kMaxRegs];
   int n_regs = 0;
   int* flag = nullptr;               // 4 bytes for the in-stream rendezvous after a fused step
+  int last_fused_reg = -1;           // registered buffer the previous fused call stored into (-1: none yet)
   unsigned long long proj_calls = 0; // projected head-sharded calls so far: picks the half of the receive buffer
   void* xchg = nullptr;              // small device buffer for exchanging handles
 };
@@ -163,8 +168,6 @@ int dt_comm_init(void** comm_out, int rank, int world, const void* unique_id_128
   *comm_out = nullptr;
   NcclApi& api = nccl();
   if (!api.ok) return DT_NCCL;
-  int ndev = 0;
-  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return DT_NO_DEVICE;
   Comm* c = new Comm();
   c->rank = rank;
   c->world = world;
@@ -288,7 +291,9 @@ int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tens
   NcclApi& api = nccl();
   if (!api.ok) return DT_NCCL;
   if (chunks <= 0 || chunks > kMaxChunks) return DT_BAD_ARG;
-  if (local->is_causal && chunks != 1) return DT_UNSUPPORTED;  // a row chunk would shift the causal diagonal
+  // A row chunk is a call of its own with fewer query rows: that would shift the bottom-right causal diagonal and the
+  // sliding window, and packed sequences cannot be cut at arbitrary rows.  Those calls run as one piece.
+  if (local->is_causal || local->sliding_window > 0 || local->seq_offsets_q) chunks = 1;
   if (local->mask || local->lse) return DT_UNSUPPORTED;
   // ---- fused mode: o_full was registered on every rank -> the epilogue stores each O tile into all ranks'
   // buffers while the tensor cores work on the next tile; one small in-stream rendezvous ends the step ----
@@ -306,7 +311,19 @@ int dt_sdpa_forward_headsharded(void* comm, const dt_sdpa_params* local, dt_tens
     for (int q = 0; q < c->world; ++q)
       if (q != c->rank) extra[n_extra++] = static_cast<char*>(reg.peer[q]) + head_off;
     cudaStream_t fs = (cudaStream_t)cuda_stream;
-    int st2 = launch_prefill(p, fs, extra, n_extra);
+    int st2 = DT_OK;
+    if (c->world > 1 && c->last_fused_reg == i) {
+      // The same buffer as in the previous call: a rank that runs ahead would store this call's tiles into a slower
+      // rank's buffer while that rank's stream still reads the previous result.  A rendezvous in front of the kernel
+      // holds every rank's stores back until all ranks' streams have got here, i.e. past their readers of the
+      // previous result.  Callers that alternate between two registered buffers never pay for it: the rendezvous
+      // that ended the call in between already gives that order.
+      ncclResult_t r0 = api.AllReduce(c->flag, c->flag, 1, ncclInt, ncclSum, c->comm, fs);
+      st2 = wait_nccl(c, r0, c->timeout_ms);
+      if (st2 != DT_OK) return st2;
+    }
+    c->last_fused_reg = i;
+    st2 = launch_prefill(p, fs, extra, n_extra);
     if (st2 != DT_OK) return st2;
     if (c->world > 1) {
       // kernel completion makes this rank's peer stores visible; after the rendezvous every rank's have landed

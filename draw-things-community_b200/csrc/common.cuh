@@ -15,6 +15,9 @@ namespace dt {
 //        5 = final-O wait.  The word keeps the first code stored.
 unsigned int* device_status_word();  // device pointer for the current device (allocated once)
 
+// Multiprocessor count of the current device (looked up once per device; 148 when there is no usable device).
+int device_sm_count();
+
 // Remember a failing cudaError_t for dt_last_cuda_error().
 int record_cuda_error(cudaError_t e);
 
@@ -31,12 +34,16 @@ inline size_t dtype_size(int dtype) { return dtype == DT_F32 ? 4 : 2; }
 // CUDA-core flash kernel: any D <= 256, any dtype, mask, causal, GQA.  Fallback and second opinion.
 int launch_generic(const dt_sdpa_params& p, cudaStream_t stream);
 
-// Split-KV decode: Sq * (Hq/Hkv) <= 16 query rows per KV head, fp16/bf16, D in {64,128}.
+// Argument rules every attention entry point shares (null or misaligned pointers, extents, NaN scale, negative
+// window, variable-length bookkeeping): DT_OK, DT_BAD_ARG or DT_UNSUPPORTED.  Nothing is launched.
+int validate_params(const dt_sdpa_params* p);
+
+// Split-KV decode: Sq * (Hq/Hkv) <= 16 query rows per KV head, fp16/bf16, D in {64,128,256}.
 bool decode_supported(const dt_sdpa_params& p);
 size_t decode_workspace_bytes(const dt_sdpa_params& p);
 int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream);
 
-// TMA + tcgen05 flash attention: fp16/bf16, D in {64,128}, no mask.
+// TMA + tcgen05 flash attention: fp16/bf16, D <= 128 (a multiple of 8), optional 16-byte aligned additive mask.
 bool prefill_supported(const dt_sdpa_params& p);
 // extra_outputs: up to 7 more [B,Sq,Hq,D] views with the same strides as p.o (other GPUs' buffers in the
 // head-sharded mode) that receive a copy of every O tile.

@@ -12,10 +12,15 @@
 //           owns one 16-key unit per stage: S^T = Q K^T and O += P V with mma.sync m16n8k16 (fp32
 //           accumulate) fed by ldmatrix from the swizzled tiles, online softmax in registers with
 //           warp-shuffle reductions.
-//   merge = the 4 warps' (m, l, O) are merged through shared memory; with more than one split the CTA
-//           writes an fp32 partial to the workspace and takes a ticket (atomicAdd); the CTA that draws
-//           the last ticket of its (batch, KV head) combines all partials.  Nothing waits on another
-//           CTA, so nothing can hang.
+//   merge = the 4 warps' (m, l, O) are merged through shared memory.  The splits of one (batch, KV head) are
+//           launched as thread-block clusters of up to 16 CTAs along the split axis: after a cluster barrier
+//           every CTA of a cluster combines its share of the output elements straight out of the other CTAs'
+//           shared memory (distributed shared memory, ordinary ld.shared::cluster loads).  When one cluster
+//           covers all splits the result goes to the output at once and no partial ever reaches global
+//           memory; otherwise each cluster writes ONE fp32 partial to the workspace and takes a ticket
+//           (atomicAdd), and the cluster that draws the last ticket of its (batch, KV head) combines the
+//           partials.  Apart from the hardware cluster barrier (which every CTA reaches unconditionally, also
+//           after a wait that ran out) nothing waits on another CTA, so nothing can hang.
 #include <stdlib.h>
 
 #include <mutex>
@@ -65,10 +70,12 @@ struct DecodeArgs {
   float* lse;
   int64_t q_sb, q_ss, q_sh, o_sb, o_ss, o_sh;
   unsigned int* counters;  // [B*Hkv]
-  float* part_ml;          // [B*Hkv][nsplit][M][2]
-  float* part_o;           // [B*Hkv][nsplit][M][D]
+  float* part_ml;          // [B*Hkv][nparts][M][2]
+  float* part_o;           // [B*Hkv][nparts][M][D]
   unsigned int* status;
+#ifdef DT_BRINGUP
   unsigned long long* dbg;  // optional per-CTA timeline (bring-up probe)
+#endif
   // decode-step fusion (all null / 0 for a plain attention call): new K/V rows to rotate, append and attend
   const void* k_new; const void* v_new; const void* rotary; void* k_cache; void* v_cache;
   int64_t kn_sb, kn_ss, kn_sh, vn_sb, vn_ss, vn_sh, rot_sb, rot_ss, kc_sb, kc_ss, kc_sh, vc_sb, vc_ss, vc_sh;
@@ -82,9 +89,17 @@ struct DecodeArgs {
   float norm_eps;
   int Tn;           // new rows appended by the step fusion (<= 16), 0 otherwise
   int nsplit, units_per_split, total_units;
+  int cluster;  // CTAs per cluster along the split axis (1 = no cluster); divides nsplit
+  int nparts;   // partials per (batch, KV head) that go through global memory: nsplit / cluster
   float scale_log2;
   int is_causal;
 };
+
+#ifdef DT_BRINGUP
+#define DT_STAMP(slot) do { if (dbg && threadIdx.x == 0) dbg[slot] = ptx::globaltimer_ns(); } while (0)
+#else
+#define DT_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   if (bf16) {
@@ -173,8 +188,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+#ifdef DT_BRINGUP
   unsigned long long* dbg = a.dbg ? a.dbg + ((size_t)(b * gridDim.y + kvh) * gridDim.x + split) * 8 : nullptr;
-  if (dbg && threadIdx.x == 0) dbg[0] = ptx::globaltimer_ns();
+#endif
+  DT_STAMP(0);
   const int unit_begin = a.unit_first + split * a.units_per_split;
   const int unit_end = min(a.total_units, unit_begin + a.units_per_split);
   const int n_units = max(0, unit_end - unit_begin);
@@ -423,7 +440,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         s_abort = 1;
         break;
       }
-      if (dbg && st == 0 && threadIdx.x == 0) dbg[1] = ptx::globaltimer_ns();
+      if (st == 0) DT_STAMP(1);
       const int unit = unit_begin + st * C::kUnitsPerStage + uslot;
       if (unit < unit_end) {
         const uint32_t kbase = ring + slot * C::kStageBytes + uslot * C::kUnitStride;
@@ -511,10 +528,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   // ---------------- merge the consumer warps through shared memory (ring is idle now) ----------------
   __syncthreads();
-  if (dbg && threadIdx.x == 0) dbg[2] = ptx::globaltimer_ns();
-  float* obuf = reinterpret_cast<float*>(ring_ptr);                    // [4][16][D]
+  DT_STAMP(2);
+  float* obuf = reinterpret_cast<float*>(ring_ptr);                    // [units per stage][16][D]
   float* mbuf = obuf + C::kUnitsPerStage * kMaxRows * D;               // [units per stage][16]
   float* lbuf = mbuf + C::kUnitsPerStage * kMaxRows;                   // [units per stage][16]
+  float* cta_o = lbuf + C::kUnitsPerStage * kMaxRows;                  // [16][D]  this CTA's merged O (cluster mode)
+  float* cta_ml = cta_o + kMaxRows * D;                                // [16][2]  this CTA's merged (m, l)
+  float* comb = cta_ml + 2 * kMaxRows;                                 // scratch of the final combine
   if (warp < kConsumerWarps) {
     const int r_lo = lane >> 2, r_hi = r_lo + 8, cq = (lane & 3) * 2;
     float* ob = obuf + uslot * kMaxRows * D + dhalf * C::kDW;
@@ -537,8 +557,17 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   __syncthreads();
 
   const int pair = b * a.Hkv + kvh;
+  const int MD = a.M * D;
   T* o = reinterpret_cast<T*>(a.o);
-  for (int idx = threadIdx.x; idx < a.M * D; idx += kThreads) {
+  // final result of one output element: sink, normalisation, store (and the row's log-sum-exp once per row)
+  auto store_final = [&](int r, int d, float mstar, float lt, float ot) {
+    const int sq = r / a.G, h = kvh * a.G + r % a.G;
+    if (a.sinks) sink_merge(to_float(reinterpret_cast<const T*>(a.sinks)[h]), mstar, lt, ot);
+    o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
+    if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+  };
+  const int part = split / a.cluster;  // which of the pair's global partials this CTA contributes to
+  for (int idx = threadIdx.x; idx < MD; idx += kThreads) {
     const int r = idx / D, d = idx - r * D;
     float mstar = -INFINITY;
 #pragma unroll
@@ -552,60 +581,121 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         ot += wgt * obuf[(w * kMaxRows + r) * D + d];
       }
     }
-    if (a.nsplit == 1) {
-      const int sq = r / a.G, h = kvh * a.G + r % a.G;
-      if (a.sinks) sink_merge(to_float(reinterpret_cast<const T*>(a.sinks)[h]), mstar, lt, ot);
-      o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
-      if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+    if (a.cluster > 1) {
+      cta_o[idx] = ot;
+      if (d == 0) {
+        cta_ml[2 * r] = mstar;
+        cta_ml[2 * r + 1] = lt;
+      }
+    } else if (a.nsplit == 1) {
+      store_final(r, d, mstar, lt, ot);
     } else {
-      const int64_t slot = (int64_t)pair * a.nsplit + split;
-      a.part_o[slot * a.M * D + idx] = ot;
+      const int64_t slot = (int64_t)pair * a.nparts + part;
+      a.part_o[slot * MD + idx] = ot;
       if (d == 0) {
         a.part_ml[(slot * a.M + r) * 2] = mstar;
         a.part_ml[(slot * a.M + r) * 2 + 1] = lt;
       }
     }
   }
-  if (a.nsplit == 1) return;
+  if (a.cluster == 1 && a.nsplit == 1) return;
 
-  // ---------------- ticket: the last CTA of this (batch, KV head) combines ----------------
-  if (dbg && threadIdx.x == 0) dbg[3] = ptx::globaltimer_ns();
+  bool leader = true;  // the CTA that takes the ticket for its partial
+  if (a.cluster > 1) {
+    // ---------------- cluster combine through distributed shared memory ----------------
+    // Every CTA of the cluster gets here whatever happened before (a wait that ran out falls through to this
+    // point), so the hardware barrier always completes.  After it, CTA c of the cluster owns output elements
+    // [c * per, (c + 1) * per) and reads them, and every CTA's (m, l), from all the cluster's shared memories.
+    ptx::cluster_sync();
+    DT_STAMP(3);
+    const int crank = (int)ptx::cluster_ctarank();
+    const int per = (MD + a.cluster - 1) / a.cluster;
+    const uint32_t o_local = ptx::smem_u32(cta_o), ml_local = ptx::smem_u32(cta_ml);
+    const int idx_end = min(MD, (crank + 1) * per);
+    for (int idx = crank * per + threadIdx.x; idx < idx_end; idx += kThreads) {
+      const int r = idx / D, d = idx - r * D;
+      float mv[16], lv[16], ov[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        if (c < a.cluster) {
+          const uint32_t ml_remote = ptx::map_to_cta(ml_local + (uint32_t)r * 8u, (uint32_t)c);
+          mv[c] = ptx::ld_cluster_f32(ml_remote);
+          lv[c] = ptx::ld_cluster_f32(ml_remote + 4u);
+          ov[c] = ptx::ld_cluster_f32(ptx::map_to_cta(o_local + (uint32_t)idx * 4u, (uint32_t)c));
+        } else {
+          mv[c] = -INFINITY;
+          lv[c] = 0.f;
+          ov[c] = 0.f;
+        }
+      }
+      float mstar = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) mstar = fmaxf(mstar, mv[c]);
+      float lt = 0.f, ot = 0.f;
+      if (mstar != -INFINITY) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float wgt = fast_exp2(mv[c] - mstar);  // exp2(-inf) = 0 for the unused slots
+          lt = fmaf(wgt, lv[c], lt);
+          ot = fmaf(wgt, ov[c], ot);
+        }
+      }
+      if (a.nparts == 1) {
+        store_final(r, d, mstar, lt, ot);
+      } else {
+        const int64_t slot = (int64_t)pair * a.nparts + part;
+        a.part_o[slot * MD + idx] = ot;
+        if (d == 0) {
+          a.part_ml[(slot * a.M + r) * 2] = mstar;
+          a.part_ml[(slot * a.M + r) * 2 + 1] = lt;
+        }
+      }
+    }
+    // No CTA may exit while another still reads its shared memory; with several clusters per (batch, KV head) the
+    // barrier also orders every CTA's slice of the partial (made visible by the fence) before the leader's ticket.
+    if (a.nparts > 1) __threadfence();
+    ptx::cluster_sync();
+    DT_STAMP(4);
+    if (a.nparts == 1) return;
+    leader = crank == 0;
+  }
+  if (!leader) return;
+
+  // ---------------- ticket: the last partial of this (batch, KV head) to arrive combines ----------------
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned int ticket = atomicAdd(&a.counters[pair], 1u);
-    s_is_last = (ticket == (unsigned int)(a.nsplit - 1));
+    s_is_last = (ticket == (unsigned int)(a.nparts - 1));
   }
   __syncthreads();
-  if (dbg && threadIdx.x == 0) dbg[4] = ptx::globaltimer_ns();
   if (!s_is_last) return;
   __threadfence();
-  // Combine.  All loads of a phase are independent so they overlap: first every (split, row) pair's (m, l) lands in
-  // shared memory and one warp per row turns them into weights (lanes over splits, shuffle reductions); then each
-  // thread owns one float4 of one output row and streams the splits' partial O, 32 loads in flight.  (Issuing the
-  // partial-O loads before the weights were known measured slower: 15.5 us instead of 14.1 at B=1.)
+  // Combine.  All loads of a phase are independent so they overlap: first every (partial, row) pair's (m, l) lands in
+  // shared memory and one warp per row turns them into weights (lanes over partials, shuffle reductions); then each
+  // thread owns one float4 of one output row and streams the partial O, 32 loads in flight.
   {
-    const int64_t base = (int64_t)pair * a.nsplit;
-    float* wbuf = reinterpret_cast<float*>(ring_ptr);   // [nsplit][M] weights
-    float* lsm = wbuf + a.nsplit * a.M;                  // [nsplit][M] l
-    float* rowinfo = lsm + a.nsplit * a.M;               // [M][2]: m*, L
-    const int nm = a.nsplit * a.M;
+    const int np = a.nparts;
+    const int64_t base = (int64_t)pair * np;
+    float* wbuf = comb;                      // [np][M] weights
+    float* lsm = wbuf + np * a.M;            // [np][M] l
+    float* rowinfo = lsm + np * a.M;         // [M][2]: m*, L
+    const int nm = np * a.M;
     constexpr int kVec = D / 4;
-    const int64_t split_stride = (int64_t)a.M * kVec;
+    const int64_t part_stride = (int64_t)a.M * kVec;
     for (int idx = threadIdx.x; idx < nm; idx += kThreads) {
       const float2 ml = __ldcg(reinterpret_cast<const float2*>(&a.part_ml[(base * a.M + idx) * 2]));
       wbuf[idx] = ml.x;
       lsm[idx] = ml.y;
     }
     __syncthreads();
-    if (dbg && threadIdx.x == 0) dbg[6] = ptx::globaltimer_ns();
     for (int r = warp; r < a.M; r += kThreads / 32) {
       float mstar = -INFINITY;
-      for (int sp = lane; sp < a.nsplit; sp += 32) mstar = fmaxf(mstar, wbuf[sp * a.M + r]);
+      for (int sp = lane; sp < np; sp += 32) mstar = fmaxf(mstar, wbuf[sp * a.M + r]);
 #pragma unroll
       for (int o2 = 16; o2 > 0; o2 >>= 1) mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, o2));
       float lt = 0.f;
-      for (int sp = lane; sp < a.nsplit; sp += 32) {
+      for (int sp = lane; sp < np; sp += 32) {
         const float wgt = mstar == -INFINITY ? 0.f : fast_exp2(wbuf[sp * a.M + r] - mstar);
         wbuf[sp * a.M + r] = wgt;
         lt += wgt * lsm[sp * a.M + r];
@@ -613,11 +703,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
       for (int o2 = 16; o2 > 0; o2 >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o2);
       if (a.sinks) {
-        // the sink is one more partial: weight 1 for it, every split's weight rescaled to the common max
+        // the sink is one more partial: weight 1 for it, every partial's weight rescaled to the common max
         const float sl = to_float(reinterpret_cast<const T*>(a.sinks)[kvh * a.G + r % a.G]) * kLog2e;
         const float m2 = fmaxf(mstar, sl);
         const float down = mstar == -INFINITY ? 0.f : fast_exp2(mstar - m2);
-        for (int sp = lane; sp < a.nsplit; sp += 32) wbuf[sp * a.M + r] *= down;
+        for (int sp = lane; sp < np; sp += 32) wbuf[sp * a.M + r] *= down;
         lt = lt * down + fast_exp2(sl - m2);
         mstar = m2;
       }
@@ -627,19 +717,18 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
     }
     __syncthreads();
-    if (dbg && threadIdx.x == 0) dbg[7] = ptx::globaltimer_ns();
     for (int item = threadIdx.x; item < a.M * kVec; item += kThreads) {
       const int r = item / kVec, d4 = item - r * kVec;
       const float4* src = reinterpret_cast<const float4*>(a.part_o) + (base * a.M + r) * kVec + d4;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int s0 = 0; s0 < a.nsplit; s0 += 32) {  // up to 32 independent loads in flight per thread
+      for (int s0 = 0; s0 < np; s0 += 32) {  // up to 32 independent loads in flight per thread
         float4 v[32];
 #pragma unroll
         for (int u = 0; u < 32; ++u)
-          v[u] = (s0 + u < a.nsplit) ? __ldcg(src + (s0 + u) * split_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[u] = (s0 + u < np) ? __ldcg(src + (s0 + u) * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
-          const float wgt = (s0 + u < a.nsplit) ? wbuf[(s0 + u) * a.M + r] : 0.f;
+          const float wgt = (s0 + u < np) ? wbuf[(s0 + u) * a.M + r] : 0.f;
           acc.x = fmaf(wgt, v[u].x, acc.x);
           acc.y = fmaf(wgt, v[u].y, acc.y);
           acc.z = fmaf(wgt, v[u].z, acc.z);
@@ -657,32 +746,61 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       if (a.lse && d4 == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
     }
   }
-  if (dbg && threadIdx.x == 0) dbg[5] = ptx::globaltimer_ns();
+  DT_STAMP(5);
   if (threadIdx.x == 0) a.counters[pair] = 0u;  // leave the workspace ready for the next call
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+#ifndef DT_DECODE_MAX_CLUSTER
+#define DT_DECODE_MAX_CLUSTER 16
+#endif
+constexpr int kMaxParts = 256;    // partials per (batch, KV head) the final combine has shared memory for
+constexpr int kMaxDevices = 64;
+constexpr int kVariants = 6;      // (fp16 | bf16) x (D = 64, 128, 256)
+
+// What the host side remembers per device: cudaFuncSetAttribute and the cluster occupancy answer are per device,
+// and a process may drive several devices (one host thread per GPU).
+struct DeviceState {
+  int sm_count = 0;
+  bool attr_set[kVariants] = {false, false, false, false, false, false};
+  int max_cluster[kVariants] = {0, 0, 0, 0, 0, 0};  // 0 = not asked yet
+  unsigned char* noalloc_scratch = nullptr;         // device addresses of the built-in scratch and its status word
+  unsigned int* noalloc_status = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mu;
+
+// Current device's slot, or null when there is no usable device (sizes are then computed for a 148-SM part).
+DeviceState* device_state() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return nullptr;
   }
-  return n;
+  DeviceState* d = &g_dev[dev];
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (d->sm_count == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    d->sm_count = n;
+  }
+  return d;
 }
 
+int sm_count() {
+  DeviceState* d = device_state();
+  return d ? d->sm_count : 148;
+}
+
+#ifdef DT_BRINGUP
 unsigned long long* g_decode_dbg = nullptr;
+#endif
 
 struct Plan {
   int nsplit, units_per_split, total_units;
+  int cluster;  // CTAs per cluster wanted (a power of two that divides nsplit); the launch may have to use fewer
 };
-
-// Split count: the path is bound by HBM, and what costs is the fixed part of a CTA (start-up, merge,
-// ticket, combine), so use as few CTAs as keep every SM streaming: the largest power of two with
-// pairs * splits <= the CTAs that are resident at once (one wave), and at least four 16-key units per
-// split.  (Measured on B200: B=16 runs at 99% of the copy peak with 2 splits and at 57% with 37.)
 
 // first 16-key unit any row of the call can see: row 0's window bound
 int first_unit(const dt_sdpa_params& p) {
@@ -691,8 +809,19 @@ int first_unit(const dt_sdpa_params& p) {
   return lo <= 0 ? 0 : (int)(lo / kUnitKeys);
 }
 
+int largest_cluster(int nsplit, int cap) {
+  int c = 1;
+  while (c * 2 <= cap && nsplit % (c * 2) == 0) c *= 2;
+  return c;
+}
+
+// Split count: the path is bound by HBM, and what costs is the fixed part of a CTA (start-up, merge, combine), so
+// use as few CTAs as keep every SM streaming: the largest power of two with pairs * splits <= the CTAs that are
+// resident at once (one wave), and at least four 16-key units per split.  (Measured on B200: B=16 runs at 99% of
+// the copy peak with 2 splits and at 57% with 37.)  The caller may fix the count with DT_FLAG_DECODE_SPLITS.
 Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
   Plan pl;
+  pl.cluster = 1;
   pl.total_units = (stream_keys + kUnitKeys - 1) / kUnitKeys - min((stream_keys + kUnitKeys - 1) / kUnitKeys, first_unit(p));
   if (pl.total_units == 0) {  // empty cache (first step of a sequence): one CTA per pair, nothing streamed
     pl.nsplit = 1;
@@ -704,44 +833,127 @@ Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
   const int slots = (p.D > 128 ? 1 : 2) * sm_count();
   int ns = 1;
   while (pairs * ns * 2 <= slots && pl.total_units / (ns * 2) >= 4) ns *= 2;
-  const char* env = getenv("DTATTN_DECODE_SPLITS");
-  const int forced = env ? atoi(env) : 0;
-  if (forced > 0) ns = forced < pl.total_units ? forced : pl.total_units;
+#ifdef DT_DECODE_ONE_CLUSTER
+  // variant: never more splits than one cluster holds, so that no partial goes through global memory
+  if (ns > DT_DECODE_MAX_CLUSTER) ns = DT_DECODE_MAX_CLUSTER;
+#endif
+  int forced = (int)((p.flags >> 16) & 0xFFFu);
+#ifdef DT_BRINGUP
+  if (const char* env = getenv("DTATTN_DECODE_SPLITS")) forced = atoi(env);
+#endif
+  if (forced > 0) ns = min(min(forced, kMaxParts), pl.total_units);
   if (pairs > kMaxSplitPairs) ns = 1;  // more (batch, KV head) pairs than counters: plenty of CTAs anyway
   pl.units_per_split = (pl.total_units + ns - 1) / ns;
-  pl.nsplit = (pl.total_units + pl.units_per_split - 1) / pl.units_per_split;
+  // a power-of-two count is kept as it is (trailing splits may be empty) so that it still forms clusters
+  pl.nsplit = (ns & (ns - 1)) == 0 ? ns : (pl.total_units + pl.units_per_split - 1) / pl.units_per_split;
+  int cap = DT_DECODE_MAX_CLUSTER;
+#ifdef DT_BRINGUP
+  if (const char* env = getenv("DTATTN_DECODE_CLUSTER")) cap = max(1, atoi(env));
+#endif
+  pl.cluster = largest_cluster(pl.nsplit, cap);
   return pl;
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-size_t plan_workspace_bytes(const dt_sdpa_params& p, const Plan& pl) {
-  if (pl.nsplit <= 1) return 0;
+// Bytes of scratch for `nparts` global partials per (batch, KV head).
+size_t scratch_bytes(const dt_sdpa_params& p, int nparts) {
+  if (nparts <= 1) return 0;
   const size_t pairs = (size_t)p.B * p.Hkv;
   const size_t M = (size_t)p.Sq * (p.Hq / p.Hkv);
-  return kCounterBytes + align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256) +
-         align_up(pairs * pl.nsplit * M * p.D * sizeof(float), 256);
+  return kCounterBytes + align_up(pairs * nparts * M * 2 * sizeof(float), 256) +
+         align_up(pairs * nparts * M * p.D * sizeof(float), 256);
+}
+
+// What dt_sdpa_workspace_size reports: enough for every cluster size the launch may end up with (a device that
+// cannot co-schedule the wanted cluster falls back to a smaller one and then writes more partials).
+size_t plan_workspace_bytes(const dt_sdpa_params& p, const Plan& pl) { return scratch_bytes(p, pl.nsplit); }
+
+// Where the partials live: the caller's workspace, or the library's built-in array (dt_sdpa_decode_noalloc).
+struct Scratch {
+  void* ptr;
+  size_t bytes;
+  unsigned int* status;    // device status word the kernel reports to
+  bool stale;              // the memory keeps an earlier call's contents: clear the ticket counters first
+  int too_small;           // status returned when the partials do not fit
+};
+
+template <typename T, int D>
+constexpr int variant_index() {
+  return (std::is_same<T, __half>::value ? 0 : 3) + (D == 64 ? 0 : D == 128 ? 1 : 2);
+}
+
+// Largest cluster size <= `want` this device can co-schedule for this kernel (asked once per device and variant).
+template <typename T, int D>
+int usable_cluster(DeviceState* dev, int want) {
+  using C = Cfg<D>;
+  constexpr int vi = variant_index<T, D>();
+  auto kern = decode_splitkv_kernel<T, D>;
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (dev->max_cluster[vi] == 0) {
+    int best = 1;
+    for (int c = DT_DECODE_MAX_CLUSTER; c > 1; c /= 2) {
+      if (c > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        continue;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(c, 1, 1);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = C::kSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = c;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) {
+        best = c;
+        break;
+      }
+      cudaGetLastError();
+    }
+    dev->max_cluster[vi] = best;
+  }
+  int c = want;
+  while (c > dev->max_cluster[vi]) c /= 2;
+  return c < 1 ? 1 : c;
 }
 
 template <typename T, int D>
-int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* workspace, size_t bytes,
-             cudaStream_t stream) {
+int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, const Scratch& scratch, cudaStream_t stream) {
   using C = Cfg<D>;
+  DeviceState* dev = device_state();
+  if (!dev) return DT_NO_DEVICE;
+  auto kern = decode_splitkv_kernel<T, D>;
+  constexpr int vi = variant_index<T, D>();
+  {
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    if (!dev->attr_set[vi]) {
+      DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+      dev->attr_set[vi] = true;
+    }
+  }
   const int Tn = step ? step->T_new : 0;
   const int stream_keys = p.Sk - Tn;
   const Plan pl = make_plan(p, stream_keys);
   const int G = p.Hq / p.Hkv, M = p.Sq * G;
   const size_t pairs = (size_t)p.B * p.Hkv;
   DecodeArgs a{};
-  if (pl.nsplit > 1) {
-    const size_t need = plan_workspace_bytes(p, pl);
-    if (!workspace || bytes < need) return DT_WORKSPACE;
-    uint8_t* w = reinterpret_cast<uint8_t*>(workspace);
+  a.cluster = pl.cluster > 1 ? usable_cluster<T, D>(dev, pl.cluster) : 1;
+  a.nparts = pl.nsplit / a.cluster;
+  if (a.nparts > 1) {
+    const size_t need = scratch_bytes(p, a.nparts);
+    if (!scratch.ptr || scratch.bytes < need) return scratch.too_small;
+    uint8_t* w = reinterpret_cast<uint8_t*>(scratch.ptr);
     a.counters = reinterpret_cast<unsigned int*>(w);
     size_t off = kCounterBytes;
     a.part_ml = reinterpret_cast<float*>(w + off);
-    off += align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256);
+    off += align_up(pairs * a.nparts * M * 2 * sizeof(float), 256);
     a.part_o = reinterpret_cast<float*>(w + off);
+    if (scratch.stale) DT_CUDA_TRY(cudaMemsetAsync(a.counters, 0, pairs * sizeof(unsigned int), stream));
   }
   // The maps cover exactly the streamed rows: what a unit reads past them is TMA zero fill, never the rows
   // another CTA of this launch is appending.  (An empty cache still needs a valid map; it is never read.)
@@ -752,9 +964,11 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
   a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
   a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
-  a.status = device_status_word();
+  a.status = scratch.status;
   if (!a.status) return DT_CUDA;
+#ifdef DT_BRINGUP
   a.dbg = g_decode_dbg;
+#endif
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
   a.stream_keys = stream_keys;
   a.Tn = Tn;
@@ -775,29 +989,28 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, void* w
   a.sinks = p.sinks;
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
-  auto kern = decode_splitkv_kernel<T, D>;
-  static bool attr_set = false;  // per (T, D) instantiation
-  if (!attr_set) {
-    DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    attr_set = true;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.nsplit, p.Hkv, p.B);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (a.cluster > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = a.cluster;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
-  dim3 grid(pl.nsplit, p.Hkv, p.B);
   if (p.flags & DT_FLAG_KV_PREFIX_STABLE) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = C::kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mk, mv, a));
-    return DT_OK;
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
   }
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mk, mv, a);
-  DT_CUDA_TRY(cudaGetLastError());
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  DT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mk, mv, a));
   return DT_OK;
 }
 
@@ -823,24 +1036,28 @@ bool decode_supported(const dt_sdpa_params& p) {
 size_t decode_workspace_bytes(const dt_sdpa_params& p) { return plan_workspace_bytes(p, make_plan(p, p.Sk)); }
 
 namespace {
-int dispatch_decode(const dt_sdpa_params& p, const dt_decode_step_params* step, void* workspace, size_t bytes,
+int dispatch_decode(const dt_sdpa_params& p, const dt_decode_step_params* step, const Scratch& scratch,
                     cudaStream_t stream) {
   if (p.dtype == DT_F16) {
-    if (p.D == 256) return launch_t<__half, 256>(p, step, workspace, bytes, stream);
-    return p.D == 128 ? launch_t<__half, 128>(p, step, workspace, bytes, stream)
-                      : launch_t<__half, 64>(p, step, workspace, bytes, stream);
+    if (p.D == 256) return launch_t<__half, 256>(p, step, scratch, stream);
+    return p.D == 128 ? launch_t<__half, 128>(p, step, scratch, stream) : launch_t<__half, 64>(p, step, scratch, stream);
   }
-  if (p.D == 256) return launch_t<__nv_bfloat16, 256>(p, step, workspace, bytes, stream);
-  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, step, workspace, bytes, stream)
-                    : launch_t<__nv_bfloat16, 64>(p, step, workspace, bytes, stream);
+  if (p.D == 256) return launch_t<__nv_bfloat16, 256>(p, step, scratch, stream);
+  return p.D == 128 ? launch_t<__nv_bfloat16, 128>(p, step, scratch, stream)
+                    : launch_t<__nv_bfloat16, 64>(p, step, scratch, stream);
+}
+
+Scratch caller_workspace(void* workspace, size_t bytes) {
+  return Scratch{workspace, bytes, device_status_word(), false, DT_WORKSPACE};
 }
 
 // Argument rules of the fused decode step on top of decode_supported().
 int validate_step(const dt_decode_step_params* s) {
   if (!s) return DT_BAD_ARG;
   const dt_sdpa_params& p = s->attn;
-  if (!p.q.ptr || !p.k.ptr || !p.v.ptr || !p.o.ptr || !s->k_new.ptr || !s->v_new.ptr) return DT_BAD_ARG;
-  if (p.B <= 0 || p.Sq <= 0 || p.Sk <= 0 || p.Hq <= 0 || p.Hkv <= 0 || p.Hq % p.Hkv) return DT_BAD_ARG;
+  const int base = validate_params(&p);
+  if (base != DT_OK) return base;
+  if (!s->k_new.ptr || !s->v_new.ptr) return DT_BAD_ARG;
   if (s->T_new < p.Sq || s->T_new > p.Sk) return DT_BAD_ARG;
   if (s->T_new > kUnitKeys) return DT_UNSUPPORTED;  // the new rows form one 16-key unit
   if (!p.is_causal && s->T_new != p.Sq) return DT_BAD_ARG;
@@ -861,7 +1078,7 @@ int validate_step(const dt_decode_step_params* s) {
 }  // namespace
 
 int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaStream_t stream) {
-  return dispatch_decode(p, nullptr, workspace, bytes, stream);
+  return dispatch_decode(p, nullptr, caller_workspace(workspace, bytes), stream);
 }
 
 }  // namespace dt
@@ -881,7 +1098,7 @@ extern "C" int dt_sdpa_decode_step(const dt_decode_step_params* s, void* workspa
   using namespace dt;
   const int st = validate_step(s);
   if (st != DT_OK) return st;
-  return dispatch_decode(s->attn, s, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(cuda_stream));
+  return dispatch_decode(s->attn, s, caller_workspace(workspace, workspace_bytes), reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 // ---- entry point that allocates nothing ----------------------------------------------------------------
@@ -895,71 +1112,16 @@ static __device__ __align__(256) unsigned int g_noalloc_status[64];
 
 // In host code the two names above are host-side stand-ins, not device addresses: the real addresses come
 // from cudaGetSymbolAddress, once per device, with that device current.
-struct NoAllocDevice {
-  unsigned char* scratch = nullptr;
-  unsigned int* status = nullptr;
-  bool attr[4] = {false, false, false, false};
-};
-NoAllocDevice g_noalloc_dev[64];
-std::mutex g_noalloc_mu;
-
-int noalloc_setup(int dev, NoAllocDevice** out) {
-  std::lock_guard<std::mutex> lk(g_noalloc_mu);
-  NoAllocDevice& d = g_noalloc_dev[dev];
-  if (!d.scratch) {
+int noalloc_setup(DeviceState* d) {
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (!d->noalloc_scratch) {
     void* ps = nullptr;
     void* pst = nullptr;
     DT_CUDA_TRY(cudaGetSymbolAddress(&ps, g_noalloc_scratch));
     DT_CUDA_TRY(cudaGetSymbolAddress(&pst, g_noalloc_status));
-    d.scratch = reinterpret_cast<unsigned char*>(ps);
-    d.status = reinterpret_cast<unsigned int*>(pst);
+    d->noalloc_status = reinterpret_cast<unsigned int*>(pst);
+    d->noalloc_scratch = reinterpret_cast<unsigned char*>(ps);
   }
-  *out = &d;
-  return DT_OK;
-}
-
-template <typename T, int D>
-int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, cudaStream_t stream) {
-  using C = Cfg<D>;
-  const Plan pl = make_plan(p, p.Sk);
-  const int G = p.Hq / p.Hkv, M = p.Sq * G;
-  const size_t pairs = (size_t)p.B * p.Hkv;
-  DecodeArgs a{};
-  if (pl.nsplit > 1) {
-    if (decode_workspace_bytes(p) > (size_t)DT_NOALLOC_SCRATCH_BYTES) return DT_SCRATCH_LIMIT;
-    unsigned char* w = dev->scratch;
-    a.counters = reinterpret_cast<unsigned int*>(w);
-    size_t off = kCounterBytes;
-    a.part_ml = reinterpret_cast<float*>(w + off);
-    off += align_up(pairs * pl.nsplit * M * 2 * sizeof(float), 256);
-    a.part_o = reinterpret_cast<float*>(w + off);
-    // the array keeps whatever the previous call left: the ticket counters must start at zero
-    DT_CUDA_TRY(cudaMemsetAsync(a.counters, 0, pairs * sizeof(unsigned int), stream));
-  }
-  CUtensorMap mk, mv;
-  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
-  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, D, p.dtype, C::kBoxRows)) return DT_UNSUPPORTED;
-  a.q = p.q.ptr; a.o = p.o.ptr; a.lse = p.lse;
-  a.q_sb = p.q.stride_b; a.q_ss = p.q.stride_s; a.q_sh = p.q.stride_h;
-  a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
-  a.status = dev->status;
-  a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
-  a.stream_keys = p.Sk;
-  a.nsplit = pl.nsplit; a.units_per_split = pl.units_per_split;
-  a.unit_first = min(first_unit(p), (a.stream_keys + kUnitKeys - 1) / kUnitKeys);
-  a.total_units = a.unit_first + pl.total_units;  // one past the last streamed unit
-  a.window = p.sliding_window;
-  a.sinks = p.sinks;
-  a.scale_log2 = p.scale * kLog2e;
-  a.is_causal = p.is_causal;
-  auto kern = decode_splitkv_kernel<T, D>;
-  if (!dev->attr[variant]) {
-    DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    dev->attr[variant] = true;
-  }
-  dim3 grid(pl.nsplit, p.Hkv, p.B);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mk, mv, a);
-  DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;
 }
 
@@ -968,23 +1130,45 @@ int launch_noalloc_t(const dt_sdpa_params& p, NoAllocDevice* dev, int variant, c
 
 extern "C" int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream) {
   using namespace dt;
-  if (!p || !p->q.ptr || !p->k.ptr || !p->v.ptr || !p->o.ptr) return DT_BAD_ARG;
-  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Hq % p->Hkv) return DT_BAD_ARG;
-  if (!decode_supported(*p) || p->D == 256) return DT_UNSUPPORTED;
-  int dev = 0;
-  DT_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return DT_NO_DEVICE;
-  NoAllocDevice* d = nullptr;
-  int st = noalloc_setup(dev, &d);
+  // the same argument rules as dt_sdpa_forward (null / misaligned pointers, NaN scale, negative window ...)
+  int st = validate_params(p);
   if (st != DT_OK) return st;
-  cudaStream_t s = (cudaStream_t)cuda_stream;
-  if (p->dtype == DT_F16)
-    return p->D == 128 ? launch_noalloc_t<__half, 128>(*p, d, 0, s) : launch_noalloc_t<__half, 64>(*p, d, 1, s);
-  return p->D == 128 ? launch_noalloc_t<__nv_bfloat16, 128>(*p, d, 2, s) : launch_noalloc_t<__nv_bfloat16, 64>(*p, d, 3, s);
+  if (p->lse && reinterpret_cast<uintptr_t>(p->lse) % sizeof(float)) return DT_BAD_ARG;
+  if (!decode_supported(*p)) return DT_UNSUPPORTED;
+  DeviceState* d = device_state();
+  if (!d) return DT_NO_DEVICE;
+  st = noalloc_setup(d);
+  if (st != DT_OK) return st;
+  const Scratch scratch{d->noalloc_scratch, (size_t)DT_NOALLOC_SCRATCH_BYTES, d->noalloc_status, true, DT_SCRATCH_LIMIT};
+  return dispatch_decode(*p, nullptr, scratch, (cudaStream_t)cuda_stream);
 }
 
-// Test hook (not part of the public header): per-CTA timeline buffer for the decode kernel.
+// Reads and clears the status word of the entry point above: a device-side wait that ran out in one of its
+// launches left a non-zero code there.  Copies four bytes into the caller's variable; allocates nothing.
+extern "C" int dt_sdpa_decode_noalloc_status(void* cuda_stream, int* code) {
+  using namespace dt;
+  if (!code) return DT_BAD_ARG;
+  DeviceState* d = device_state();
+  if (!d) return DT_NO_DEVICE;
+  int st = noalloc_setup(d);
+  if (st != DT_OK) return st;
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  unsigned int h = 0;
+  DT_CUDA_TRY(cudaMemcpyAsync(&h, d->noalloc_status, sizeof(h), cudaMemcpyDeviceToHost, s));
+  DT_CUDA_TRY(cudaStreamSynchronize(s));
+  *code = (int)h;
+  if (h) {
+    DT_CUDA_TRY(cudaMemsetAsync(d->noalloc_status, 0, sizeof(h), s));
+    DT_CUDA_TRY(cudaStreamSynchronize(s));
+    return DT_TIMEOUT;
+  }
+  return DT_OK;
+}
+
+#ifdef DT_BRINGUP
+// Bring-up builds only: per-CTA timeline buffer for the decode kernel.
 extern "C" int dt_internal_set_decode_dump(unsigned long long* device_buffer) {
   dt::g_decode_dbg = device_buffer;
   return 0;
 }
+#endif

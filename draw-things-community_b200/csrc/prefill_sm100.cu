@@ -1,8 +1,9 @@
 // Flash-attention forward for sm_100a: TMA-staged Q/K/V tiles, tcgen05.mma with TMEM accumulators,
 // warp-specialised online softmax.  Serves the diffusion shapes of the reference
 // (Libraries/SwiftDiffusion/Sources/Models/Flux1.swift:224-232 joint attention, Wan.swift:95-131 video
-// self-attention, UNetXL.swift:67-185 cross-attention): fp16/bf16 I/O, fp32 accumulation, head dim 64 or
-// 128, grouped KV heads, optional bottom-right causal mask, BSHD strided views.
+// self-attention, UNetXL.swift:67-185 cross-attention) and the masked text encoders (an additive mask as 4th
+// input, alone or with isCausal: Llama.swift:70-73, CLIPTextModel.swift:46-51): fp16/bf16 I/O, fp32 accumulation,
+// head dim up to 128, grouped KV heads, optional bottom-right causal rule, BSHD strided views.
 //
 // One CTA = one (batch, head, pair of 128-row query tiles).  12 warps:
 //   warp 0      TMA producer: Q tiles once, then K(j), V(j) blocks of 128 keys through a ring of slots
@@ -60,7 +61,10 @@ struct Cfg {
 struct PrefillArgs {
   void* o;
   float* lse;
-  float* dbg;  // optional [2][128][128] fp32 dump of the first S block of CTA (0,0,0)
+#ifdef DT_BRINGUP
+  float* dbg;   // optional [2][128][128] fp32 dump of the first S block of CTA (0,0,0), or timeline stamps
+  int options;  // bit 1: timeline probe of CTA 0 into dbg
+#endif
   int64_t o_sb, o_ss, o_sh;
   unsigned int* status;
   int Sq, Sk, Hq, Hkv;
@@ -68,7 +72,11 @@ struct PrefillArgs {
   int is_causal;
   int window;         // sliding window W (0 = off): row i sees keys j > i + (Sk - Sq) - W
   const void* sinks;  // [Hq] attention sinks in the tensors' type, or null
-  int options;  // bit 1: timeline probe of CTA 0 into dbg (bring-up only)
+  // additive mask [B or 1, Hq or 1, Sq, Sk] in the tensors' type (kernel variant kMask only): element strides,
+  // 0 on a broadcast axis; rows are 16-byte aligned (base and strides multiples of 8 elements)
+  const void* mask;
+  int64_t m_sb, m_sh, m_sq;
+  float scale;  // the plain scale (scale_log2 = scale * log2(e)); the masked variant adds the mask in this domain
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
   // variable-length batch (both null otherwise): packed rows, sequence s owns query rows [off_q[s], off_q[s+1])
   // and key rows [off_k[s], off_k[s+1]); the item's batch index is then the sequence
@@ -132,13 +140,24 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint6
   }
 }
 
-// Timeline probe (options bit 1): globaltimer stamps of CTA 0 into the debug buffer (bring-up only).
+// Timeline probe of bring-up builds (options bit 1): globaltimer stamps of CTA 0 into the debug buffer.
+#ifdef DT_BRINGUP
 __device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
   if ((a.options & 2) && a.dbg != nullptr && blockIdx.x == 0 && slot < 4096)
     reinterpret_cast<unsigned long long*>(a.dbg)[slot] = ptx::globaltimer_ns();
 }
+#else
+__device__ __forceinline__ void stamp(const PrefillArgs&, int) {}
+#endif
 
-template <typename T, int D>
+// 16-bit pair -> two floats (the mask is stored in the tensors' type)
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t x) {
+  if constexpr (std::is_same<T, __half>::value) return __half22float2(*reinterpret_cast<const __half2*>(&x));
+  else return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+}
+
+template <typename T, int D, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -421,7 +440,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t t_o = tmem + (t ? C::kColO1 : C::kColO0) + lane_addr;
     uint32_t sph = 0, oph = 0;  // phases of s_full[t] / o_full[t], continue across items
     bool ok = true;
+#ifdef DT_BRINGUP
     bool first_dump = true;
+#endif
     int n_item = 0;
     const bool probe = (warp == 4 && lane == 0);
 
@@ -435,6 +456,30 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float m_used = -INFINITY, l = 0.f;
 
       for (int j = 0; j < w.nkv; ++j) {
+        // Masked variant: this row's 128 mask values of the block (256 contiguous bytes) are requested before the
+        // wait for S, so that they arrive while the tensor pipe still works on it.  Vectors that straddle Sk are
+        // fetched element by element (nothing beyond the row's Sk entries is ever read); rows beyond Sq load nothing.
+        uint4 mk[kMask ? 16 : 1];
+        if constexpr (kMask) {
+          const int key0m = (w.j0 + j) * kBN;
+          const T* mrow = reinterpret_cast<const T*>(a.mask) + (int64_t)w.b * a.m_sb + (int64_t)w.h * a.m_sh +
+                          (int64_t)row * a.m_sq + key0m;
+          const int left = row < w.sq ? w.sk - key0m : 0;  // mask entries of this row from key0m on
+          uint4 tail = make_uint4(0u, 0u, 0u, 0u);
+          const int tv = left > 0 && left < kBN && (left & 7) ? (left >> 3) : -1;  // the vector that straddles Sk
+          if (tv >= 0) {
+            uint32_t e[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              e[i] = tv * 8 + i < left ? (uint32_t) * reinterpret_cast<const unsigned short*>(mrow + tv * 8 + i) : 0u;
+            tail = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+          }
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            if (v * 8 + 8 <= left) mk[v] = __ldg(reinterpret_cast<const uint4*>(mrow) + v);
+            else mk[v] = v == tv ? tail : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
           atomicCAS(a.status, 0u, 3u);
           *abort_flag = 1;
@@ -445,14 +490,47 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (probe && j == 0) stamp(a, 16 * n_item + 8);
         ptx::tc_fence_after();
         uint32_t s[4][32];
-        ptx::tmem_ld32(t_s + 0, s[0]);
-        ptx::tmem_ld32(t_s + 32, s[1]);
-        ptx::tmem_ld32(t_s + 64, s[2]);
-        ptx::tmem_ld32(t_s + 96, s[3]);
-        ptx::tc_wait_ld();
+        if constexpr (kMask) {
+          // scores in two halves, each turned into scale * s + mask as soon as it is in registers: the mask
+          // registers of the first half are free before the second half of S arrives
+          auto add_mask = [&](int c) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 m4 = mk[c * 4 + v];
+              const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 mf = unpack_pair<T>(mw[u]);
+                const int i = v * 8 + u * 2;
+                s[c][i] = __float_as_uint(fmaf(__uint_as_float(s[c][i]), a.scale, mf.x));
+                s[c][i + 1] = __float_as_uint(fmaf(__uint_as_float(s[c][i + 1]), a.scale, mf.y));
+              }
+            }
+          };
+          ptx::tmem_ld32(t_s + 0, s[0]);
+          ptx::tmem_ld32(t_s + 32, s[1]);
+          ptx::tc_wait_ld();
+          add_mask(0);
+          add_mask(1);
+          ptx::tmem_ld32(t_s + 64, s[2]);
+          ptx::tmem_ld32(t_s + 96, s[3]);
+          ptx::tc_wait_ld();
+          add_mask(2);
+          add_mask(3);
+        } else {
+          ptx::tmem_ld32(t_s + 0, s[0]);
+          ptx::tmem_ld32(t_s + 32, s[1]);
+          ptx::tmem_ld32(t_s + 64, s[2]);
+          ptx::tmem_ld32(t_s + 96, s[3]);
+          ptx::tc_wait_ld();
+        }
+        // from here on the scores are multiplied by `sl2`: scale * log2(e), or log2(e) alone once the masked
+        // variant has applied the scale together with the mask
+        const float sl2 = kMask ? kLog2e : a.scale_log2;
         if (probe && j == 0) stamp(a, 16 * n_item + 4);
 
-        if (a.dbg != nullptr && first_dump && j == 0 && blockIdx.x == 0) {
+#ifdef DT_BRINGUP
+        if (a.dbg != nullptr && !(a.options & 2) && first_dump && j == 0 && blockIdx.x == 0) {
           float* dst = a.dbg + ((size_t)t * kBM + row_in_tile) * kBN;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -460,6 +538,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < 32; ++i) dst[c * 32 + i] = __uint_as_float(s[c][i]);
         }
         first_dump = false;
+#endif
 
         const int key0 = (w.j0 + j) * kBN;
         const bool need_mask = (key0 + kBN > w.sk) || (a.is_causal && (long long)(key0 + kBN - 1) > vis) || (long long)key0 < lo;
@@ -504,7 +583,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mxc[c] = fmaxf(mxc[c], __uint_as_float(s[c][31]));
         }
         float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
-        mx *= a.scale_log2;  // scale > 0 is a precondition of this kernel
+        mx *= sl2;  // scale > 0 is a precondition of this kernel
         const float m_cand = fmaxf(m_used, mx);
         // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
         const bool grow = (m_cand - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_cand != -INFINITY);
@@ -530,7 +609,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (probe && j == 0) stamp(a, 16 * n_item + 13);
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
-        const uint64_t scale2 = ptx::pack_f32x2(a.scale_log2, a.scale_log2);
+        const uint64_t scale2 = ptx::pack_f32x2(sl2, sl2);
         uint64_t lsum[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -675,10 +754,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
+#ifdef DT_BRINGUP
 int g_options = 0;
 float* g_dbg = nullptr;
+#endif
 
-template <typename T, int D>
+template <typename T, int D, bool kMask>
 int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, int n_extra) {
   using C = Cfg<D>;
   CUtensorMap mq, mk, mv, mo;
@@ -689,16 +770,21 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   PrefillArgs a{};
   a.o = p.o.ptr;
   a.lse = p.lse;
+#ifdef DT_BRINGUP
   a.dbg = g_dbg;
+  a.options = g_options;
+#endif
   a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
   a.status = device_status_word();
   if (!a.status) return DT_CUDA;
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv;
   a.scale_log2 = p.scale * kLog2e;
+  a.scale = p.scale;
+  a.mask = p.mask;
+  a.m_sb = p.mask_stride_b; a.m_sh = p.mask_stride_h; a.m_sq = p.mask_stride_q;
   a.is_causal = p.is_causal;
   a.window = p.sliding_window;
   a.sinks = p.sinks;
-  a.options = g_options;
   if (n_extra < 0 || n_extra > kMaxExtraOutputs) return DT_BAD_ARG;
   a.n_extra = n_extra;
   a.d_real = p.D;
@@ -708,14 +794,9 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   a.off_k = p.seq_offsets_k;
   a.n_qpairs = ((varlen ? p.max_seq_q : p.Sq) + 2 * kBM - 1) / (2 * kBM);
   a.n_items = a.n_qpairs * p.Hq * (varlen ? p.n_seq : p.B);
-  auto kern = prefill_tcgen05_kernel<T, D>;
+  auto kern = prefill_tcgen05_kernel<T, D, kMask>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
-  }
+  const int n_sm = device_sm_count();
   dim3 grid(a.n_items < n_sm ? a.n_items : n_sm);  // one persistent CTA per SM
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, mo, a);
   DT_CUDA_TRY(cudaGetLastError());
@@ -731,7 +812,9 @@ bool prefill_supported(const dt_sdpa_params& p) {
   if (p.sliding_window > 0 && p.Sq > p.Sk) return false;  // rows that may see no key: generic kernel
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
   if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)
-  if (p.mask) return false;
+  // additive mask: each row's entries are read with 16-byte loads
+  if (p.mask && (reinterpret_cast<uintptr_t>(p.mask) % 16 || p.mask_stride_b % 8 || p.mask_stride_h % 8 || p.mask_stride_q % 8))
+    return false;
   if (!(p.scale > 0.f)) return false;
   if (p.Hq % p.Hkv) return false;
   if (p.Hq > 65535 || p.B > 65535) return false;
@@ -744,15 +827,23 @@ bool prefill_supported(const dt_sdpa_params& p) {
 }
 
 int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra) {
+  const bool wide = p.D > 64;
+  if (p.mask) {
+    if (p.dtype == DT_F16)
+      return wide ? launch_t<__half, 128, true>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64, true>(p, stream, extra_outputs, n_extra);
+    return wide ? launch_t<__nv_bfloat16, 128, true>(p, stream, extra_outputs, n_extra)
+                : launch_t<__nv_bfloat16, 64, true>(p, stream, extra_outputs, n_extra);
+  }
   if (p.dtype == DT_F16)
-    return p.D > 64 ? launch_t<__half, 128>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64>(p, stream, extra_outputs, n_extra);
-  return p.D > 64 ? launch_t<__nv_bfloat16, 128>(p, stream, extra_outputs, n_extra)
-                    : launch_t<__nv_bfloat16, 64>(p, stream, extra_outputs, n_extra);
+    return wide ? launch_t<__half, 128, false>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64, false>(p, stream, extra_outputs, n_extra);
+  return wide ? launch_t<__nv_bfloat16, 128, false>(p, stream, extra_outputs, n_extra)
+              : launch_t<__nv_bfloat16, 64, false>(p, stream, extra_outputs, n_extra);
 }
 
 }  // namespace dt
 
-// Test hooks (not part of the public header): kernel variant bits and the S-dump buffer.
+#ifdef DT_BRINGUP
+// Bring-up builds only: kernel probe bits and the buffer the probes write to.
 extern "C" int dt_internal_set_prefill_options(int options) {
   dt::g_options = options;
   return 0;
@@ -761,3 +852,4 @@ extern "C" int dt_internal_set_prefill_dump(float* device_buffer) {
   dt::g_dbg = device_buffer;
   return 0;
 }
+#endif

@@ -73,6 +73,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// ---- thread-block clusters and distributed shared memory -------------------------------------------
+
+// Hardware barrier over all threads of all CTAs of the cluster; release / acquire at cluster scope, so shared
+// memory written before it is visible to the other CTAs' ld.shared::cluster after it.  Every thread of every
+// CTA of the cluster must reach it (there is no bounded form: callers keep the control flow up to it unconditional).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `cta_rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {

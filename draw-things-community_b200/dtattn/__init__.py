@@ -28,6 +28,13 @@ DT_SCRATCH_LIMIT = -8
 NOALLOC_SCRATCH_BYTES = 8 << 20
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 DT_FLAG_FP16_ACCUM_HINT, DT_FLAG_FORCE_GENERIC, DT_FLAG_KV_PREFIX_STABLE = 1, 2, 4
+
+
+def DT_FLAG_DECODE_SPLITS(n):
+    """Fix the split count of the split-KV decode kernel (1..256; 0 = automatic)."""
+    return (int(n) & 0xFFF) << 16
+
+
 _DTYPES = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
 
 
@@ -90,6 +97,7 @@ SYMBOLS = [
     ("dt_sdpa_decode_step_workspace_size", ctypes.c_int, [_P(DecodeStepParams), _P(ctypes.c_size_t)]),
     ("dt_sdpa_decode_step", ctypes.c_int, [_P(DecodeStepParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_sdpa_decode_noalloc", ctypes.c_int, [_P(SdpaParams), ctypes.c_void_p]),
+    ("dt_sdpa_decode_noalloc_status", ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int)]),
     ("dt_sdpa_projected_workspace_size", ctypes.c_int, [_P(SdpaParams), _P(OutProj), _P(ctypes.c_size_t)]),
     ("dt_sdpa_forward_projected", ctypes.c_int,
      [_P(SdpaParams), _P(OutProj), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),

@@ -10,7 +10,10 @@
  * Conventions
  *   - plain C types only; no exceptions; every function returns a dt_status (0 = OK, <0 = error).
  *   - all tensors are caller-owned DEVICE memory (except dt_sdpa_forward_host, which takes host
- *     memory); the library never takes ownership and never allocates inside dt_sdpa_forward.
+ *     memory); the library never takes ownership.  dt_sdpa_forward, dt_sdpa_decode_step, dt_qk_prologue and
+ *     dt_sdpa_forward_projected allocate no device memory: scratch is the caller's workspace and the
+ *     device status word is part of the library image.  (dt_sdpa_forward_host and the communicator
+ *     set-up calls do allocate.)
  *   - tensors are 4-D views [B, S, H, D] ("BSHD", the layout every reference call site passes, e.g.
  *     Libraries/SwiftDiffusion/Sources/Models/UNet.swift:139-155) described by element strides; the
  *     innermost (D) stride is 1.  Strided views (row-offset views, batch strides larger than S*H*D)
@@ -59,6 +62,10 @@ typedef struct {
                                       memory from the cache while the preceding kernel drains, and everything else
                                       (Q, new rows, workspace, outputs) waits for that kernel to complete.  Ignored by
                                       the other kernels. */
+/* Split-KV decode tuning: fix the number of splits of every (batch, KV head) to n (1..256; 0 = the library's own
+   choice, which fills the SMs once).  The value is part of what dt_sdpa_workspace_size depends on: pass the same
+   flags to both calls.  Ignored by the other kernels. */
+#define DT_FLAG_DECODE_SPLITS(n) ((((uint32_t)(n)) & 0xFFFu) << 16)
 
 typedef struct {
   int32_t B, Sq, Sk, Hq, Hkv, D; /* Hq % Hkv == 0; query head h reads KV head h / (Hq/Hkv)
@@ -219,7 +226,7 @@ int dt_qk_prologue(const dt_qk_prologue_params* q, const dt_qk_prologue_params* 
  * executor owns device memory this way) has nothing left for a late cudaMalloc, and inside a latency-bound
  * token loop a device allocation would also stall every stream while it runs.  For them this entry point
  * runs the split-KV decode kernel (the same shapes dt_sdpa_forward routes to "decode_splitkv": fp16/bf16,
- * D 64 or 128, Sq * Hq/Hkv <= 16, no mask) with its partial results kept in a fixed array of
+ * D 64, 128 or 256, Sq * Hq/Hkv <= 16, no mask) with its partial results kept in a fixed array of
  * DT_NOALLOC_SCRATCH_BYTES that is part of the library image; each GPU that loads the library holds that
  * array until the process ends.  It calls no cudaMalloc, cudaFree or allocating library routine; the caller
  * still owns q, k, v, o (and lse).
@@ -229,11 +236,17 @@ int dt_qk_prologue(const dt_qk_prologue_params* q, const dt_qk_prologue_params* 
  *   - All calls on a device share the one array and it keeps what the last call wrote.  The call clears the
  *     few words that must start at zero, on `cuda_stream`.  Two calls that overlap on the GPU (different
  *     streams, or different host threads without ordering) race on it: serialise them.
- *   - A device-side wait that runs out is recorded in a status word inside the library image, not the one
- *     dt_device_status reads.
+ *   - Arguments are checked exactly as dt_sdpa_forward checks them (null or misaligned pointers, NaN scale,
+ *     negative window ...) before anything is launched.
+ *   - A device-side wait that runs out is recorded in a status word of this entry point's own (inside the
+ *     library image, not the one dt_device_status reads).  dt_sdpa_decode_noalloc_status copies it into *code
+ *     and clears it (synchronises `cuda_stream`; allocates nothing): DT_OK with *code == 0 when every launch
+ *     so far ran to its end, DT_TIMEOUT with the code otherwise, in which case the outputs of the calls since
+ *     the last check are not to be trusted.
  */
 #define DT_NOALLOC_SCRATCH_BYTES (8u << 20)
 int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream);
+int dt_sdpa_decode_noalloc_status(void* cuda_stream, int* code);
 
 /* Device status word ------------------------------------------------------------------------------
  * Kernels never spin without a bound: a wait that runs out stores a non-zero code into a per-device
@@ -258,11 +271,18 @@ int dt_comm_destroy(void* comm);
  * dt_sdpa_forward_headsharded whose o_full.ptr is a registered buffer stores each output tile straight into
  * all ranks' buffers from the attention kernel's epilogue (ordinary peer stores over NVLink, overlapped with
  * the tensor-core work) and ends with one small in-stream rendezvous, instead of all-gather + permute.
- * Up to 8 buffers per communicator, up to 8 ranks. */
+ * Up to 8 buffers per communicator, up to 8 ranks.
+ * Ordering rule of the fused mode: a rank's stores land in the OTHER ranks' buffers, so whatever reads a buffer on
+ * a rank must be ordered before the other ranks' next stores into it.  Readers enqueued on the stream that is passed
+ * to dt_sdpa_forward_headsharded are: register two buffers and alternate between them, and the rendezvous that ends
+ * the call in between gives that order for free; when two consecutive calls name the same buffer the library puts
+ * one more rendezvous in front of the second call's kernel.  A reader on another stream must be joined to that
+ * stream (an event) before the next call that stores into the buffer it reads. */
 int dt_comm_register_output(void* comm, void* o_full, size_t bytes);
 /* Run the local head slice (`local`: Hq and Hkv are the per-rank counts, o is ignored) and gather the
  * full output into o_full ([B, Sq, Hq*world, D], contiguous rows) on every rank.  `chunks` >= 1 splits
- * the query rows into that many pieces so the gather of one piece overlaps the attention of the next.
+ * the query rows into that many pieces so the gather of one piece overlaps the attention of the next (causal,
+ * sliding-window and variable-length calls always run as one piece; masks and lse are refused).
  * `workspace_bytes` must be at least dt_sdpa_headsharded_workspace_size.
  */
 int dt_sdpa_headsharded_workspace_size(const dt_sdpa_params* local, int world, int chunks, size_t* bytes);

@@ -72,6 +72,35 @@ def test_bad_arguments_are_rejected(dtattn):
     assert lib.dt_comm_unique_id(None) == dtattn.DT_BAD_ARG
 
 
+def test_noalloc_entry_point_validates_before_anything_runs(dtattn):
+    """dt_sdpa_decode_noalloc applies the argument rules of dt_sdpa_forward: misaligned output / sink / log-sum-exp
+    pointers, a NaN scale and a negative window come back as DT_BAD_ARG on a machine without any GPU."""
+    lib = dtattn.lib()
+    for over in (dict(scale=float("nan")), dict(sliding_window=-1), dict(sinks=0x10001), dict(lse=0x10002), dict(B=0)):
+        p, keep = _params(dtattn, Sq=1, Sk=512, D=128, **over)
+        assert lib.dt_sdpa_decode_noalloc(ctypes.byref(p), None) == dtattn.DT_BAD_ARG, over
+    p, keep = _params(dtattn, Sq=1, Sk=512, D=128)
+    p.o.ptr = keep[3].data_ptr() + 1
+    assert lib.dt_sdpa_decode_noalloc(ctypes.byref(p), None) == dtattn.DT_BAD_ARG
+    p, keep = _params(dtattn, Sq=64, Sk=512, D=128)  # 64 rows x 2 heads per KV head: not a decode shape
+    assert lib.dt_sdpa_decode_noalloc(ctypes.byref(p), None) == dtattn.DT_UNSUPPORTED
+    assert lib.dt_sdpa_decode_noalloc_status(None, None) == dtattn.DT_BAD_ARG
+
+
+def test_decode_split_flag_changes_the_workspace_only_within_bounds(dtattn):
+    """DT_FLAG_DECODE_SPLITS fixes the split count; it is clamped to 256 and to the number of 16-key units, so the
+    combining CTA's shared-memory tables cannot be overrun by a caller's value."""
+    sizes = {}
+    for n in (0, 1, 2, 64, 256, 4095):
+        p, keep = _params(dtattn, B=2, Sq=1, Sk=16384, Hq=8, Hkv=2, D=128, flags=dtattn.DT_FLAG_DECODE_SPLITS(n))
+        assert dtattn.kernel_name(p) == "decode_splitkv"
+        sizes[n] = dtattn.workspace_size(p)
+    assert sizes[1] == 0 and sizes[2] < sizes[64] < sizes[256] == sizes[4095]
+    p, keep = _params(dtattn, B=1, Sq=1, Sk=48, Hq=8, Hkv=2, D=128, flags=dtattn.DT_FLAG_DECODE_SPLITS(200))
+    per_part = 4 * 128 * 4 + 4 * 2 * 4  # one partial of one KV head: 4 rows x (128 floats + m, l)
+    assert dtattn.workspace_size(p) <= 4096 + 2 * 256 + 2 * 3 * per_part  # 48 keys = 3 units = at most 3 splits
+
+
 def test_kernel_selection(dtattn):
     """Which kernel serves which reference call site (decided on the host, no GPU needed)."""
     def pick(B, Sq, Sk, Hq, Hkv, D, dtype, causal=False, flags=0):

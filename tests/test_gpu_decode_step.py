@@ -4,7 +4,6 @@ attention in one launch, against the oracle's restatement of the reference's sep
 operations and one rounding on both sides); the attention output within the stated tolerance
 (max-abs <= 2e-3, mean-abs <= 2e-4, plus the 16-bit output's own rounding on small shapes)."""
 import ctypes
-import os
 
 import pytest
 import torch
@@ -31,7 +30,7 @@ def make_case(B, cached, Tn, Sq, Hq, Hkv, D, dtype, seed, rotary_dim=None, capac
     return q, k_cache, v_cache, k_new, v_new, rot
 
 
-def run_step(dtattn, case, cached, scale, dtype, what):
+def run_step(dtattn, case, cached, scale, dtype, what, flags=0):
     q, k_cache, v_cache, k_new, v_new, rot = case
     Tn = k_new.shape[1]
     kc_ref, vc_ref = k_cache.clone(), v_cache.clone()
@@ -39,7 +38,7 @@ def run_step(dtattn, case, cached, scale, dtype, what):
     ref = so.decode_step_explicit(q, kc_ref, vc_ref, k_new, v_new, rot_ref, scale, cached, dtype)
     kc, vc = k_cache.to(DEV), v_cache.to(DEV)
     out = dtattn.decode_step(q.to(DEV), kc, vc, k_new.to(DEV), v_new.to(DEV), None if rot is None else rot.to(DEV),
-                             scale, cached)
+                             scale, cached, flags=flags)
     torch.cuda.synchronize()
     assert dtattn.device_status() == 0, "a device-side wait ran out"
     # the whole cache, not only the appended rows: nothing else may have been touched
@@ -75,15 +74,13 @@ def test_decode_step_per_batch_table_and_no_table(dtattn):
     run_step(dtattn, c, 300, 128 ** -0.5, torch.bfloat16, "no rotary")
 
 
-@pytest.mark.parametrize("splits", ["1", "3", "16"])
+@pytest.mark.parametrize("splits", [1, 3, 16, 32, 48])
 def test_decode_step_split_counts(dtattn, splits):
-    """The appended rows are attended by the last split only, whatever the split count."""
-    os.environ["DTATTN_DECODE_SPLITS"] = splits
-    try:
-        c = make_case(2, 1234, 2, 2, 8, 2, 128, torch.bfloat16, 721)
-        run_step(dtattn, c, 1234, 128 ** -0.5, torch.bfloat16, f"splits={splits}")
-    finally:
-        del os.environ["DTATTN_DECODE_SPLITS"]
+    """The appended rows are attended by the last split only, whatever the split count (fixed here with
+    DT_FLAG_DECODE_SPLITS): one CTA, an odd count (no cluster), one full cluster, two clusters whose partials go
+    through the workspace, three clusters."""
+    c = make_case(2, 1234, 2, 2, 8, 2, 128, torch.bfloat16, 721)
+    run_step(dtattn, c, 1234, 128 ** -0.5, torch.bfloat16, f"splits={splits}", flags=dtattn.DT_FLAG_DECODE_SPLITS(splits))
 
 
 def test_decode_loop_equals_attention_over_final_cache(dtattn):
