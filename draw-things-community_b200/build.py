@@ -1,6 +1,10 @@
 """Build lib/libdtattn.so (sm_100a only) from csrc/*.cu with nvcc.  No GPU is needed to build.
 
-    python draw-things-community_b200/build.py [--force] [--verbose]
+    python draw-things-community_b200/build.py [--force] [--verbose] [--define NAME[=VALUE] ...] [--out PATH]
+
+--define adds preprocessor definitions (DT_BRINGUP compiles the timeline probes and the environment overrides of
+the bring-up builds in); a build with definitions must name its own --out, and keeps its objects beside it, so it
+never replaces the product library.
 """
 import os
 import subprocess
@@ -26,20 +30,24 @@ def _headers():
            [os.path.join(HERE, "..", "include", "dtattn.h")]
 
 
-def build(force=False, verbose=False):
-    os.makedirs(OBJ, exist_ok=True)
-    os.makedirs(LIB_DIR, exist_ok=True)
+def build(force=False, verbose=False, defines=(), out=None):
+    if defines and not out:
+        raise ValueError("a build with --define needs its own --out")
+    lib = os.path.abspath(out) if out else LIB
+    obj_dir = os.path.join(os.path.dirname(lib), "obj_" + os.path.basename(lib)) if out else OBJ
+    os.makedirs(obj_dir, exist_ok=True)
+    os.makedirs(os.path.dirname(lib), exist_ok=True)
     hdr_time = _newest(_headers())
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, src.replace(".cu", ".o"))
+        o = os.path.join(obj_dir, src.replace(".cu", ".o"))
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_time):
-            cmd = ["nvcc", *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = ["nvcc", *NVCC_FLAGS, *["-D" + d for d in defines], "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
-    objs = [os.path.join(OBJ, s.replace(".cu", ".o")) for s in SOURCES]
+    objs = [os.path.join(obj_dir, s.replace(".cu", ".o")) for s in SOURCES]
 
     def run(cmd):
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -51,14 +59,17 @@ def build(force=False, verbose=False):
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
             if r.returncode:
                 raise RuntimeError("nvcc failed: " + cmd[-3])
-    if jobs or force or not os.path.exists(LIB):
-        cmd = ["nvcc", "-shared", "-o", LIB, *objs, "-ldl", "-lpthread"]
+    if jobs or force or not os.path.exists(lib):
+        cmd = ["nvcc", "-shared", "-o", lib, *objs, "-ldl", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    argv = sys.argv[1:]
+    defs = [argv[i + 1] for i, a in enumerate(argv[:-1]) if a == "--define"]
+    outs = [argv[i + 1] for i, a in enumerate(argv[:-1]) if a == "--out"]
+    print(build(force="--force" in argv, verbose="--verbose" in argv, defines=defs, out=outs[0] if outs else None))

@@ -12,14 +12,15 @@
 //           owns one 16-key unit per stage: S^T = Q K^T and O += P V with mma.sync m16n8k16 (fp32
 //           accumulate) fed by ldmatrix from the swizzled tiles, online softmax in registers with
 //           warp-shuffle reductions.
-//   merge = the 4 warps' (m, l, O) are merged through shared memory.  The splits of one (batch, KV head) are
-//           launched as thread-block clusters of up to 16 CTAs along the split axis: after a cluster barrier
-//           every CTA of a cluster combines its share of the output elements straight out of the other CTAs'
-//           shared memory (distributed shared memory, ordinary ld.shared::cluster loads).  When one cluster
-//           covers all splits the result goes to the output at once and no partial ever reaches global
-//           memory; otherwise each cluster writes ONE fp32 partial to the workspace and takes a ticket
-//           (atomicAdd), and the cluster that draws the last ticket of its (batch, KV head) combines the
-//           partials.  Apart from the hardware cluster barrier (which every CTA reaches unconditionally, also
+//   merge = the 4 warps' (m, l, O) are merged through shared memory.  Up to 8 splits per (batch, KV head) are
+//           launched as ONE thread-block cluster along the split axis: after a cluster barrier every CTA
+//           combines its share of the output elements straight out of the other CTAs' shared memory
+//           (distributed shared memory, ordinary ld.shared::cluster loads) and stores the result; no partial
+//           reaches global memory.  With more splits (few (batch, KV head) pairs, e.g. batch 1) each CTA writes
+//           an fp32 partial to the workspace and takes a ticket (atomicAdd), and the CTA that draws the last
+//           ticket of its (batch, KV head) combines all partials.  (Measured on B200: clusters of 16, or
+//           several clusters per pair, cost more in scheduling than they save: 14.1 - 22 us against 13.4 at
+//           batch 1.)  Apart from the hardware cluster barrier (which every CTA reaches unconditionally, also
 //           after a wait that ran out) nothing waits on another CTA, so nothing can hang.
 #include <stdlib.h>
 
@@ -30,6 +31,9 @@
 namespace dt {
 namespace {
 
+#ifndef DT_DECODE_MAX_CLUSTER
+#define DT_DECODE_MAX_CLUSTER 8  // the portable cluster size; one cluster must hold all splits of a (batch, KV head)
+#endif
 constexpr int kUnitKeys = 16;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
@@ -59,6 +63,7 @@ struct Cfg {
   static constexpr int kHalfStride = kStageBoxes ? kStageBox : kBoxBytes;   // bytes between 64-dim halves of a tile
   static constexpr int kUnitStride = kStageBoxes ? kBoxBytes : kWarpTileBytes;  // bytes between units of a stage
   static constexpr int kBoxRows = kStageBoxes ? kUnitKeys * kUnitsPerStage : kUnitKeys;
+  // (A deeper ring for grids that leave every CTA an SM of its own was measured on B200 and changed nothing.)
   static constexpr int kStages = D == 64 ? 4 : 3;
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -89,8 +94,8 @@ struct DecodeArgs {
   float norm_eps;
   int Tn;           // new rows appended by the step fusion (<= 16), 0 otherwise
   int nsplit, units_per_split, total_units;
-  int cluster;  // CTAs per cluster along the split axis (1 = no cluster); divides nsplit
-  int nparts;   // partials per (batch, KV head) that go through global memory: nsplit / cluster
+  int cluster;  // nsplit when the splits of a (batch, KV head) form one thread-block cluster, else 1
+  int nparts;   // partials per (batch, KV head) that go through global memory: nsplit without a cluster, else none
   float scale_log2;
   int is_causal;
 };
@@ -181,8 +186,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t ring = (raw + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - raw);
+  constexpr int nst = C::kStages;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring_ptr + C::kRingBytes);
-  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* empty_bar = full_bar + nst;
   __shared__ int s_abort;
   __shared__ int s_is_last;
 
@@ -208,7 +214,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   if (threadIdx.x == 0) {
     s_abort = 0;
     s_is_last = 0;
-    for (int i = 0; i < C::kStages; ++i) {
+    for (int i = 0; i < nst; ++i) {
       ptx::mbar_init(&full_bar[i], 1);
       ptx::mbar_init(&empty_bar[i], kConsumerWarps);
     }
@@ -396,9 +402,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     // ---------------- producer ----------------
     if (lane == 0) {
       for (int st = 0; st < n_stages; ++st) {
-        const int slot = st % C::kStages;
-        if (st >= C::kStages) {
-          if (!ptx::mbar_wait(&empty_bar[slot], ((st / C::kStages) - 1) & 1, &s_abort)) {
+        const int slot = st % nst;
+        if (st >= nst) {
+          if (!ptx::mbar_wait(&empty_bar[slot], ((st / nst) - 1) & 1, &s_abort)) {
             atomicCAS(a.status, 0u, 2u);
             s_abort = 1;
             break;
@@ -434,8 +440,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   } else {
     // ---------------- consumers ----------------
     for (int st = 0; st < n_stages; ++st) {
-      const int slot = st % C::kStages;
-      if (!ptx::mbar_wait(&full_bar[slot], (st / C::kStages) & 1, &s_abort)) {
+      const int slot = st % nst;
+      if (!ptx::mbar_wait(&full_bar[slot], (st / nst) & 1, &s_abort)) {
         atomicCAS(a.status, 0u, 1u);
         s_abort = 1;
         break;
@@ -566,7 +572,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     o[b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d] = from_float<T>(lt > 0.f ? ot / lt : 0.f);
     if (a.lse && d == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
   };
-  const int part = split / a.cluster;  // which of the pair's global partials this CTA contributes to
   for (int idx = threadIdx.x; idx < MD; idx += kThreads) {
     const int r = idx / D, d = idx - r * D;
     float mstar = -INFINITY;
@@ -590,7 +595,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     } else if (a.nsplit == 1) {
       store_final(r, d, mstar, lt, ot);
     } else {
-      const int64_t slot = (int64_t)pair * a.nparts + part;
+      const int64_t slot = (int64_t)pair * a.nparts + split;
       a.part_o[slot * MD + idx] = ot;
       if (d == 0) {
         a.part_ml[(slot * a.M + r) * 2] = mstar;
@@ -600,7 +605,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   }
   if (a.cluster == 1 && a.nsplit == 1) return;
 
-  bool leader = true;  // the CTA that takes the ticket for its partial
   if (a.cluster > 1) {
     // ---------------- cluster combine through distributed shared memory ----------------
     // Every CTA of the cluster gets here whatever happened before (a wait that ran out falls through to this
@@ -614,9 +618,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int idx_end = min(MD, (crank + 1) * per);
     for (int idx = crank * per + threadIdx.x; idx < idx_end; idx += kThreads) {
       const int r = idx / D, d = idx - r * D;
-      float mv[16], lv[16], ov[16];
+      float mv[DT_DECODE_MAX_CLUSTER], lv[DT_DECODE_MAX_CLUSTER], ov[DT_DECODE_MAX_CLUSTER];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < DT_DECODE_MAX_CLUSTER; ++c) {
         if (c < a.cluster) {
           const uint32_t ml_remote = ptx::map_to_cta(ml_local + (uint32_t)r * 8u, (uint32_t)c);
           mv[c] = ptx::ld_cluster_f32(ml_remote);
@@ -630,36 +634,23 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
       float mstar = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) mstar = fmaxf(mstar, mv[c]);
+      for (int c = 0; c < DT_DECODE_MAX_CLUSTER; ++c) mstar = fmaxf(mstar, mv[c]);
       float lt = 0.f, ot = 0.f;
       if (mstar != -INFINITY) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < DT_DECODE_MAX_CLUSTER; ++c) {
           const float wgt = fast_exp2(mv[c] - mstar);  // exp2(-inf) = 0 for the unused slots
           lt = fmaf(wgt, lv[c], lt);
           ot = fmaf(wgt, ov[c], ot);
         }
       }
-      if (a.nparts == 1) {
-        store_final(r, d, mstar, lt, ot);
-      } else {
-        const int64_t slot = (int64_t)pair * a.nparts + part;
-        a.part_o[slot * MD + idx] = ot;
-        if (d == 0) {
-          a.part_ml[(slot * a.M + r) * 2] = mstar;
-          a.part_ml[(slot * a.M + r) * 2 + 1] = lt;
-        }
-      }
+      store_final(r, d, mstar, lt, ot);
     }
-    // No CTA may exit while another still reads its shared memory; with several clusters per (batch, KV head) the
-    // barrier also orders every CTA's slice of the partial (made visible by the fence) before the leader's ticket.
-    if (a.nparts > 1) __threadfence();
+    // no CTA may exit while another still reads its shared memory
     ptx::cluster_sync();
     DT_STAMP(4);
-    if (a.nparts == 1) return;
-    leader = crank == 0;
+    return;
   }
-  if (!leader) return;
 
   // ---------------- ticket: the last partial of this (batch, KV head) to arrive combines ----------------
   __threadfence();
@@ -752,9 +743,6 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
 // ---- host side ---------------------------------------------------------------------------------------
 
-#ifndef DT_DECODE_MAX_CLUSTER
-#define DT_DECODE_MAX_CLUSTER 16
-#endif
 constexpr int kMaxParts = 256;    // partials per (batch, KV head) the final combine has shared memory for
 constexpr int kMaxDevices = 64;
 constexpr int kVariants = 6;      // (fp16 | bf16) x (D = 64, 128, 256)
@@ -799,7 +787,7 @@ unsigned long long* g_decode_dbg = nullptr;
 
 struct Plan {
   int nsplit, units_per_split, total_units;
-  int cluster;  // CTAs per cluster wanted (a power of two that divides nsplit); the launch may have to use fewer
+  int cluster;  // nsplit when the splits should form one cluster, else 1 (the launch falls back to 1 when the device cannot co-schedule it)
 };
 
 // first 16-key unit any row of the call can see: row 0's window bound
@@ -807,12 +795,6 @@ int first_unit(const dt_sdpa_params& p) {
   if (p.sliding_window <= 0) return 0;
   const long long lo = (long long)(p.Sk - p.Sq) - p.sliding_window + 1;
   return lo <= 0 ? 0 : (int)(lo / kUnitKeys);
-}
-
-int largest_cluster(int nsplit, int cap) {
-  int c = 1;
-  while (c * 2 <= cap && nsplit % (c * 2) == 0) c *= 2;
-  return c;
 }
 
 // Split count: the path is bound by HBM, and what costs is the fixed part of a CTA (start-up, merge, combine), so
@@ -833,10 +815,6 @@ Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
   const int slots = (p.D > 128 ? 1 : 2) * sm_count();
   int ns = 1;
   while (pairs * ns * 2 <= slots && pl.total_units / (ns * 2) >= 4) ns *= 2;
-#ifdef DT_DECODE_ONE_CLUSTER
-  // variant: never more splits than one cluster holds, so that no partial goes through global memory
-  if (ns > DT_DECODE_MAX_CLUSTER) ns = DT_DECODE_MAX_CLUSTER;
-#endif
   int forced = (int)((p.flags >> 16) & 0xFFFu);
 #ifdef DT_BRINGUP
   if (const char* env = getenv("DTATTN_DECODE_SPLITS")) forced = atoi(env);
@@ -850,7 +828,8 @@ Plan make_plan(const dt_sdpa_params& p, int stream_keys) {
 #ifdef DT_BRINGUP
   if (const char* env = getenv("DTATTN_DECODE_CLUSTER")) cap = max(1, atoi(env));
 #endif
-  pl.cluster = largest_cluster(pl.nsplit, cap);
+  // one cluster for all splits of a pair, or none
+  pl.cluster = pl.nsplit > 1 && pl.nsplit <= cap && (pl.nsplit & (pl.nsplit - 1)) == 0 ? pl.nsplit : 1;
   return pl;
 }
 
@@ -875,6 +854,7 @@ struct Scratch {
   size_t bytes;
   unsigned int* status;    // device status word the kernel reports to
   bool stale;              // the memory keeps an earlier call's contents: clear the ticket counters first
+  bool reported_size;      // a caller workspace must hold what dt_sdpa_workspace_size reported, whatever this launch uses
   int too_small;           // status returned when the partials do not fit
 };
 
@@ -917,9 +897,7 @@ int usable_cluster(DeviceState* dev, int want) {
     }
     dev->max_cluster[vi] = best;
   }
-  int c = want;
-  while (c > dev->max_cluster[vi]) c /= 2;
-  return c < 1 ? 1 : c;
+  return want <= dev->max_cluster[vi] ? want : 1;
 }
 
 template <typename T, int D>
@@ -943,7 +921,11 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, const S
   const size_t pairs = (size_t)p.B * p.Hkv;
   DecodeArgs a{};
   a.cluster = pl.cluster > 1 ? usable_cluster<T, D>(dev, pl.cluster) : 1;
-  a.nparts = pl.nsplit / a.cluster;
+  a.nparts = a.cluster > 1 ? 1 : pl.nsplit;
+  if (scratch.reported_size) {
+    const size_t reported = plan_workspace_bytes(p, pl);
+    if (reported > 0 && (!scratch.ptr || scratch.bytes < reported)) return scratch.too_small;
+  }
   if (a.nparts > 1) {
     const size_t need = scratch_bytes(p, a.nparts);
     if (!scratch.ptr || scratch.bytes < need) return scratch.too_small;
@@ -1048,7 +1030,7 @@ int dispatch_decode(const dt_sdpa_params& p, const dt_decode_step_params* step, 
 }
 
 Scratch caller_workspace(void* workspace, size_t bytes) {
-  return Scratch{workspace, bytes, device_status_word(), false, DT_WORKSPACE};
+  return Scratch{workspace, bytes, device_status_word(), false, true, DT_WORKSPACE};
 }
 
 // Argument rules of the fused decode step on top of decode_supported().
@@ -1139,7 +1121,7 @@ extern "C" int dt_sdpa_decode_noalloc(const dt_sdpa_params* p, void* cuda_stream
   if (!d) return DT_NO_DEVICE;
   st = noalloc_setup(d);
   if (st != DT_OK) return st;
-  const Scratch scratch{d->noalloc_scratch, (size_t)DT_NOALLOC_SCRATCH_BYTES, d->noalloc_status, true, DT_SCRATCH_LIMIT};
+  const Scratch scratch{d->noalloc_scratch, (size_t)DT_NOALLOC_SCRATCH_BYTES, d->noalloc_status, true, false, DT_SCRATCH_LIMIT};
   return dispatch_decode(*p, nullptr, scratch, (cudaStream_t)cuda_stream);
 }
 

@@ -74,11 +74,11 @@ def test_decode_step_per_batch_table_and_no_table(dtattn):
     run_step(dtattn, c, 300, 128 ** -0.5, torch.bfloat16, "no rotary")
 
 
-@pytest.mark.parametrize("splits", [1, 3, 16, 32, 48])
+@pytest.mark.parametrize("splits", [1, 3, 4, 8, 16, 48])
 def test_decode_step_split_counts(dtattn, splits):
     """The appended rows are attended by the last split only, whatever the split count (fixed here with
-    DT_FLAG_DECODE_SPLITS): one CTA, an odd count (no cluster), one full cluster, two clusters whose partials go
-    through the workspace, three clusters."""
+    DT_FLAG_DECODE_SPLITS): one CTA, an odd count, clusters of 4 and 8 that combine through distributed shared
+    memory, and counts whose partials go through the workspace."""
     c = make_case(2, 1234, 2, 2, 8, 2, 128, torch.bfloat16, 721)
     run_step(dtattn, c, 1234, 128 ** -0.5, torch.bfloat16, f"splits={splits}", flags=dtattn.DT_FLAG_DECODE_SPLITS(splits))
 

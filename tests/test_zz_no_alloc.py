@@ -26,9 +26,9 @@ def test_noalloc_matches_workspace_entry_point_twice(dtattn):
     lib = dtattn.lib()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     # two different requests back to back: the second must not see anything of the first in the shared array
-    # (inputs, split count): the library's own choice keeps every split inside one cluster for the usual shapes, so
-    # most cases fix a count that makes the partials go through the scratch array (several clusters per KV head,
-    # or an odd count that forms no cluster); the head-dim-256 shape does so by itself
+    # (inputs, split count): with up to 8 splits per KV head the CTAs combine inside a thread-block cluster and
+    # need no scratch, so most cases fix a larger or an odd count, which makes the partials go through the scratch
+    # array; the batch-1 shapes (the last but one) do so by the library's own choice
     cases = [(_case(301, 2, 3000, 32, 8, 128, torch.float16), 48), (_case(311, 1, 8192, 32, 8, 128, torch.float16), 64),
              (_case(321, 3, 777, 8, 8, 64, torch.bfloat16), 5), (_case(341, 1, 8192, 16, 4, 256, torch.bfloat16), 0),
              (_case(351, 2, 3000, 32, 8, 128, torch.float16), 0)]
