@@ -165,11 +165,14 @@ int validate_params(const dt_sdpa_params* p) {
   return DT_OK;
 }
 
-enum Kernel { kGeneric = 0, kDecode = 1, kPrefill = 2 };
+enum Kernel { kGeneric = 0, kDecode = 1, kPrefill = 2, kShortKV = 3 };
 
 static Kernel choose(const dt_sdpa_params& p) {
   if (p.flags & DT_FLAG_FORCE_GENERIC) return kGeneric;
   if (decode_supported(p) && p.Sk >= 256) return kDecode;
+  // a short key/value sequence under many query rows: the dedicated streaming kernel (a handful of rows stays with
+  // the kernels below, which need fewer resources per launch)
+  if (short_kv_supported(p) && (long long)p.B * p.Hq * p.Sq >= 4096) return kShortKV;
   if (prefill_supported(p)) return kPrefill;
   if (decode_supported(p)) return kDecode;
   return kGeneric;
@@ -204,7 +207,7 @@ int dt_sdpa_kernel_name(const dt_sdpa_params* p, const char** name) {
   int st = validate_params(p);
   if (st != DT_OK) return st;
   if (!name) return DT_BAD_ARG;
-  static const char* names[3] = {"generic", "decode_splitkv", "prefill_tcgen05"};
+  static const char* names[4] = {"generic", "decode_splitkv", "prefill_tcgen05", "crossattn_short"};
   *name = names[choose(*p)];
   return DT_OK;
 }
@@ -230,6 +233,7 @@ int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_b
   switch (choose(*p)) {
     case kDecode: return launch_decode(*p, workspace, workspace_bytes, stream);
     case kPrefill: return launch_prefill(*p, stream);
+    case kShortKV: return launch_short_kv(*p, stream);
     default: return launch_generic(*p, stream);
   }
 }

@@ -49,6 +49,11 @@ bool prefill_supported(const dt_sdpa_params& p);
 // head-sharded mode) that receive a copy of every O tile.
 int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs = nullptr, int n_extra = 0);
 
+// Cross-attention over a short key/value sequence (Sk <= 96, head dim <= 64, the plain operator): three independent
+// warpgroup pipelines per CTA, TMA + tcgen05.
+bool short_kv_supported(const dt_sdpa_params& p);
+int launch_short_kv(const dt_sdpa_params& p, cudaStream_t stream);
+
 // C[B,S,N] = A[B,S,K] . W[N,K]^T + bias: the output projection behind the attention kernel (TMA + tcgen05 GEMM).
 int launch_out_proj(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
                     const dt_tensor4& out, int dtype, cudaStream_t stream);

@@ -1,0 +1,386 @@
+// Cross-attention over a SHORT key/value sequence for sm_100a: the text-conditioning attention of the UNet models
+// (Libraries/SwiftDiffusion/Sources/Models/UNetXL.swift:57-185, UNet.swift:269-504: thousands of image queries
+// against the 77 tokens of a text prompt).  All keys fit one block, so there is no online-softmax loop: a 128-row
+// query tile is  S = Q K^T  ->  row softmax  ->  O = P V  ->  store.  The path is bound by streaming Q in and O out
+// of HBM once, and what costs is the latency of that chain, so the CTA runs THREE independent chains:
+//
+//   three warpgroups (12 warps), each one a self-contained pipeline over its own run of query tiles.  Thread 0 of a
+//   warpgroup issues the TMA loads (Q tiles double-buffered one tile ahead, K/V once per head) and the tcgen05.mma
+//   instructions; all 128 threads are softmax / epilogue threads (one query row each).  While one warpgroup waits
+//   for its MMA or its loads the other two compute.
+//   per tile:  wait S -> S row from TMEM -> mask keys >= Sk -> max, exp2, sum -> P (16-bit) back to TMEM over S
+//              -> warpgroup barrier -> thread 0: O = P V, then S' = Q' K^T of the NEXT tile (the tensor pipe runs
+//              them in order, so S' may overwrite P) -> wait O -> O / l -> swizzled staging -> TMA store
+//   TMEM: warpgroup g owns columns [160 g, 160 g + 160): S / P in the first 96 (up to 96 keys), O in the last 64.
+//
+// fp16 / bf16, head dim <= 64 (zero-padded by TMA), Sk <= 96, no causal rule / window / mask / sinks (those take
+// the general kernel).  Every mbarrier wait is bounded and reports through the device status word; a warpgroup that
+// gives up still reaches the CTA-wide teardown, so TMEM is always released.
+#include <type_traits>
+
+#include "sm100_ptx.cuh"
+
+namespace dt {
+namespace {
+
+constexpr int kRows = 128;            // query rows per tile
+constexpr int kGroups = 3;            // warpgroups = independent pipelines per CTA
+constexpr int kThreadsShort = kGroups * 128;
+constexpr int kQBytes = 128 * 128;    // one Q tile: 128 rows x 64 x 16-bit, one TMA box
+constexpr int kStageBytesShort = 4 * 32 * 128;  // O staging of one warpgroup: 4 warps x 32 rows x 128 B
+constexpr uint32_t kColsPerGroup = 160, kColO = 96;
+
+template <int NU>  // NU = 16-key units of the key block (5: up to 80 keys, 6: up to 96)
+struct ShortCfg {
+  static constexpr int kKeys = NU * 16;
+  static constexpr int kKVBytes = kKeys * 128;  // K (or V) block: kKeys rows x 64 x 16-bit
+  static constexpr int kGroupBytes = 2 * kQBytes + 2 * kKVBytes + kStageBytesShort;
+  static constexpr int kSmemBytes = kGroups * kGroupBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct ShortArgs {
+  float* lse;
+  unsigned int* status;
+  int Sq, Sk, Hq, Hkv;
+  int n_qtiles, n_tiles;  // tiles = (batch, head, 128-row query tile), query tile fastest
+  float scale_log2;
+};
+
+struct GroupBars {
+  uint64_t q_full[2];
+  uint64_t kv_full;
+  uint64_t s_full;
+  uint64_t o_full;
+};
+
+__device__ __forceinline__ void group_sync(int group) {  // the 128 threads of one warpgroup
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (std::is_same<T, __half>::value) return ptx::cvt_pack_f16(lo, hi);
+  else return ptx::cvt_pack_bf16(lo, hi);
+}
+
+template <typename T, int NU>
+__global__ void __launch_bounds__(kThreadsShort, 1)
+crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                       const ShortArgs a) {
+  using C = ShortCfg<NU>;
+  constexpr int kBf16 = std::is_same<T, __half>::value ? 0 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s[kGroups];
+
+  const int group = threadIdx.x >> 7, tid = threadIdx.x & 127;
+  const int wig = tid >> 5, lane = tid & 31;  // warp in group, lane
+  const bool leader = tid == 0;
+  // this warpgroup's shared memory: [Q buffer 0][Q buffer 1][K][V][O staging]
+  uint8_t* g_ptr = base_ptr + group * C::kGroupBytes;
+  const uint32_t g_smem = base + (uint32_t)(group * C::kGroupBytes);
+  const uint32_t k_smem = g_smem + 2 * kQBytes, v_smem = k_smem + C::kKVBytes;
+  const uint32_t stage_smem = v_smem + C::kKVBytes + (uint32_t)wig * (32 * 128);
+  GroupBars* bars = reinterpret_cast<GroupBars*>(base_ptr + kGroups * C::kGroupBytes) + group;
+  volatile int* abort_flag = &abort_s[group];
+
+  if (leader) {
+    ptx::mbar_init(&bars->q_full[0], 1);
+    ptx::mbar_init(&bars->q_full[1], 1);
+    ptx::mbar_init(&bars->kv_full, 1);
+    ptx::mbar_init(&bars->s_full, 1);
+    ptx::mbar_init(&bars->o_full, 1);
+    abort_s[group] = 0;
+    ptx::fence_mbar_init();
+  }
+  if (threadIdx.x < 32) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_all = tmem_base_s;
+  const uint32_t tmem = tmem_all + (uint32_t)group * kColsPerGroup;
+  const uint32_t lane_addr = (uint32_t)(wig << 5) << 16;
+  const uint32_t t_s = tmem + lane_addr, t_o = tmem + kColO + lane_addr;
+
+  // this warpgroup's run of tiles: an even share of all (batch, head, query tile) triples, consecutive, so that
+  // most of a run reads one head's K/V
+  const long long n_groups = (long long)gridDim.x * kGroups, gi = (long long)blockIdx.x * kGroups + group;
+  const int t_begin = (int)(gi * a.n_tiles / n_groups), t_end = (int)((gi + 1) * a.n_tiles / n_groups);
+  const int G = a.Hq / a.Hkv;
+  struct Tile { int b, h, kvh, q0; };
+  auto decode_tile = [&](int t) {
+    Tile w;
+    const int bh = t / a.n_qtiles;
+    w.q0 = (t - bh * a.n_qtiles) * kRows;
+    w.b = bh / a.Hq;
+    w.h = bh - w.b * a.Hq;
+    w.kvh = w.h / G;
+    return w;
+  };
+
+  constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kRows, C::kKeys, 0, 0);
+  constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kRows, 64, 0, 1);
+  const uint64_t desc_q0 = ptx::make_smem_desc_sw128(g_smem, 16, 1024);              // K-major: Q buffers, K
+  const uint64_t desc_k = ptx::make_smem_desc_sw128(k_smem, 16, 1024);
+  const uint64_t desc_v = ptx::make_smem_desc_sw128(v_smem, (uint32_t)C::kKVBytes, 1024);  // MN-major: V
+  auto issue_qk = [&](int buf) {  // S = Q[buf] K^T: four steps of 16 head dims, 32 B apart inside the 128-byte rows
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      ptx::mma_ss(tmem, desc_q0 + (uint64_t)((buf * kQBytes + ks * 32) >> 4), desc_k + (uint64_t)((ks * 32) >> 4), idesc_qk,
+                  ks > 0 ? 1u : 0u);
+    ptx::tc_commit(&bars->s_full);
+  };
+  auto load_q = [&](int buf, const Tile& w) {
+    ptx::mbar_arrive_expect_tx(&bars->q_full[buf], (uint32_t)kQBytes);
+    ptx::tma_load_4d(g_ptr + buf * kQBytes, &map_q, &bars->q_full[buf], 0, w.h, w.q0, w.b);
+  };
+  auto load_kv = [&](const Tile& w) {
+    ptx::mbar_arrive_expect_tx(&bars->kv_full, (uint32_t)(2 * C::kKVBytes));
+    ptx::tma_load_4d(g_ptr + 2 * kQBytes, &map_k, &bars->kv_full, 0, w.kvh, 0, w.b);
+    ptx::tma_load_4d(g_ptr + 2 * kQBytes + C::kKVBytes, &map_v, &bars->kv_full, 0, w.kvh, 0, w.b);
+  };
+  auto give_up = [&](unsigned code) {
+    atomicCAS(a.status, 0u, code);
+    *abort_flag = 1;
+  };
+
+  uint32_t qph0 = 0, qph1 = 0, kvph = 0, sph = 0, oph = 0;  // barrier phases (q / kv: leader only)
+  if (leader && t_begin < t_end) {
+    // prologue: K/V of the first head, the first two Q tiles, the first S
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+    ptx::prefetch_tensormap(&map_o);
+    const Tile w0 = decode_tile(t_begin);
+    load_kv(w0);
+    load_q(0, w0);
+    if (t_begin + 1 < t_end) load_q(1, decode_tile(t_begin + 1));
+    if (ptx::mbar_wait(&bars->kv_full, kvph, abort_flag) && ptx::mbar_wait(&bars->q_full[0], qph0, abort_flag)) {
+      kvph ^= 1;
+      qph0 ^= 1;
+      ptx::tc_fence_after();
+      issue_qk(0);
+    } else {
+      give_up(1u);
+    }
+  }
+
+  for (int t = t_begin; t < t_end; ++t) {
+    const int buf = (t - t_begin) & 1;
+    const Tile w = decode_tile(t);
+    const int row = w.q0 + (wig << 5) + lane;
+    float l = 0.f, m = -INFINITY;
+    // ---- S row -> P row ----
+    bool good = __all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full, sph, abort_flag));
+    sph ^= 1;
+    if (good) {
+      ptx::tc_fence_after();
+      if (leader && t + 2 < t_end) {  // S(t) is complete, so Q buffer `buf` is free: fetch the tile after next into it
+        load_q(buf, decode_tile(t + 2));
+      }
+      __syncwarp();
+      uint32_t s[NU][16];
+#pragma unroll
+      for (int u = 0; u < NU; ++u) ptx::tmem_ld16(t_s + u * 16, s[u]);
+      ptx::tc_wait_ld();
+      // keys >= Sk are TMA zero fill (score 0, not -inf): hide them
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+        if (u * 16 + 15 < a.Sk) continue;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (u * 16 + i >= a.Sk) s[u][i] = 0xff800000u;
+      }
+      float mx[NU];
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+        mx[u] = ptx::max3(__uint_as_float(s[u][0]), __uint_as_float(s[u][1]), __uint_as_float(s[u][2]));
+#pragma unroll
+        for (int i = 3; i < 15; i += 2) mx[u] = ptx::max3(mx[u], __uint_as_float(s[u][i]), __uint_as_float(s[u][i + 1]));
+        mx[u] = fmaxf(mx[u], __uint_as_float(s[u][15]));
+      }
+      float mall = mx[0];
+#pragma unroll
+      for (int u = 1; u < NU; ++u) mall = fmaxf(mall, mx[u]);
+      m = mall * a.scale_log2;  // scale > 0 is a precondition of this kernel
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
+      const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
+      const uint64_t scale2 = ptx::pack_f32x2(a.scale_log2, a.scale_log2);
+      uint64_t lsum[2] = {0ull, 0ull};
+      uint32_t pk[48];  // P as 16-bit pairs: 8 columns per 16 keys; the columns beyond NU * 8 stay zero
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[u][2 * i]), __uint_as_float(s[u][2 * i + 1])),
+                                             scale2, neg_m2);
+          float p0, p1;
+          if ((i % 3) == 2) {  // a share of the exponentials runs on the FMA pipes instead of the special-function unit
+            ptx::exp2_poly_x2(x2, p0, p1);
+          } else {
+            float x0, x1;
+            ptx::unpack_f32x2(x2, x0, x1);
+            p0 = fast_exp2(x0);
+            p1 = fast_exp2(x1);
+          }
+          lsum[i & 1] = ptx::add_f32x2(lsum[i & 1], ptx::pack_f32x2(p0, p1));
+          pk[u * 8 + i] = pack16<T>(p0, p1);
+        }
+      }
+#pragma unroll
+      for (int i = NU * 8; i < 48; ++i) pk[i] = 0u;
+      ptx::tmem_st16(t_s + 0, pk);
+      ptx::tmem_st16(t_s + 16, pk + 16);
+      ptx::tmem_st16(t_s + 32, pk + 32);
+      ptx::tc_wait_st();
+      float a0, a1;
+      ptx::unpack_f32x2(ptx::add_f32x2(lsum[0], lsum[1]), a0, a1);
+      l = a0 + a1;
+    } else {
+      give_up(3u);
+    }
+    // every thread of the warpgroup gets here (also after a wait that ran out), so the barrier cannot hang
+    ptx::tc_fence_before();
+    group_sync(group);
+    if (*abort_flag) break;  // the same answer for all 128 threads: the flag was written before the barrier
+
+    // ---- leader: O = P V, then the next tile's S = Q K^T behind it in the tensor pipe ----
+    if (leader) {
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < NU; ++kk)
+        ptx::mma_ts(tmem + kColO, tmem + kk * 8, desc_v + (uint64_t)(kk * (2048 >> 4)), idesc_pv, kk > 0 ? 1u : 0u);
+      ptx::tc_commit(&bars->o_full);
+      if (t + 1 < t_end) {
+        const Tile nx = decode_tile(t + 1);
+        bool ready = true;
+        if (nx.b != w.b || nx.kvh != w.kvh) {
+          // another head: its K/V replace the current ones once the P V above has read V (S(t) read K long ago)
+          ready = ptx::mbar_wait(&bars->o_full, oph, abort_flag);
+          if (ready) {
+            load_kv(nx);
+            ready = ptx::mbar_wait(&bars->kv_full, kvph, abort_flag);
+            kvph ^= 1;
+          }
+        }
+        uint32_t& qph = buf ? qph0 : qph1;  // the next tile sits in the other Q buffer
+        ready = ready && ptx::mbar_wait(&bars->q_full[buf ^ 1], qph, abort_flag);
+        qph ^= 1;
+        if (ready) {
+          ptx::tc_fence_after();
+          issue_qk(buf ^ 1);
+        } else {
+          give_up(1u);
+        }
+      }
+    }
+    __syncwarp();
+
+    // ---- epilogue: O / l -> swizzled staging rows -> one TMA store per warp ----
+    good = __all_sync(0xffffffffu, ptx::mbar_wait(&bars->o_full, oph, abort_flag));
+    oph ^= 1;
+    if (!good) {
+      give_up(5u);
+      continue;  // the next pass ends at the barrier above for the whole warpgroup
+    }
+    ptx::tc_fence_after();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (lane == 0) ptx::bulk_wait_read_all();  // the previous store of this warp has read the staging rows
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t ov[32];
+      ptx::tmem_ld32(t_o + c * 32, ov);
+      ptx::tc_wait_ld();
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint32_t x = pack16<T>(__uint_as_float(ov[v * 8 + 0]) * inv, __uint_as_float(ov[v * 8 + 1]) * inv);
+        const uint32_t y = pack16<T>(__uint_as_float(ov[v * 8 + 2]) * inv, __uint_as_float(ov[v * 8 + 3]) * inv);
+        const uint32_t z = pack16<T>(__uint_as_float(ov[v * 8 + 4]) * inv, __uint_as_float(ov[v * 8 + 5]) * inv);
+        const uint32_t ww = pack16<T>(__uint_as_float(ov[v * 8 + 6]) * inv, __uint_as_float(ov[v * 8 + 7]) * inv);
+        // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
+        const uint32_t q = (uint32_t)(c * 4 + v);
+        const uint32_t addr = stage_smem + (uint32_t)lane * 128 + ((q ^ ((uint32_t)lane & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(ww) : "memory");
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    const int wrow0 = w.q0 + (wig << 5);
+    if (lane == 0 && wrow0 < a.Sq) {  // rows beyond Sq are clipped by the tensor map
+      ptx::tma_store_4d(&map_o, stage_smem, 0, w.h, wrow0, w.b);
+      ptx::bulk_commit_group();
+    }
+    if (a.lse && row < a.Sq) a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
+    // the next tile's P V overwrites O: order this thread's TMEM reads before the barrier it arrives at next
+    ptx::tc_fence_before();
+  }
+
+  // =========================== teardown ===========================
+  if (lane == 0) ptx::bulk_wait_all();
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_all, 512);
+  }
+}
+
+template <typename T, int NU>
+int launch_short_t(const dt_sdpa_params& p, cudaStream_t stream) {
+  using C = ShortCfg<NU>;
+  CUtensorMap mq, mk, mv, mo;
+  if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, p.D, p.dtype, kRows)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, p.D, p.dtype, C::kKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mv, p.v, p.B, p.Sk, p.Hkv, p.D, p.dtype, C::kKeys)) return DT_UNSUPPORTED;
+  if (!make_bshd_tensor_map(&mo, p.o, p.B, p.Sq, p.Hq, p.D, p.dtype, 32)) return DT_UNSUPPORTED;
+  ShortArgs a{};
+  a.lse = p.lse;
+  a.status = device_status_word();
+  if (!a.status) return DT_CUDA;
+  a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv;
+  a.n_qtiles = (p.Sq + kRows - 1) / kRows;
+  const long long tiles = (long long)a.n_qtiles * p.Hq * p.B;
+  if (tiles > 0x7fffffffLL) return DT_UNSUPPORTED;
+  a.n_tiles = (int)tiles;
+  a.scale_log2 = p.scale * kLog2e;
+  auto kern = crossattn_short_kernel<T, NU>;
+  DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  const int n_sm = device_sm_count();
+  const int want = (a.n_tiles + kGroups - 1) / kGroups;  // at least one tile per warpgroup
+  dim3 grid(want < n_sm ? want : n_sm);                   // one persistent CTA per SM
+  kern<<<grid, kThreadsShort, C::kSmemBytes, stream>>>(mq, mk, mv, mo, a);
+  DT_CUDA_TRY(cudaGetLastError());
+  return DT_OK;
+}
+
+}  // namespace
+
+bool short_kv_supported(const dt_sdpa_params& p) {
+  if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
+  if (p.D < 8 || p.D > 64 || p.D % 8) return false;
+  if (p.Sk > 96) return false;
+  if (p.is_causal || p.sliding_window > 0 || p.mask || p.sinks || p.seq_offsets_q) return false;
+  if (!(p.scale > 0.f)) return false;
+  if (p.Hq % p.Hkv || p.Hq > 65535 || p.B > 65535) return false;
+  auto ok = [](const dt_tensor4& t) {
+    return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && t.stride_b % 8 == 0 && t.stride_s % 8 == 0 &&
+           t.stride_h % 8 == 0;
+  };
+  return ok(p.q) && ok(p.k) && ok(p.v) && ok(p.o);
+}
+
+int launch_short_kv(const dt_sdpa_params& p, cudaStream_t stream) {
+  const bool five = p.Sk <= 80;
+  if (p.dtype == DT_F16) return five ? launch_short_t<__half, 5>(p, stream) : launch_short_t<__half, 6>(p, stream);
+  return five ? launch_short_t<__nv_bfloat16, 5>(p, stream) : launch_short_t<__nv_bfloat16, 6>(p, stream);
+}
+
+}  // namespace dt

@@ -117,7 +117,11 @@ def test_kernel_selection(dtattn):
 
     assert pick(2, 4096, 4096, 8, 8, 40, torch.float32) == "generic"              # SD1.5 self-attention, fp32 (upcast)
     assert pick(2, 4096, 4096, 8, 8, 40, torch.float16) == "prefill_tcgen05"       # SD1.5 in half precision: D padded to 64
-    assert pick(2, 4096, 77, 20, 20, 64, torch.float16) == "prefill_tcgen05"       # SDXL cross-attention
+    assert pick(2, 4096, 77, 20, 20, 64, torch.float16) == "crossattn_short"       # SDXL cross-attention: 77 text tokens
+    assert pick(2, 4096, 77, 8, 8, 40, torch.float16) == "crossattn_short"         # SD1.5 cross-attention
+    assert pick(1, 128, 77, 2, 2, 64, torch.float16) == "prefill_tcgen05"          # a handful of rows: the general kernel
+    assert pick(2, 64, 77, 20, 20, 64, torch.float16, True) == "prefill_tcgen05"   # causal: the general kernel
+    assert pick(2, 4096, 128, 20, 20, 64, torch.float16) == "prefill_tcgen05"      # more than 96 keys
     assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16) == "prefill_tcgen05"   # Flux joint attention
     assert pick(1, 75600, 75600, 5, 5, 128, torch.bfloat16) == "prefill_tcgen05"   # Wan, one rank's heads
     assert pick(16, 1, 8192, 32, 8, 128, torch.float16, True) == "decode_splitkv"  # GQA decode

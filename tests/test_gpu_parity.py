@@ -207,7 +207,7 @@ PREFILL = [
     (1, 256, 1536, 2, 2, 128, torch.float16, False),   # ring wraps (12 K/V blocks through 5 slots)
     (2, 300, 333, 3, 3, 128, torch.bfloat16, False),   # ragged rows and keys, batch
     (1, 128, 77, 2, 2, 64, torch.float16, False),      # SDXL cross-attention shape, head dim 64
-    (2, 640, 77, 4, 4, 64, torch.float16, False),
+    (2, 500, 77, 4, 4, 64, torch.float16, False),      # (larger short-key shapes take the dedicated kernel: test_gpu_short_kv.py)
     (1, 512, 512, 4, 2, 64, torch.bfloat16, False),    # grouped KV heads
     (1, 384, 384, 2, 2, 128, torch.bfloat16, True),    # causal
     (1, 200, 456, 2, 1, 128, torch.float16, True),     # causal, bottom-right aligned, ragged
