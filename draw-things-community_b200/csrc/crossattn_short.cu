@@ -23,6 +23,9 @@
 namespace dt {
 namespace {
 
+#ifndef DT_SHORT_POLY
+#define DT_SHORT_POLY 1
+#endif
 constexpr int kRows = 128;            // query rows per tile
 constexpr int kGroups = 3;            // warpgroups = independent pipelines per CTA
 constexpr int kThreadsShort = kGroups * 128;
@@ -44,7 +47,17 @@ struct ShortArgs {
   int Sq, Sk, Hq, Hkv;
   int n_qtiles, n_tiles;  // tiles = (batch, head, 128-row query tile), query tile fastest
   float scale_log2;
+#ifdef DT_BRINGUP
+  unsigned long long* dbg;  // timeline probe: [warpgroup run][tile of the run][8] globaltimer stamps
+#endif
 };
+
+#ifdef DT_BRINGUP
+unsigned long long* g_short_dbg = nullptr;
+#define DT_SSTAMP(k) do { if (a.dbg && leader && (t - t_begin) < 8) a.dbg[(gi * 8 + (t - t_begin)) * 8 + (k)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define DT_SSTAMP(k) do { } while (0)
+#endif
 
 struct GroupBars {
   uint64_t q_full[2];
@@ -97,17 +110,12 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     abort_s[group] = 0;
     ptx::fence_mbar_init();
   }
-  if (threadIdx.x < 32) {
-    ptx::tmem_alloc(&tmem_base_s, 512);
-    ptx::tmem_relinquish();
+  if (leader) {
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+    ptx::prefetch_tensormap(&map_o);
   }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem_all = tmem_base_s;
-  const uint32_t tmem = tmem_all + (uint32_t)group * kColsPerGroup;
-  const uint32_t lane_addr = (uint32_t)(wig << 5) << 16;
-  const uint32_t t_s = tmem + lane_addr, t_o = tmem + kColO + lane_addr;
 
   // this warpgroup's run of tiles: an even share of all (batch, head, query tile) triples, consecutive, so that
   // most of a run reads one head's K/V
@@ -125,6 +133,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     return w;
   };
 
+  uint32_t tmem_all = 0, tmem = 0, t_s = 0, t_o = 0;  // set once TMEM is allocated (below)
   constexpr uint32_t idesc_qk = ptx::make_idesc_f16(kBf16, kRows, C::kKeys, 0, 0);
   constexpr uint32_t idesc_pv = ptx::make_idesc_f16(kBf16, kRows, 64, 0, 1);
   const uint64_t desc_q0 = ptx::make_smem_desc_sw128(g_smem, 16, 1024);              // K-major: Q buffers, K
@@ -152,16 +161,29 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   };
 
   uint32_t qph0 = 0, qph1 = 0, kvph = 0, sph = 0, oph = 0;  // barrier phases (q / kv: leader only)
+#ifdef DT_BRINGUP
+  if (a.dbg && leader) a.dbg[(gi * 8 + 7) * 8 + 7] = ptx::globaltimer_ns();  // start of this warpgroup's run
+#endif
   if (leader && t_begin < t_end) {
-    // prologue: K/V of the first head, the first two Q tiles, the first S
-    ptx::prefetch_tensormap(&map_q);
-    ptx::prefetch_tensormap(&map_k);
-    ptx::prefetch_tensormap(&map_v);
-    ptx::prefetch_tensormap(&map_o);
+    // first loads (K/V of the first head, the first two Q tiles): issued before the CTA-wide barrier below, they
+    // need only this warpgroup's own barriers and run while TMEM is being allocated
     const Tile w0 = decode_tile(t_begin);
     load_kv(w0);
     load_q(0, w0);
     if (t_begin + 1 < t_end) load_q(1, decode_tile(t_begin + 1));
+  }
+  if (threadIdx.x < 32) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  tmem_all = tmem_base_s;
+  tmem = tmem_all + (uint32_t)group * kColsPerGroup;
+  t_s = tmem + ((uint32_t)(wig << 5) << 16);
+  t_o = t_s + kColO;
+  if (leader && t_begin < t_end) {
     if (ptx::mbar_wait(&bars->kv_full, kvph, abort_flag) && ptx::mbar_wait(&bars->q_full[0], qph0, abort_flag)) {
       kvph ^= 1;
       qph0 ^= 1;
@@ -178,8 +200,10 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int row = w.q0 + (wig << 5) + lane;
     float l = 0.f, m = -INFINITY;
     // ---- S row -> P row ----
+    DT_SSTAMP(0);
     bool good = __all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full, sph, abort_flag));
     sph ^= 1;
+    DT_SSTAMP(1);
     if (good) {
       ptx::tc_fence_after();
       if (leader && t + 2 < t_end) {  // S(t) is complete, so Q buffer `buf` is free: fetch the tile after next into it
@@ -222,7 +246,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[u][2 * i]), __uint_as_float(s[u][2 * i + 1])),
                                              scale2, neg_m2);
           float p0, p1;
-          if ((i % 3) == 2) {  // a share of the exponentials runs on the FMA pipes instead of the special-function unit
+          if (DT_SHORT_POLY && (i % 3) == 2) {  // a share of the exponentials runs on the FMA pipes instead of the special-function unit
             ptx::exp2_poly_x2(x2, p0, p1);
           } else {
             float x0, x1;
@@ -250,6 +274,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     ptx::tc_fence_before();
     group_sync(group);
     if (*abort_flag) break;  // the same answer for all 128 threads: the flag was written before the barrier
+    DT_SSTAMP(2);
 
     // ---- leader: O = P V, then the next tile's S = Q K^T behind it in the tensor pipe ----
     if (leader) {
@@ -281,6 +306,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
     }
+    DT_SSTAMP(3);
     __syncwarp();
 
     // ---- epilogue: O / l -> swizzled staging rows -> one TMA store per warp ----
@@ -290,6 +316,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       give_up(5u);
       continue;  // the next pass ends at the barrier above for the whole warpgroup
     }
+    DT_SSTAMP(4);
     ptx::tc_fence_after();
     const float inv = l > 0.f ? 1.f / l : 0.f;
     if (lane == 0) ptx::bulk_wait_read_all();  // the previous store of this warp has read the staging rows
@@ -321,6 +348,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (a.lse && row < a.Sq) a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
     // the next tile's P V overwrites O: order this thread's TMEM reads before the barrier it arrives at next
     ptx::tc_fence_before();
+    DT_SSTAMP(5);
   }
 
   // =========================== teardown ===========================
@@ -351,6 +379,9 @@ int launch_short_t(const dt_sdpa_params& p, cudaStream_t stream) {
   if (tiles > 0x7fffffffLL) return DT_UNSUPPORTED;
   a.n_tiles = (int)tiles;
   a.scale_log2 = p.scale * kLog2e;
+#ifdef DT_BRINGUP
+  a.dbg = g_short_dbg;
+#endif
   auto kern = crossattn_short_kernel<T, NU>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   const int n_sm = device_sm_count();
@@ -384,3 +415,11 @@ int launch_short_kv(const dt_sdpa_params& p, cudaStream_t stream) {
 }
 
 }  // namespace dt
+
+#ifdef DT_BRINGUP
+// Bring-up builds only: timeline buffer of the short key/value kernel.
+extern "C" int dt_internal_set_short_dump(unsigned long long* device_buffer) {
+  dt::g_short_dbg = device_buffer;
+  return 0;
+}
+#endif
