@@ -264,6 +264,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle, 16-bit elements.
 //   K-major operand (rows of 64 elements = 128 B, 8-row groups 1024 B apart): lbo = 1 (unused), sbo = 1024 B.
 //   MN-major operand ([k][64 contiguous MN elements], 8-k groups 1024 B apart, next 64 MN elements
