@@ -140,6 +140,37 @@ def make_sets(w, n_sets, device, heads=None, seed=0):
     return sets
 
 
+def make_head_inputs(w, h, device):
+    """q, k, v of ONE head ([B, S, 1, D]) from a seed that depends only on the head, so that every rank can rebuild
+    any head's inputs when it checks the gathered output."""
+    g = torch.Generator(device=device).manual_seed(3000 + h)
+    dt = TDT[w["dtype"]]
+    q = torch.randn((w["B"], w["Sq"], 1, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+    k = torch.randn((w["B"], w["Sk"], 1, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+    v = torch.randn((w["B"], w["Sk"], 1, w["D"]), generator=g, device=device, dtype=torch.float32).to(dt)
+    return q, k, v
+
+
+def check_gathered_output(w, o_full, device, n_rows=64):
+    """Sampled rows x ALL heads of the gathered output against the CPU oracle (the checker, outside every timed
+    region).  Head by head: the head's K/V are rebuilt from its seed, moved to the host, and the C oracle computes the
+    sampled query rows over all keys.  Returns (max_abs, mean_abs, rows, heads)."""
+    from oracle import c_oracle
+    S = w["Sq"]
+    rows = torch.linspace(0, S - 1, n_rows).round().long().unique()
+    mx, tot, cnt = 0.0, 0.0, 0
+    for h in range(w["Hq"]):
+        q, k, v = make_head_inputs(w, h, device)
+        ref = c_oracle.sdpa_c(q[:, rows.to(device)].float().cpu(), k.float().cpu(), v.float().cpu(), w["D"] ** -0.5, False)
+        got = o_full[:, rows.to(device), h:h + 1].float().cpu()
+        d = (got - ref).abs()
+        mx = max(mx, float(d.max()))
+        tot += float(d.sum())
+        cnt += d.numel()
+        del q, k, v
+    return mx, tot / max(cnt, 1), int(rows.numel()), w["Hq"]
+
+
 def time_device(fn, steps, warmup):
     """CUDA-event time of `steps` calls of fn(i) on the current stream, after `warmup` calls."""
     for i in range(warmup):
@@ -221,7 +252,35 @@ def side_measurements(dtattn, device, peaks):
     out.update(decode_step_measurements(dtattn, device))
     out.update(prologue_measurements(dtattn, device, peaks))
     out.update(out_proj_measurements(dtattn, device, peaks))
+    out.update(masked_measurements(dtattn, device, peaks))
     return out
+
+
+def masked_measurements(dtattn, device, peaks):
+    """An LLM text encoder's attention (Llama.swift:57-96: 32 query heads over 8 KV heads, d128, isCausal plus a
+    padding mask shared by the heads) at 4096 tokens: the additive mask on the tensor-core kernel, beside the same
+    call without the mask.  FLOPs count the visible half of the causal square."""
+    B, S, Hq, Hkv, D, dt = 1, 4096, 32, 8, 128, torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(29)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=device, dtype=torch.float32).to(dt)
+    n_sets = 4
+    sets = [(rnd(B, S, Hq, D), rnd(B, S, Hkv, D), rnd(B, S, Hkv, D), torch.empty(B, S, Hq, D, device=device, dtype=dt))
+            for _ in range(n_sets)]
+    mask = torch.zeros(1, 1, S, S, device=device, dtype=dt)
+    mask[..., 3800:] = -torch.finfo(dt).max  # the last 296 positions are padding
+    scale = D ** -0.5
+    p = dtattn.make_params(sets[0][0], sets[0][1], sets[0][2], sets[0][3], scale, True, mask)
+    fl = 4.0 * B * Hq * S * (S + 1) / 2 * D
+    res = {"kernel": dtattn.kernel_name(p), "shape": dict(B=B, S=S, Hq=Hq, Hkv=Hkv, D=D), "visible_gflop": round(fl / 1e9, 1)}
+    for label, m in (("masked", mask), ("causal_only", None)):
+        fns = [(lambda s=s, m=m: dtattn.sdpa_forward(s[0], s[1], s[2], scale, True, m, out=s[3])) for s in sets]
+        ms = time_graph(fns, reps=5)
+        res["us_" + label] = round(ms * 1e3, 1)
+        res["tflops_" + label] = round(fl / (ms * 1e-3) / 1e12, 1)
+        res["frac_bf16_peak_" + label] = round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)
+    del sets
+    torch.cuda.empty_cache()
+    return {"llm_text_encoder_masked": res}
 
 
 def out_proj_measurements(dtattn, device, peaks):
@@ -353,9 +412,22 @@ def cpu_baseline(w, max_seconds=25.0):
     c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
     dt_s = time.perf_counter() - t0
     fl = 4 * w["B"] * w["Hq"] * sample_rows * w["Sk"] * w["D"]
+    # second opinion on what these host cores can do: torch's own CPU attention (fp32, all threads) on the same sample
+    sanity = None
+    try:
+        import torch.nn.functional as F
+        qt, kt, vt = (x.permute(0, 2, 1, 3).contiguous() for x in (q, k, v))
+        F.scaled_dot_product_attention(qt[:, :, :64], kt, vt, enable_gqa=w["Hq"] != w["Hkv"])
+        t0 = time.perf_counter()
+        F.scaled_dot_product_attention(qt, kt, vt, enable_gqa=w["Hq"] != w["Hkv"])
+        sanity = {"value": round(fl / (time.perf_counter() - t0) / 1e12, 5), "unit": UNIT, "threads": torch.get_num_threads(),
+                  "what": "torch.nn.functional.scaled_dot_product_attention on the CPU, same sample"}
+    except Exception as e:  # a sanity figure must not take the line down
+        sanity = {"error": str(e)[:120]}
     return {"value": round(fl / dt_s / 1e12, 5), "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{sample_rows} of {rows} query rows x all {w['Hq']} heads x all {w['Sk']} keys, fp32, "
-                      f"{dt_s:.1f} s; non-causal so every sampled row costs the same"}
+                      f"{dt_s:.1f} s; non-causal so every sampled row costs the same",
+            "torch_cpu_sdpa": sanity}
 
 
 def run_reference(args):
@@ -376,10 +448,12 @@ def run_reference(args):
     c_oracle.sdpa_c(probe, k, v, w["D"] ** -0.5, w["causal"] and False)
     per_row = (time.perf_counter() - t0) / 8
     rows = int(max(8, min(w["Sq"], 3.0 / max(per_row, 1e-9))))
+    if name == "wan_self":  # the long video shape is sampled on at least 512 query rows per step
+        rows = max(rows, 512)
     q = torch.randn((w["B"], rows, w["Hq"], w["D"]), generator=g)
     for _ in range(min(args.warmup, 1)):
         c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, min(args.steps, 5 if name != "wan_self" else 3))
     t0 = time.perf_counter()
     for _ in range(steps):
         c_oracle.sdpa_c(q, k, v, w["D"] ** -0.5, False)
@@ -455,7 +529,9 @@ def run_single(args, dtattn, device, peaks):
             "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": name, **{k2: w[k2] for k2 in ("B", "Sq", "Sk", "Hq", "Hkv", "D")},
-                       "l2": f"rotating {n_sets} input sets of {nbytes >> 20} MiB (> 126 MiB L2 in total)"},
+                       "l2": f"rotating {n_sets} input sets of {nbytes >> 20} MiB (> 126 MiB L2 in total)",
+                       "inputs": "N(0,1) drawn on the device (the values do not change the time; the parity tests run the "
+                                 "same shape on CPU-seeded inputs with the rotary table applied)"},
             "clocks": clk.summary(), "roofline": roof, "cpu_baseline": base,
             "e2e": {"value": round(fl / e2e_s / 1e12, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_s * 1e3, 3), "api": "dt_sdpa_forward_host (pinned host tensors)"},
@@ -482,6 +558,10 @@ def run_sharded(args, dtattn, device, peaks):
     nbytes_local = bytes_of(w) // world
     n_sets = 2 if nbytes_local > L2_BYTES else min(8, -(-2 * L2_BYTES // nbytes_local) + 1)
     sets = make_sets(w, n_sets, device, heads=hl, seed=rank)
+    # set 0 is rebuilt from per-head seeds (this rank's heads), so that the gathered output can be checked afterwards
+    heads = [make_head_inputs(w, rank * hl + j, device) for j in range(hl)]
+    sets[0] = tuple(torch.cat([t[i] for t in heads], dim=2).contiguous() for i in range(3)) + (sets[0][3],)
+    del heads
     o_full = [torch.empty((w["B"], w["Sq"], w["Hq"], w["D"]), dtype=TDT[w["dtype"]], device=device) for _ in range(2)]
     chunks = args.chunks
     fused = not args.no_fused
@@ -519,9 +599,22 @@ def run_sharded(args, dtattn, device, peaks):
     fl = flops_of(w)
     tflops = fl / (ms_step * 1e-3) / 1e12
 
-    # end to end: local q/k/v from pinned host memory, full gathered output back to pinned host memory
+    # parity of the gathered result, outside every timed region: one more step on the per-head seeded inputs, then
+    # sampled rows x all heads of THIS rank's copy of the full output against the CPU oracle
+    comm.forward(sets[0][0], sets[0][1], sets[0][2], scale, o_full[0], chunks=chunks)
+    torch.cuda.synchronize()
+    dist.barrier()
+    p_max, p_mean, p_rows, p_heads = check_gathered_output(w, o_full[0], device) if not args.no_parity else (0.0, 0.0, 0, 0)
+    tp = torch.tensor([p_max, p_mean], device=device)
+    dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+    p_max, p_mean = float(tp[0].item()), float(tp[1].item())
+    parity_ok = p_max <= 2e-3 and p_mean <= 2e-4
+
+    # end to end: local q/k/v from pinned host memory; every rank holds the full output on its GPU and returns ITS
+    # block of rows to pinned host memory, so the result crosses the N PCIe links once, in parallel
     hq, hk, hv, _ = [x.cpu().pin_memory() for x in sets[0]]
-    ho = torch.empty(o_full[0].shape, dtype=o_full[0].dtype).pin_memory()
+    r0, r1 = rank * w["Sq"] // world, (rank + 1) * w["Sq"] // world
+    ho = torch.empty((w["B"], r1 - r0, w["Hq"], w["D"]), dtype=o_full[0].dtype).pin_memory()
     dq, dk, dv = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1]), torch.empty_like(sets[0][2])
 
     def e2e_step():
@@ -529,7 +622,7 @@ def run_sharded(args, dtattn, device, peaks):
         dk.copy_(hk, non_blocking=True)
         dv.copy_(hv, non_blocking=True)
         comm.forward(dq, dk, dv, scale, o_full[0], chunks=chunks)
-        ho.copy_(o_full[0], non_blocking=True)
+        ho.copy_(o_full[0][:, r0:r1], non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_step()
@@ -605,7 +698,12 @@ def run_sharded(args, dtattn, device, peaks):
                 "cpu_baseline": None,
                 "e2e": {"value": round(fl / e2e_s / 1e12, 3), "unit": UNIT,
                         "h2d_bytes_per_step": 2 * (hq.numel() + hk.numel() + hv.numel()),
-                        "d2h_bytes_per_step": 2 * ho.numel(), "ms_per_step": round(e2e_s * 1e3, 3)},
+                        "d2h_bytes_per_step": 2 * ho.numel(), "ms_per_step": round(e2e_s * 1e3, 3),
+                        "bytes_are": "per rank", "returns": f"each rank its {r1 - r0} of {w['Sq']} output rows x all heads "
+                                                             "(every GPU also keeps the full output)"},
+                "parity": {"max_abs": p_max, "mean_abs": p_mean, "rows": p_rows, "heads": p_heads, "ok": parity_ok,
+                           "against": "CPU oracle (oracle/sdpa_oracle.c) on per-head seeded inputs, every rank checks "
+                                      "its own copy of the gathered output; max over ranks", "tolerance": [2e-3, 2e-4]},
                 "gpu_launches": launches, "device_status": status,
                 "t1_same_workload_ms": round(t1, 3) if t1 else None,
                 "strong_scaling_efficiency_same_run": round(t1 / (world * ms_step), 4) if t1 else None,
@@ -613,6 +711,8 @@ def run_sharded(args, dtattn, device, peaks):
         print(json.dumps(line))
     comm.close()
     dist.destroy_process_group()
+    if not parity_ok:
+        raise SystemExit(f"gathered output differs from the oracle: max-abs {p_max:.3e} mean-abs {p_mean:.3e}")
 
 
 def main():
@@ -627,9 +727,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-fused", action="store_true", help="head-sharded mode through NCCL all-gather + permute instead of peer stores")
     ap.add_argument("--no-t1", action="store_true", help="skip the single-GPU run of the sharded workload")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the gathered output (N > 1)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
-    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj"],
+    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj", "masked"],
                     help="run one group of side measurements alone and print it (for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
@@ -648,7 +749,8 @@ def main():
     if args.only:
         fn = {"prologue": lambda: prologue_measurements(dtattn, device, peaks),
               "decode_step": lambda: decode_step_measurements(dtattn, device),
-              "out_proj": lambda: out_proj_measurements(dtattn, device, peaks)}[args.only]
+              "out_proj": lambda: out_proj_measurements(dtattn, device, peaks),
+              "masked": lambda: masked_measurements(dtattn, device, peaks)}[args.only]
         print(json.dumps({"only": args.only, "also": fn()}))
         return
     if world > 1:

@@ -79,6 +79,43 @@ def _worker(rank, world, port, q):
             assert mx <= 2e-3 + 2 * 2.0 ** -8 * float(want.abs().max()), ("projected max-abs", rank, mx)
             assert mean <= 2e-4 + 2.0 ** -8 * float(want.abs().mean()), ("projected mean-abs", rank, mean)
             keep.append(recv)
+        # the same registered buffer in consecutive calls with DIFFERENT inputs, one rank reading its result late:
+        # a rank that runs ahead must not store the next call's tiles into the slow rank's buffer before that rank's
+        # stream has read the previous result (the library puts a rendezvous in front of such a call)
+        B, S, H, D = 1, 1024, 8, 128
+        q0, q1, kv0, kv1 = sharding.head_range(rank, world, H, H)
+        o_same = torch.zeros((B, S, H, D), dtype=torch.bfloat16, device=dev)
+        comm.register_output(o_same)
+        steps, snaps, wants = 4, [], []
+        step_inputs = []
+        for st in range(steps):
+            cfg = so.AttnConfig("t", B, S, S, H, H, D, "bf16", 100 + st)
+            step_inputs.append((cfg, [t.to(dev) for t in so.make_inputs(cfg, heads=(q0, q1))]))
+        for st in range(steps):  # expected results through the all-gather path into separate buffers
+            cfg, (ql, kl, vl) = step_inputs[st]
+            want = torch.zeros_like(o_same)
+            comm.forward(ql, kl, vl, cfg.scale, want, chunks=1)
+            wants.append(want)
+        torch.cuda.synchronize()
+        dist.barrier()
+        for st in range(steps):
+            cfg, (ql, kl, vl) = step_inputs[st]
+            comm.forward(ql, kl, vl, cfg.scale, o_same, chunks=1)
+            if rank == 1:
+                torch.cuda._sleep(int(3e6))  # a slow consumer in front of the read, in stream order (about 2 ms)
+            snaps.append(o_same.clone())
+        torch.cuda.synchronize()
+        dist.barrier()
+        for st in range(steps):
+            assert torch.equal(snaps[st], wants[st]), f"step {st}: the late reader saw another step's tiles"
+        # buffers of different sizes on the two ranks are refused on every rank
+        odd = torch.zeros(4096 * (rank + 1), dtype=torch.uint8, device=dev)
+        try:
+            comm.register_output(odd)
+            mismatch = "accepted"
+        except dtattn.DtError as e:
+            mismatch = e.status
+        assert mismatch == dtattn.DT_BAD_ARG, mismatch
         comm.close()
         q.put((rank, errs, dtattn.device_status()))
     finally:
