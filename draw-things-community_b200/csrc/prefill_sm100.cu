@@ -34,10 +34,12 @@ constexpr int kThreads = 384;
 constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 x 16-bit] = 16 KB, one TMA box
 constexpr float kRescaleThreshold = 8.f;
 constexpr int kMaxExtraOutputs = 7;
-// every kPolyPeriod-th pair of exponentials is evaluated with the polynomial instead of MUFU.EX2 (5 of 16 pairs with
-// period 3; measured on B200: period 3 about 1 % faster than 4, periods 2 and none about 1-2 % slower)
+// every kPolyPeriod-th pair of exponentials is evaluated with the polynomial instead of MUFU.EX2 (1 of 16 pairs with
+// period 16).  The softmax warps are bound by the number of instructions they issue, not by the special-function unit
+// (measured on B200, Flux shape, TFLOP/s: period 1 (all polynomial) 996, 2: 1066, 3: 1123, 4: 1140, 6: 1157, 8: 1149,
+// 16: 1160, none: 1147; with the softmax and the MMA warps free-running, never waiting for each other, the same order)
 #ifndef DT_POLY_PERIOD
-#define DT_POLY_PERIOD 3
+#define DT_POLY_PERIOD 16
 #endif
 constexpr int kPolyPeriod = DT_POLY_PERIOD;
 // 128 * kRegsLow + 256 * kRegsHigh must not exceed what the CTA was launched with (384 threads * 168)
@@ -78,6 +80,7 @@ struct PrefillArgs {
   int64_t m_sb, m_sh, m_sq;
   float scale;  // the plain scale (scale_log2 = scale * log2(e)); the masked variant adds the mask in this domain
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
+  int n_slots;            // n_items rounded up to whole rounds over the grid (the causal order leaves some slots empty)
   // variable-length batch (both null otherwise): packed rows, sequence s owns query rows [off_q[s], off_q[s+1])
   // and key rows [off_k[s], off_k[s+1]); the item's batch index is then the sequence
   const int32_t* off_q;
@@ -140,7 +143,13 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint6
   }
 }
 
-// Timeline probe of bring-up builds (options bit 1): globaltimer stamps of CTA 0 into the debug buffer.
+// Experiment builds (-DDT_PREFILL_OPTIONS=bits, never the product): bit 3 = the softmax warps skip the exponentials;
+// bit 4 = nobody waits for S or P (free-running softmax and MMA: garbage results, the pure throughput of each
+// side); bit 5 = the softmax warps skip the row maximum; bit 6 (with bit 4) = the softmax warps do nothing per block.  Bring-up builds: a.options bit 1 = timeline probe of CTA 0.
+#ifndef DT_PREFILL_OPTIONS
+#define DT_PREFILL_OPTIONS 0
+#endif
+#define DT_OPT(bit) ((DT_PREFILL_OPTIONS & (bit)) != 0)
 #ifdef DT_BRINGUP
 __device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
   if ((a.options & 2) && a.dbg != nullptr && blockIdx.x == 0 && slot < 4096)
@@ -186,8 +195,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   };
   auto decode_item = [&](int item) {
     Item it;
-    const int qt = item % a.n_qpairs;
-    const int bh = item / a.n_qpairs;
+    int qt = item % a.n_qpairs;
+    int bh = item / a.n_qpairs;
+    if (a.is_causal) {
+      // Under the causal rule an item's work grows with its query position.  The items are dealt out heaviest
+      // first (all heads' last tile pair, then the one before, ...), forwards in even rounds over the CTAs and
+      // backwards in odd rounds, so that every CTA's items add up to about the same number of K/V blocks.
+      const int round = item / (int)gridDim.x;
+      int pos = item - round * (int)gridDim.x;
+      if (round & 1) pos = (int)gridDim.x - 1 - pos;
+      const int order = round * (int)gridDim.x + pos;
+      const int nbh = a.n_items / a.n_qpairs;
+      const int level = order / nbh;
+      bh = order - level * nbh;
+      qt = a.n_qpairs - 1 - level;
+      if (order >= a.n_items) {  // a slot of the last, incomplete round without an item
+        it = Item{};
+        it.nkv = 0;
+        return it;
+      }
+    }
     it.h = bh % a.Hq;
     it.b = bh / a.Hq;
     it.kvh = it.h / G;
@@ -281,7 +308,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ++ring_it;
           return true;
         };
-        for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
+        for (int item = blockIdx.x; item < a.n_slots && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
           if (w.nkv == 0) {  // empty item: not counted (the loop header increments n_item)
             --n_item;
@@ -290,7 +317,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // The Q tiles of the NEXT item are pulled into L2 now: their rows are 256-byte pieces a whole
           // token stride apart (slow to gather from HBM), and the real load sits on the critical path
           // between two items.
-          if (item + (int)gridDim.x < a.n_items) {
+          if (item + (int)gridDim.x < a.n_slots) {
             const Item nx = decode_item(item + gridDim.x);
             for (int t = 0; t < (nx.two ? 2 : 1); ++t)
 #pragma unroll
@@ -340,7 +367,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         auto advance = [&]() {
           if (++slot == C::kSlots) { slot = 0; par ^= 1; }
         };
-        for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x, ++n_item) {
+        for (int item = blockIdx.x; item < a.n_slots && ok; item += gridDim.x, ++n_item) {
           const Item w = decode_item(item);
           if (w.nkv == 0) {  // empty item: not counted (the loop header increments n_item)
             --n_item;
@@ -393,11 +420,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint64_t kd = ring_k + (uint64_t)(slot_k * (C::kTileBytes >> 4));
             const bool last_qk = more && (j + 2 == w.nkv);  // the QK issued in this iteration is the item's last
             // ---- tile 0 ----  (P arrives in two halves of 64 keys so P*V starts while the softmax still runs)
-            if (!ptx::mbar_wait(&bars->p_half[0][0], pph0, abort_flag)) { fail(4u); break; }
+            if (!DT_OPT(16) && !ptx::mbar_wait(&bars->p_half[0][0], pph0, abort_flag)) { fail(4u); break; }
             if (j == 0) stamp(a, 16 * n_item + 2);
             ptx::tc_fence_after();
             issue_pv(o0, s0, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
-            if (!ptx::mbar_wait(&bars->p_half[0][1], pph0, abort_flag)) { fail(4u); break; }
+            if (!DT_OPT(16) && !ptx::mbar_wait(&bars->p_half[0][1], pph0, abort_flag)) { fail(4u); break; }
             pph0 ^= 1;
             ptx::tc_fence_after();
             issue_pv(o0, s0, vd, idesc_pv, 1u, k_mid, ksteps);
@@ -411,10 +438,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             // ---- tile 1 ----
             if (ntile == 2) {
-              if (!ptx::mbar_wait(&bars->p_half[1][0], pph1, abort_flag)) { fail(4u); break; }
+              if (!DT_OPT(16) && !ptx::mbar_wait(&bars->p_half[1][0], pph1, abort_flag)) { fail(4u); break; }
               ptx::tc_fence_after();
               issue_pv(o1, s1, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
-              if (!ptx::mbar_wait(&bars->p_half[1][1], pph1, abort_flag)) { fail(4u); break; }
+              if (!DT_OPT(16) && !ptx::mbar_wait(&bars->p_half[1][1], pph1, abort_flag)) { fail(4u); break; }
               pph1 ^= 1;
               ptx::tc_fence_after();
               issue_pv(o1, s1, vd, idesc_pv, 1u, k_mid, ksteps);
@@ -446,7 +473,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     int n_item = 0;
     const bool probe = (warp == 4 && lane == 0);
 
-    for (int item = blockIdx.x; item < a.n_items && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < a.n_slots && ok; item += gridDim.x) {
       const Item w = decode_item(item);
       if (w.nkv == 0) continue;
       if (t == 1 && !w.two) continue;  // this item has no second tile: neither side touches tile 1's barriers
@@ -455,7 +482,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const long long lo = a.window > 0 ? (long long)row + w.off - a.window + 1 : 0;  // first visible key
       float m_used = -INFINITY, l = 0.f;
 
-      for (int j = 0; j < w.nkv; ++j) {
+      for (int j = 0; j < (DT_OPT(64) ? 0 : w.nkv); ++j) {  // (experiment bit 6: no softmax work at all)
         // Masked variant: this row's 128 mask values of the block (256 contiguous bytes) are requested before the
         // wait for S, so that they arrive while the tensor pipe still works on it.  Vectors that straddle Sk are
         // fetched element by element (nothing beyond the row's Sk entries is ever read); rows beyond Sq load nothing.
@@ -480,7 +507,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             else mk[v] = v == tv ? tail : make_uint4(0u, 0u, 0u, 0u);
           }
         }
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
+        if (!DT_OPT(16) && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
           atomicCAS(a.status, 0u, 3u);
           *abort_flag = 1;
           ok = false;
@@ -583,6 +610,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mxc[c] = fmaxf(mxc[c], __uint_as_float(s[c][31]));
         }
         float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
+        if (DT_OPT(32)) mx = __uint_as_float(s[0][0]);  // bring-up: no row maximum
         mx *= sl2;  // scale > 0 is a precondition of this kernel
         const float m_cand = fmaxf(m_used, mx);
         // Lazy rescale: keep the old reference max unless the new one is larger by more than the threshold.
@@ -621,7 +649,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint64_t x2 = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
                                                scale2, neg_m2);
             float p0, p1;
-            if ((i % kPolyPeriod) == kPolyPeriod - 1) {  // a share of the exponentials runs on the FMA pipes
+            if (DT_OPT(8)) {  // bring-up: no exponentials
+              ptx::unpack_f32x2(x2, p0, p1);
+            } else if ((i % kPolyPeriod) == kPolyPeriod - 1) {  // a share of the exponentials runs on the FMA pipes
               ptx::exp2_poly_x2(x2, p0, p1);
             } else {
               float x0, x1;
@@ -653,7 +683,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (probe) stamp(a, 16 * n_item + 9);
 
       // ---- epilogue: O / l -> global (the MMA warp already works on the next item's first S meanwhile) ----
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->o_full[t], oph, abort_flag))) {
+      if (!DT_OPT(16) && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars->o_full[t], oph, abort_flag))) {
         atomicCAS(a.status, 0u, 5u);
         *abort_flag = 1;
         ok = false;
@@ -798,6 +828,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   const int n_sm = device_sm_count();
   dim3 grid(a.n_items < n_sm ? a.n_items : n_sm);  // one persistent CTA per SM
+  a.n_slots = (a.n_items + (int)grid.x - 1) / (int)grid.x * (int)grid.x;
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, mo, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;
