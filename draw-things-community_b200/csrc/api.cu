@@ -216,7 +216,8 @@ int dt_sdpa_workspace_size(const dt_sdpa_params* p, size_t* bytes) {
   int st = validate_params(p);
   if (st != DT_OK) return st;
   if (!bytes) return DT_BAD_ARG;
-  *bytes = choose(*p) == kDecode ? decode_workspace_bytes(*p) : 0;
+  const Kernel k = choose(*p);
+  *bytes = k == kDecode ? decode_workspace_bytes(*p) : k == kPrefill ? prefill_workspace_bytes(*p) : 0;
   return DT_OK;
 }
 
@@ -232,7 +233,7 @@ int dt_sdpa_forward(const dt_sdpa_params* p, void* workspace, size_t workspace_b
   cudaStream_t stream = (cudaStream_t)cuda_stream;
   switch (choose(*p)) {
     case kDecode: return launch_decode(*p, workspace, workspace_bytes, stream);
-    case kPrefill: return launch_prefill(*p, stream);
+    case kPrefill: return launch_prefill(*p, stream, nullptr, 0, workspace, workspace_bytes);
     case kShortKV: return launch_short_kv(*p, stream);
     default: return launch_generic(*p, stream);
   }

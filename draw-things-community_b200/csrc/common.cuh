@@ -47,7 +47,10 @@ int launch_decode(const dt_sdpa_params& p, void* workspace, size_t bytes, cudaSt
 bool prefill_supported(const dt_sdpa_params& p);
 // extra_outputs: up to 7 more [B,Sq,Hq,D] views with the same strides as p.o (other GPUs' buffers in the
 // head-sharded mode) that receive a copy of every O tile.
-int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs = nullptr, int n_extra = 0);
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs = nullptr, int n_extra = 0,
+                   void* workspace = nullptr, size_t workspace_bytes = 0);
+// Scratch of the masked variant: one byte per (32 query rows x 64 keys) patch of the mask, "has a non-zero entry".
+size_t prefill_workspace_bytes(const dt_sdpa_params& p);
 
 // Cross-attention over a short key/value sequence (Sk <= 96, head dim <= 64, the plain operator): three independent
 // warpgroup pipelines per CTA, TMA + tcgen05.

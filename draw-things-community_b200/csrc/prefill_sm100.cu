@@ -45,17 +45,19 @@ constexpr int kPolyPeriod = DT_POLY_PERIOD;
 // 128 * kRegsLow + 256 * kRegsHigh must not exceed what the CTA was launched with (384 threads * 168)
 constexpr int kRegsLow = 80, kRegsHigh = 208;
 
-template <int D>
+template <int D, bool kMask = false>
 struct Cfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = kHalves * kHalfBytes;  // one Q tile / one K block / one V block
-  static constexpr int kSlots = D == 128 ? 4 : 8;
+  // the masked variant gives 32 KB of the K/V ring to the second mask staging buffers
+  static constexpr int kSlots = (D == 128 ? 4 : 8) - (kMask ? 32 * 1024 / kTileBytes : 0);
+  static constexpr int kMaskBytes = kMask ? 8 * 32 * 128 : 0;  // per softmax warp: 32 rows x 64 keys x 16-bit (one half block)
   static constexpr int kStageBytes = 8 * 32 * 128;  // per softmax warp: 32 rows x 64 x 16-bit of O for the TMA store
   static constexpr int kQBufs = D == 128 ? 1 : 2;       // Q buffers: with D = 64 there is room to load the next item's Q early
   static constexpr int kQBytes = kQBufs * 2 * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + kMaskBytes + kBarBytes + 1024;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
 };
@@ -78,6 +80,10 @@ struct PrefillArgs {
   // 0 on a broadcast axis; rows are 16-byte aligned (base and strides multiples of 8 elements)
   const void* mask;
   int64_t m_sb, m_sh, m_sq;
+  // one byte per (32 query rows x 64 keys) patch of the mask: non-zero when the patch holds a non-zero entry;
+  // [mask batches][mask heads][n_rg row groups][n_kh key halves, padded to an even count]
+  const unsigned char* mask_flags;
+  int n_rg, n_kh;
   float scale;  // the plain scale (scale_log2 = scale * log2(e)); the masked variant adds the mask in this domain
   int n_qpairs, n_items;  // work items = (batch, head, pair of query tiles)
   int n_slots;            // n_items rounded up to whole rounds over the grid (the causal order leaves some slots empty)
@@ -159,6 +165,37 @@ __device__ __forceinline__ void stamp(const PrefillArgs& a, int slot) {
 __device__ __forceinline__ void stamp(const PrefillArgs&, int) {}
 #endif
 
+// Pre-pass of the masked variant: which (32 rows x 64 keys) patches of the additive mask hold anything but zeros.
+// A padding mask is zero almost everywhere, and the attention kernel skips the patches flagged zero altogether.
+// One warp per patch, 8 lanes on a row's 128 contiguous bytes; entries beyond Sq / Sk are never read.
+__global__ void __launch_bounds__(256) mask_flags_kernel(const unsigned short* __restrict__ mask, int64_t m_sb, int64_t m_sh,
+                                                         int64_t m_sq, int Hm, int Sq, int Sk, int n_rg, int n_kh,
+                                                         int is_causal, unsigned char* __restrict__ flags) {
+  const int lane = threadIdx.x & 31;
+  const int kh = blockIdx.x * 8 + (threadIdx.x >> 5), rg = blockIdx.y, bh = blockIdx.z;
+  if (kh >= n_kh) return;
+  const int mb = bh / Hm, mh = bh - mb * Hm;
+  const unsigned short* base = mask + mb * m_sb + mh * m_sh;
+  const int key = kh * 64 + (lane & 7) * 8;
+  uint32_t any = 0u;
+  // under the causal rule the attention kernel never visits a patch that lies wholly beyond its rows' last visible key
+  const bool visited = !is_causal || (long long)kh * 64 <= (long long)rg * 32 + 31 + (Sk - Sq);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = rg * 32 + i * 4 + (lane >> 3);
+    if (!visited || row >= Sq || key >= Sk) continue;
+    const unsigned short* src = base + (int64_t)row * m_sq + key;
+    if (key + 8 <= Sk) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+      any |= v.x | v.y | v.z | v.w;
+    } else {
+      for (int e = 0; key + e < Sk; ++e) any |= src[e];
+    }
+  }
+  const bool nz = __any_sync(0xffffffffu, any != 0u);
+  if (lane == 0) flags[((int64_t)bh * n_rg + rg) * n_kh + kh] = nz ? 1 : 0;
+}
+
 // 16-bit pair -> two floats (the mask is stored in the tensors' type)
 template <typename T>
 __device__ __forceinline__ float2 unpack_pair(uint32_t x) {
@@ -171,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                        const PrefillArgs a) {
-  using C = Cfg<D>;
+  using C = Cfg<D, kMask>;
   constexpr int kBf16 = std::is_same<T, __half>::value ? 0 : 1;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -180,7 +217,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t q_smem = base;
   const uint32_t ring_smem = base + C::kQBytes;
   const uint32_t stage_smem = base + C::kQBytes + C::kRingBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kStageBytes);
+  // masked variant: [second mask staging buffers] between the O staging rows and the barriers
+  const uint32_t mask_smem = stage_smem + C::kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(base_ptr + C::kQBytes + C::kRingBytes + C::kStageBytes + C::kMaskBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.Hq / a.Hkv;
@@ -481,30 +520,59 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const long long vis = a.is_causal ? (long long)row + w.off : (long long)w.sk;  // last visible key
       const long long lo = a.window > 0 ? (long long)row + w.off - a.window + 1 : 0;  // first visible key
       float m_used = -INFINITY, l = 0.f;
+      // masked variant: this warp's row of patch flags (null when its 32 rows lie beyond Sq: nothing to add there)
+      const unsigned char* patch_flags = nullptr;
+      if constexpr (kMask) {
+        const int rg = (w.q0 + t * kBM + ((warp & 3) << 5)) >> 5;
+        if (rg < a.n_rg) {
+          const int64_t mb = a.m_sb ? w.b : 0, mh = a.m_sh ? w.h : 0;
+          const int64_t hm = a.m_sh ? a.Hq : 1;
+          patch_flags = a.mask_flags + ((mb * hm + mh) * a.n_rg + rg) * a.n_kh;
+        }
+      }
+      // flags of block jj: bit 0 = its first 64 keys carry mask values, bit 1 = its second 64 keys
+      auto block_flags = [&](int jj) -> uint32_t {
+        if (!kMask || patch_flags == nullptr || jj >= w.nkv) return 0u;
+        const uint32_t f = __ldg(reinterpret_cast<const unsigned short*>(patch_flags + 2 * (w.j0 + jj)));
+        return ((f & 0xffu) ? 1u : 0u) | ((f >> 8) ? 2u : 0u);
+      };
+      uint32_t flags_cur = block_flags(0);
 
       for (int j = 0; j < (DT_OPT(64) ? 0 : w.nkv); ++j) {  // (experiment bit 6: no softmax work at all)
-        // Masked variant: this row's 128 mask values of the block (256 contiguous bytes) are requested before the
-        // wait for S, so that they arrive while the tensor pipe still works on it.  Vectors that straddle Sk are
-        // fetched element by element (nothing beyond the row's Sk entries is ever read); rows beyond Sq load nothing.
-        uint4 mk[kMask ? 16 : 1];
-        if constexpr (kMask) {
-          const int key0m = (w.j0 + j) * kBN;
-          const T* mrow = reinterpret_cast<const T*>(a.mask) + (int64_t)w.b * a.m_sb + (int64_t)w.h * a.m_sh +
-                          (int64_t)row * a.m_sq + key0m;
-          const int left = row < w.sq ? w.sk - key0m : 0;  // mask entries of this row from key0m on
-          uint4 tail = make_uint4(0u, 0u, 0u, 0u);
-          const int tv = left > 0 && left < kBN && (left & 7) ? (left >> 3) : -1;  // the vector that straddles Sk
-          if (tv >= 0) {
-            uint32_t e[8];
+        const uint32_t flags_next = block_flags(j + 1);  // asked for early, used when the next block's mask is requested
+        // Masked variant: the warp's 32 rows x 128 mask values of a block travel global -> shared memory with
+        // asynchronous 16-byte copies, 8 lanes on one row's 128 contiguous bytes (whole cache lines; a lane fetching its
+        // own row's 256 bytes would touch 32 lines per instruction and that made the L1 the bottleneck), in two halves
+        // of 64 keys with a staging buffer each: the first one in this warp's O staging rows (idle until the epilogue), the
+        // second one in the area taken from the K/V ring.  A block's halves are requested one block ahead; rows beyond Sq
+        // and keys beyond Sk are zero-filled, never read.
+        auto mask_prefetch = [&](int jj, int half, uint32_t flags) {
+          if constexpr (kMask) {
+            if (jj < w.nkv && ((flags >> half) & 1u)) {  // patches without mask values are not even fetched
+              const int keyh = (w.j0 + jj) * kBN + half * 64;
+              const uint32_t buf = (half ? mask_smem : stage_smem) + (uint32_t)(warp - 4) * (32 * 128);
+              const T* mbase = reinterpret_cast<const T*>(a.mask) + (int64_t)w.b * a.m_sb + (int64_t)w.h * a.m_sh + keyh;
+              const int ch = lane & 7;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              e[i] = tv * 8 + i < left ? (uint32_t) * reinterpret_cast<const unsigned short*>(mrow + tv * 8 + i) : 0u;
-            tail = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+              for (int i = 0; i < 8; ++i) {
+                const int r = i * 4 + (lane >> 3);  // row within the warp's 32
+                const int grow = w.q0 + t * kBM + ((warp & 3) << 5) + r;
+                const int left = grow < w.sq ? w.sk - (keyh + ch * 8) : 0;  // mask entries from this chunk's first key on
+                const int nbytes = left >= 8 ? 16 : (left > 0 ? left * 2 : 0);
+                ptx::cp_async_16(buf + (uint32_t)r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4),
+                                 nbytes ? (const void*)(mbase + (int64_t)grow * a.m_sq + ch * 8) : (const void*)a.mask, nbytes);
+              }
+            }
+            ptx::cp_async_commit();  // always a group, possibly empty, so that the wait counts stay regular
           }
-#pragma unroll
-          for (int v = 0; v < 16; ++v) {
-            if (v * 8 + 8 <= left) mk[v] = __ldg(reinterpret_cast<const uint4*>(mrow) + v);
-            else mk[v] = v == tv ? tail : make_uint4(0u, 0u, 0u, 0u);
+        };
+        if constexpr (kMask) {
+          if (j == 0) {
+            // the O staging rows double as the first mask buffer: the previous item's TMA store must have read them
+            if (lane == 0) ptx::bulk_wait_read_all();
+            __syncwarp();
+            mask_prefetch(0, 0, flags_cur);
+            mask_prefetch(0, 1, flags_cur);
           }
         }
         if (!DT_OPT(16) && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
@@ -518,32 +586,53 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ptx::tc_fence_after();
         uint32_t s[4][32];
         if constexpr (kMask) {
-          // scores in two halves, each turned into scale * s + mask as soon as it is in registers: the mask
-          // registers of the first half are free before the second half of S arrives
-          auto add_mask = [&](int c) {
+          // scores in two halves of 64 keys; each half gets mask / scale added once its mask values have landed (the
+          // scores stay in the unscaled domain of the unmasked kernel).  A half whose mask values are all zero for the
+          // whole warp -- most of a padding mask -- is left as it is.
+          const uint64_t inv2 = ptx::pack_f32x2(1.f / a.scale, 1.f / a.scale);
+          auto add_mask_half = [&](int half) {
+            if (!((flags_cur >> half) & 1u)) return;  // the same answer for the whole warp
+            const uint32_t buf = (half ? mask_smem : stage_smem) + (uint32_t)(warp - 4) * (32 * 128) + (uint32_t)lane * 128;
+            uint4 mk[8];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const uint4 m4 = mk[c * 4 + v];
-              const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
+            for (int q = 0; q < 8; ++q) mk[q] = ptx::ld_shared_v4(buf + ((((uint32_t)q) ^ ((uint32_t)lane & 7u)) << 4));
+            uint32_t any = 0u;
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float2 mf = unpack_pair<T>(mw[u]);
-                const int i = v * 8 + u * 2;
-                s[c][i] = __float_as_uint(fmaf(__uint_as_float(s[c][i]), a.scale, mf.x));
-                s[c][i + 1] = __float_as_uint(fmaf(__uint_as_float(s[c][i + 1]), a.scale, mf.y));
+            for (int q = 0; q < 8; ++q) any |= mk[q].x | mk[q].y | mk[q].z | mk[q].w;
+            if (__any_sync(0xffffffffu, any != 0u)) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint32_t mw[4] = {mk[q].x, mk[q].y, mk[q].z, mk[q].w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const float2 mf = unpack_pair<T>(mw[u]);
+                  const int c = half * 2 + (q >> 2), i = (q & 3) * 8 + u * 2;
+                  const uint64_t r2 = ptx::fma_f32x2(ptx::pack_f32x2(mf.x, mf.y), inv2,
+                                                     ptx::pack_f32x2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])));
+                  float r0, r1;
+                  ptx::unpack_f32x2(r2, r0, r1);
+                  s[c][i] = __float_as_uint(r0);
+                  s[c][i + 1] = __float_as_uint(r1);
+                }
               }
             }
+            __syncwarp();  // every lane has read its row: the buffer may be refilled
           };
           ptx::tmem_ld32(t_s + 0, s[0]);
           ptx::tmem_ld32(t_s + 32, s[1]);
+          ptx::cp_async_wait<1>();  // this block's first half has landed (its second half may still be on its way)
+          __syncwarp();
           ptx::tc_wait_ld();
-          add_mask(0);
-          add_mask(1);
+          add_mask_half(0);
+          mask_prefetch(j + 1, 0, flags_next);
           ptx::tmem_ld32(t_s + 64, s[2]);
           ptx::tmem_ld32(t_s + 96, s[3]);
+          ptx::cp_async_wait<1>();  // this block's second half (the group behind it is the next block's first half)
+          __syncwarp();
           ptx::tc_wait_ld();
-          add_mask(2);
-          add_mask(3);
+          add_mask_half(1);
+          mask_prefetch(j + 1, 1, flags_next);
+          flags_cur = flags_next;
         } else {
           ptx::tmem_ld32(t_s + 0, s[0]);
           ptx::tmem_ld32(t_s + 32, s[1]);
@@ -551,9 +640,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ptx::tmem_ld32(t_s + 96, s[3]);
           ptx::tc_wait_ld();
         }
-        // from here on the scores are multiplied by `sl2`: scale * log2(e), or log2(e) alone once the masked
-        // variant has applied the scale together with the mask
-        const float sl2 = kMask ? kLog2e : a.scale_log2;
+        const float sl2 = a.scale_log2;
         if (probe && j == 0) stamp(a, 16 * n_item + 4);
 
 #ifdef DT_BRINGUP
@@ -790,8 +877,9 @@ float* g_dbg = nullptr;
 #endif
 
 template <typename T, int D, bool kMask>
-int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, int n_extra) {
-  using C = Cfg<D>;
+int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, int n_extra, void* workspace,
+             size_t workspace_bytes) {
+  using C = Cfg<D, kMask>;
   CUtensorMap mq, mk, mv, mo;
   if (!make_bshd_tensor_map(&mq, p.q, p.B, p.Sq, p.Hq, p.D, p.dtype, kBM)) return DT_UNSUPPORTED;
   if (!make_bshd_tensor_map(&mk, p.k, p.B, p.Sk, p.Hkv, p.D, p.dtype, kBN)) return DT_UNSUPPORTED;
@@ -812,6 +900,19 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   a.scale = p.scale;
   a.mask = p.mask;
   a.m_sb = p.mask_stride_b; a.m_sh = p.mask_stride_h; a.m_sq = p.mask_stride_q;
+  if (kMask) {
+    if (!workspace || workspace_bytes < prefill_workspace_bytes(p)) return DT_WORKSPACE;
+    const int Bm = p.mask_stride_b ? p.B : 1, Hm = p.mask_stride_h ? p.Hq : 1;
+    a.n_rg = (p.Sq + 31) / 32;
+    a.n_kh = ((p.Sk + 63) / 64 + 1) & ~1;
+    a.mask_flags = static_cast<const unsigned char*>(workspace);
+    dim3 fgrid((a.n_kh + 7) / 8, a.n_rg, Bm * Hm);
+    if (fgrid.y > 65535 || fgrid.z > 65535) return DT_UNSUPPORTED;
+    mask_flags_kernel<<<fgrid, 256, 0, stream>>>(static_cast<const unsigned short*>(p.mask), p.mask_stride_b, p.mask_stride_h,
+                                                p.mask_stride_q, Hm, p.Sq, p.Sk, a.n_rg, a.n_kh, p.is_causal,
+                                                static_cast<unsigned char*>(workspace));
+    DT_CUDA_TRY(cudaGetLastError());
+  }
   a.is_causal = p.is_causal;
   a.window = p.sliding_window;
   a.sinks = p.sinks;
@@ -857,18 +958,24 @@ bool prefill_supported(const dt_sdpa_params& p) {
   return ok(p.q) && ok(p.k) && ok(p.v) && ok(p.o);
 }
 
-int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra) {
+size_t prefill_workspace_bytes(const dt_sdpa_params& p) {
+  if (!p.mask) return 0;
+  const size_t Bm = p.mask_stride_b ? p.B : 1, Hm = p.mask_stride_h ? p.Hq : 1;
+  const size_t n_rg = (p.Sq + 31) / 32, n_kh = ((p.Sk + 63) / 64 + 1) & ~(size_t)1;
+  return (Bm * Hm * n_rg * n_kh + 255) / 256 * 256;
+}
+
+int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra, void* workspace,
+                   size_t workspace_bytes) {
   const bool wide = p.D > 64;
+#define DT_PREFILL_GO(T, DD, M) launch_t<T, DD, M>(p, stream, extra_outputs, n_extra, workspace, workspace_bytes)
   if (p.mask) {
-    if (p.dtype == DT_F16)
-      return wide ? launch_t<__half, 128, true>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64, true>(p, stream, extra_outputs, n_extra);
-    return wide ? launch_t<__nv_bfloat16, 128, true>(p, stream, extra_outputs, n_extra)
-                : launch_t<__nv_bfloat16, 64, true>(p, stream, extra_outputs, n_extra);
+    if (p.dtype == DT_F16) return wide ? DT_PREFILL_GO(__half, 128, true) : DT_PREFILL_GO(__half, 64, true);
+    return wide ? DT_PREFILL_GO(__nv_bfloat16, 128, true) : DT_PREFILL_GO(__nv_bfloat16, 64, true);
   }
-  if (p.dtype == DT_F16)
-    return wide ? launch_t<__half, 128, false>(p, stream, extra_outputs, n_extra) : launch_t<__half, 64, false>(p, stream, extra_outputs, n_extra);
-  return wide ? launch_t<__nv_bfloat16, 128, false>(p, stream, extra_outputs, n_extra)
-              : launch_t<__nv_bfloat16, 64, false>(p, stream, extra_outputs, n_extra);
+  if (p.dtype == DT_F16) return wide ? DT_PREFILL_GO(__half, 128, false) : DT_PREFILL_GO(__half, 64, false);
+  return wide ? DT_PREFILL_GO(__nv_bfloat16, 128, false) : DT_PREFILL_GO(__nv_bfloat16, 64, false);
+#undef DT_PREFILL_GO
 }
 
 }  // namespace dt
