@@ -68,8 +68,23 @@ def build(force=False, verbose=False, defines=(), out=None):
     return lib
 
 
+# The wait-runs-out test (tests/test_gpu_wait_limit.py) needs a library whose device-side waits give up after a few
+# milliseconds and whose decode kernel can be told by the host to skip its loads: a bring-up build kept beside the product.
+WAIT_TEST_LIB = os.path.join(LIB_DIR, "libdtattn_waittest.so")
+WAIT_TEST_DEFINES = ("DT_BRINGUP", "DT_WAIT_LIMIT_NS=5000000ull")
+
+
+def build_all(force=False):
+    path = build(force=force)
+    build(force=force, defines=WAIT_TEST_DEFINES, out=WAIT_TEST_LIB)
+    return path
+
+
 if __name__ == "__main__":
     argv = sys.argv[1:]
+    if "--all" in argv:
+        print(build_all(force="--force" in argv))
+        sys.exit(0)
     defs = [argv[i + 1] for i, a in enumerate(argv[:-1]) if a == "--define"]
     outs = [argv[i + 1] for i, a in enumerate(argv[:-1]) if a == "--out"]
     print(build(force="--force" in argv, verbose="--verbose" in argv, defines=defs, out=outs[0] if outs else None))

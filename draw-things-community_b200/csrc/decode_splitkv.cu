@@ -80,6 +80,8 @@ struct DecodeArgs {
   unsigned int* status;
 #ifdef DT_BRINGUP
   unsigned long long* dbg;  // optional per-CTA timeline (bring-up probe)
+  int skip_loads;           // failure injection on the host's request: the producer lane issues no loads, so the
+                            // consumers' bounded wait runs out and the kernel reports it and returns
 #endif
   // decode-step fusion (all null / 0 for a plain attention call): new K/V rows to rotate, append and attend
   const void* k_new; const void* v_new; const void* rotary; void* k_cache; void* v_cache;
@@ -400,7 +402,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
+#ifdef DT_BRINGUP
+    if (lane == 0 && !a.skip_loads) {
+#else
     if (lane == 0) {
+#endif
       for (int st = 0; st < n_stages; ++st) {
         const int slot = st % nst;
         if (st >= nst) {
@@ -783,6 +789,7 @@ int sm_count() {
 
 #ifdef DT_BRINGUP
 unsigned long long* g_decode_dbg = nullptr;
+int g_decode_skip_loads = 0;
 #endif
 
 struct Plan {
@@ -950,6 +957,7 @@ int launch_t(const dt_sdpa_params& p, const dt_decode_step_params* step, const S
   if (!a.status) return DT_CUDA;
 #ifdef DT_BRINGUP
   a.dbg = g_decode_dbg;
+  a.skip_loads = g_decode_skip_loads;
 #endif
   a.Sq = p.Sq; a.Sk = p.Sk; a.Hq = p.Hq; a.Hkv = p.Hkv; a.G = G; a.M = M;
   a.stream_keys = stream_keys;
@@ -1148,6 +1156,11 @@ extern "C" int dt_sdpa_decode_noalloc_status(void* cuda_stream, int* code) {
 }
 
 #ifdef DT_BRINGUP
+// Bring-up builds only: host-made failure for the wait-runs-out test (see DecodeArgs::skip_loads).
+extern "C" int dt_internal_set_decode_skip_loads(int on) {
+  dt::g_decode_skip_loads = on;
+  return 0;
+}
 // Bring-up builds only: per-CTA timeline buffer for the decode kernel.
 extern "C" int dt_internal_set_decode_dump(unsigned long long* device_buffer) {
   dt::g_decode_dbg = device_buffer;

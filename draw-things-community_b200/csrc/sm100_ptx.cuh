@@ -55,8 +55,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wall-clock limit of every device-side wait.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// Wall-clock limit of every device-side wait (2 s; the wait-runs-out test builds with a few milliseconds).
+#ifndef DT_WAIT_LIMIT_NS
+#define DT_WAIT_LIMIT_NS 2000000000ull
+#endif
+constexpr uint64_t kWaitLimitNs = DT_WAIT_LIMIT_NS;
 
 // Waits for the phase with the given parity to complete.  Returns false when the limit ran out or when
 // *abort_flag (shared memory, may be null) became non-zero; the caller must then unwind.
