@@ -27,9 +27,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "draw-things-community_b200"))
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-# (profiles/prefill_tcgen05_flux_joint.md, profiles/decode_splitkv_gqa_8192.md); None = not captured
-NCU_TRAFFIC_BYTES = {"flux_joint": 91.7e6, "decode_b16": 541.3e6, "decode_b1": 33.6e6, "wan_self": None, "sdxl_cross": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of this command (--set full, one kernel, two
+# launches); None = not captured.  For the SDXL shape the capture sees the O writes only (Q stays in L2 across replays).
+NCU_TRAFFIC_BYTES = {"flux_joint": 91.4e6, "decode_b16": 541.3e6, "decode_b1": 33.6e6, "wan_self": None, "sdxl_cross": 22.0e6}
 
 METRIC = "sdpa_fwd_tflops"
 UNIT = "TFLOP/s"
