@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libdtattn.so")
-SOURCES = ["api.cu", "generic.cu", "decode_splitkv.cu", "prefill_sm100.cu", "crossattn_short.cu", "comm.cu", "qk_prologue.cu", "out_proj.cu"]
+SOURCES = ["api.cu", "generic.cu", "decode_splitkv.cu", "prefill_sm100.cu", "crossattn_short.cu", "sparse_indexed.cu", "comm.cu", "qk_prologue.cu", "out_proj.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

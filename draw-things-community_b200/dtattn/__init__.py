@@ -73,6 +73,16 @@ class OutProj(ctypes.Structure):
     _fields_ = [("weight", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("C", ctypes.c_int32), ("out", Tensor4)]
 
 
+class SparseIndexedParams(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("Sq", ctypes.c_int32), ("Hq", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+                ("D", ctypes.c_int32), ("Sr", ctypes.c_int32), ("Sc", ctypes.c_int32), ("n_selected", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("scale", ctypes.c_float), ("is_causal", ctypes.c_int32),
+                ("sliding_window", ctypes.c_int32),
+                ("q", Tensor4), ("o", Tensor4), ("k_raw", Tensor4), ("v_raw", Tensor4), ("k_comp", Tensor4), ("v_comp", Tensor4),
+                ("selected", ctypes.c_void_p), ("selected_stride_b", ctypes.c_int64), ("selected_stride_q", ctypes.c_int64),
+                ("sinks", ctypes.c_void_p), ("lse", ctypes.c_void_p)]
+
+
 class DtError(RuntimeError):
     def __init__(self, status, what):
         self.status = status
@@ -102,6 +112,7 @@ SYMBOLS = [
     ("dt_sdpa_forward_projected", ctypes.c_int,
      [_P(SdpaParams), _P(OutProj), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     ("dt_qk_prologue", ctypes.c_int, [_P(QkPrologueParams), _P(QkPrologueParams), ctypes.c_void_p]),
+    ("dt_sparse_indexed_attention", ctypes.c_int, [_P(SparseIndexedParams), ctypes.c_void_p]),
     ("dt_comm_unique_id", ctypes.c_int, [ctypes.c_void_p]),
     ("dt_comm_init", ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]),
     ("dt_comm_destroy", ctypes.c_int, [ctypes.c_void_p]),
@@ -362,6 +373,62 @@ def sdpa_forward_projected(q, k, v, scale, weight, bias=None, is_causal=False, o
     _check(lib().dt_sdpa_forward_projected(ctypes.byref(p), ctypes.byref(pr), ctypes.c_void_p(ptr), nbytes,
                                            ctypes.c_void_p(s)), "dt_sdpa_forward_projected")
     return out
+
+
+def sparse_indexed_attention(q, k_raw, v_raw, k_comp, v_comp, selected, scale, sinks=None, sliding_window=0,
+                             is_causal=True, out=None, lse=None, stream=None):
+    """SparseIndexedAttention (DeepSeek4.swift:521-545): q [B,Sq,Hq,D] over its sliding causal window of the raw rows
+    k_raw / v_raw [B,Sr,Hkv,D] and over the rows of k_comp / v_comp [B,Sc,Hkv,D] (None when there are none) that
+    `selected` (int32 [B or 1, Sq, n_selected]; entries outside [0, Sc) mean "no row") names, in one softmax with the
+    sinks [Hq].  Device tensors."""
+    assert q.is_cuda
+    B, Sq, Hq, D = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    p = SparseIndexedParams()
+    p.B, p.Sq, p.Hq, p.Hkv, p.D = B, Sq, Hq, k_raw.shape[2], D
+    p.Sr = k_raw.shape[1]
+    p.Sc = 0 if k_comp is None else k_comp.shape[1]
+    p.dtype = _DTYPES[q.dtype]
+    p.scale = float(scale)
+    p.is_causal = int(bool(is_causal))
+    p.sliding_window = int(sliding_window)
+    p.q, p.o, p.k_raw, p.v_raw = _view4(q), _view4(out), _view4(k_raw), _view4(v_raw)
+    if k_comp is not None and p.Sc > 0:
+        p.k_comp, p.v_comp = _view4(k_comp), _view4(v_comp)
+    if selected is not None:
+        assert selected.dtype == torch.int32 and selected.dim() == 3 and selected.shape[1] == Sq and selected.stride(2) == 1
+        p.n_selected = selected.shape[2]
+        p.selected = selected.data_ptr()
+        p.selected_stride_b = selected.stride(0) if selected.shape[0] > 1 else 0
+        p.selected_stride_q = selected.stride(1)
+    if sinks is not None:
+        assert sinks.dtype == q.dtype and sinks.is_contiguous() and sinks.numel() == Hq
+        p.sinks = sinks.data_ptr()
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, Hq, Sq)
+        p.lse = lse.data_ptr()
+    s = stream if stream is not None else torch.cuda.current_stream(q.device).cuda_stream
+    _check(lib().dt_sparse_indexed_attention(ctypes.byref(p), ctypes.c_void_p(s)), "dt_sparse_indexed_attention")
+    return out
+
+
+class SparseIndexedAttention:
+    """NNC.SparseIndexedAttention(scale:isCausal:hasAttentionSinks:slidingWindow:) with the reference's input order
+    (DeepSeek4.swift:536-545): op(queries, rawKeys, rawValues, compressedKeys, compressedValues, selectedRows, sinks)."""
+
+    def __init__(self, scale, is_causal=True, has_attention_sinks=True, sliding_window=0, name=""):
+        self.scale, self.is_causal = float(scale), bool(is_causal)
+        self.has_attention_sinks, self.sliding_window, self.name = bool(has_attention_sinks), int(sliding_window), name
+
+    def __call__(self, queries, raw_keys, raw_values, compressed_keys, compressed_values, selected_rows, sinks=None, out=None):
+        if self.has_attention_sinks != (sinks is not None):
+            raise ValueError("hasAttentionSinks and the number of inputs disagree")
+        if selected_rows is not None and selected_rows.dim() == 2:  # the reference passes [queryLength, selectedRowCount]
+            selected_rows = selected_rows.unsqueeze(0)
+        return sparse_indexed_attention(queries, raw_keys, raw_values, compressed_keys, compressed_values, selected_rows,
+                                        self.scale, None if sinks is None else sinks.reshape(-1).contiguous(),
+                                        self.sliding_window, self.is_causal, out=out)
 
 
 _workspaces = {}

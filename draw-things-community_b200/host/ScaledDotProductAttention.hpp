@@ -163,6 +163,38 @@ class ScaledDotProductAttention {
   bool fused_projection_ = false;
 };
 
+// SparseIndexedAttention(scale:, isCausal:, hasAttentionSinks:, slidingWindow:) with the reference's input order
+// (SwiftLLM/Sources/Models/DeepSeek4.swift:521-545): op(queries, rawKeys, rawValues, compressedKeys, compressedValues,
+// selectedRows, sinks) -> out.  selectedRows: int32 [queryLength, selectedRowCount] (one list per query, shared by the
+// batch); entries outside [0, compressed rows) name no row.
+class SparseIndexedAttention {
+ public:
+  SparseIndexedAttention(float scale, bool isCausal = true, bool hasAttentionSinks = true, int slidingWindow = 0,
+                         std::string name = "")
+      : scale_(scale), causal_(isCausal), has_sinks_(hasAttentionSinks), window_(slidingWindow), name_(std::move(name)) {}
+  void operator()(const TensorView& q, const TensorView& rawK, const TensorView& rawV, const TensorView* compK,
+                  const TensorView* compV, const int32_t* selectedRows, int selectedRowCount, const void* sinks,
+                  const TensorView& out, void* stream) const {
+    if (has_sinks_ != (sinks != nullptr)) throw Error(DT_BAD_ARG, "hasAttentionSinks and the inputs disagree");
+    dt_sparse_indexed_params p{};
+    p.B = q.B; p.Sq = q.S; p.Hq = q.H; p.Hkv = rawK.H; p.D = q.D;
+    p.Sr = rawK.S; p.Sc = compK ? compK->S : 0; p.n_selected = selectedRowCount;
+    p.dtype = q.dtype; p.scale = scale_; p.is_causal = causal_ ? 1 : 0; p.sliding_window = window_;
+    p.q = q.abi(); p.o = out.abi(); p.k_raw = rawK.abi(); p.v_raw = rawV.abi();
+    if (compK && compV) { p.k_comp = compK->abi(); p.v_comp = compV->abi(); }
+    p.selected = selectedRows; p.selected_stride_b = 0; p.selected_stride_q = selectedRowCount;
+    p.sinks = sinks;
+    int st = dt_sparse_indexed_attention(&p, stream);
+    if (st != DT_OK) throw Error(st, "dt_sparse_indexed_attention(" + name_ + ")");
+  }
+
+ private:
+  float scale_;
+  bool causal_, has_sinks_;
+  int window_;
+  std::string name_;
+};
+
 // ---- the steps either side of the operator, as free functions over the same views --------------------------
 
 // One KV-cache step (Qwen3_5.swift:164-196): optional qNorm / kNorm, rotary cmul on the last q.S queries and the

@@ -280,3 +280,56 @@ public final class ScaledDotProductAttention {
     precondition(status == DT_OK.rawValue, "dt_qk_prologue: \(String(cString: dt_status_string(status)))")
   }
 }
+
+/// SparseIndexedAttention(scale:isCausal:hasAttentionSinks:slidingWindow:) with the reference's input order
+/// (DeepSeek4.swift:521-545): op(queries, rawKeys, rawValues, compressedKeys, compressedValues, selectedRows, sinks).
+/// selectedRows is an Int32 view [queryLength, selectedRowCount]; compressedKeys / compressedValues may be empty
+/// (the reference passes a [0] tensor when there are no compressed rows yet).
+public final class SparseIndexedAttention {
+  public let scale: Float
+  public let isCausal: Bool
+  public let hasAttentionSinks: Bool
+  public let slidingWindow: Int
+  public var stream: UnsafeMutableRawPointer?
+  public var allocator: ScaledDotProductAttention.Allocator
+
+  public init(
+    scale: Float, isCausal: Bool = true, hasAttentionSinks: Bool = true, slidingWindow: Int = 0,
+    stream: UnsafeMutableRawPointer? = nil, allocator: @escaping ScaledDotProductAttention.Allocator
+  ) {
+    self.scale = scale
+    self.isCausal = isCausal
+    self.hasAttentionSinks = hasAttentionSinks
+    self.slidingWindow = slidingWindow
+    self.stream = stream
+    self.allocator = allocator
+  }
+
+  @discardableResult
+  public func callAsFunction(
+    _ queries: DeviceView, _ rawKeys: DeviceView, _ rawValues: DeviceView, _ compressedKeys: DeviceView,
+    _ compressedValues: DeviceView, _ selectedRows: DeviceView, _ sinks: DeviceView? = nil
+  ) -> DeviceView {
+    precondition(hasAttentionSinks == (sinks != nil), "hasAttentionSinks and the inputs disagree")
+    var p = dt_sparse_indexed_params()
+    p.B = Int32(queries.shape[0]); p.Sq = Int32(queries.shape[1]); p.Hq = Int32(queries.shape[2]); p.D = Int32(queries.shape[3])
+    p.Hkv = Int32(rawKeys.shape[2]); p.Sr = Int32(rawKeys.shape[1])
+    let compressedRows = compressedKeys.shape.count == 4 ? compressedKeys.shape[1] : 0
+    p.Sc = Int32(compressedRows)
+    p.n_selected = Int32(selectedRows.shape[1])
+    p.dtype = Int32(queries.dtype.rawValue)
+    p.scale = scale
+    p.is_causal = isCausal ? 1 : 0
+    p.sliding_window = Int32(slidingWindow)
+    let out = DeviceView(pointer: allocator(queries.shape.reduce(1, *) * queries.elementSize), shape: queries.shape, dtype: queries.dtype)
+    p.q = queries.abi4; p.o = out.abi4; p.k_raw = rawKeys.abi4; p.v_raw = rawValues.abi4
+    if compressedRows > 0 { p.k_comp = compressedKeys.abi4; p.v_comp = compressedValues.abi4 }
+    p.selected = UnsafePointer<Int32>(OpaquePointer(selectedRows.pointer))
+    p.selected_stride_b = 0
+    p.selected_stride_q = Int64(selectedRows.strides[0])
+    p.sinks = sinks.map { UnsafeRawPointer($0.pointer) }
+    let status = dt_sparse_indexed_attention(&p, stream)
+    precondition(status == DT_OK.rawValue, "dt_sparse_indexed_attention: \(String(cString: dt_status_string(status)))")
+    return out
+  }
+}

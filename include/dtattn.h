@@ -220,6 +220,35 @@ typedef struct {
 } dt_qk_prologue_params;
 int dt_qk_prologue(const dt_qk_prologue_params* q, const dt_qk_prologue_params* k, void* cuda_stream);
 
+/* Sparse indexed attention --------------------------------------------------------------------------
+ * SparseIndexedAttention(scale:, isCausal: true, hasAttentionSinks: true, slidingWindow:)(queries, rawKeys, rawValues,
+ * compressedKeys, compressedValues, selectedRows, sinks) (Libraries/SwiftLLM/Sources/Models/DeepSeek4.swift:521-545,
+ * called at :1080 and :1127): every query attends, in ONE softmax, to its sliding causal window of the raw key/value
+ * rows and to the rows of a second, compressed key/value tensor that its list of selected rows names, plus the sink of
+ * its head.  q, o: [B, Sq, Hq, D]; k_raw, v_raw: [B, Sr, Hkv, D] (query i sees raw rows j with j <= i + (Sr - Sq) when
+ * is_causal, and j > i + (Sr - Sq) - sliding_window when sliding_window > 0); k_comp, v_comp: [B, Sc, Hkv, D] (may be
+ * NULL when Sc == 0); selected: int32 [B or 1, Sq, n_selected] (strides in elements; stride_b 0 = one list for the
+ * whole batch): an entry outside [0, Sc) means "no row", a row listed twice counts twice; sinks: [Hq] in the tensors'
+ * dtype or NULL; lse: optional fp32 [B, Hq, Sq].  The reference's model uses one shared KV head for 64 query heads of
+ * dim 512 with the same tensor as keys and values; here keys and values are separate views (pass the same pointer
+ * twice for that layout), D <= 512, fp16 / bf16 / fp32.  The arithmetic of the reference's operator is in its absent
+ * back end: "no row" for out-of-range entries and duplicates counting twice are this library's definition.
+ */
+typedef struct {
+  int32_t B, Sq, Hq, Hkv, D;
+  int32_t Sr, Sc, n_selected;
+  int32_t dtype;
+  float scale;
+  int32_t is_causal;
+  int32_t sliding_window;
+  dt_tensor4 q, o, k_raw, v_raw, k_comp, v_comp;
+  const int32_t* selected;
+  int64_t selected_stride_b, selected_stride_q;
+  const void* sinks;
+  float* lse;
+} dt_sparse_indexed_params;
+int dt_sparse_indexed_attention(const dt_sparse_indexed_params* p, void* cuda_stream);
+
 /* Decode without any allocation ---------------------------------------------------------------------
  * No counterpart in the reference.  Some hosts of this library cannot obtain device memory at the moment
  * they call: a runtime that handed the whole device to its own allocator at start-up (the reference's graph

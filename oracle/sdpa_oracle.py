@@ -111,6 +111,65 @@ def sdpa_varlen_explicit(q, k, v, scale, offsets_q, offsets_k, is_causal=False, 
     return out
 
 
+def sparse_indexed_explicit(q, k_raw, v_raw, k_comp, v_comp, selected, scale, sinks=None, sliding_window=0,
+                            is_causal=True, compute_dtype=torch.float32, return_lse=False):
+    """SparseIndexedAttention (DeepSeek4.swift:521-545: queries, raw keys / values, compressed keys / values, selected
+    rows [queryLength, selectedRowCount], sinks; isCausal, hasAttentionSinks, slidingWindow).  The operator's arithmetic
+    is in the absent back end, so the definition is restated from its use (:1080-1133: the selected rows are what a
+    top-k indexer picked, or every compressed row the query may see): query i attends, in ONE softmax, to the raw rows
+    j with j <= i + (Sr - Sq) [causal] and j > i + (Sr - Sq) - W [window], and to compressed row c once for every time
+    c appears in selected[i]; entries outside [0, Sc) name no row; the sink of the head joins the denominator.
+    q [B,Sq,Hq,D], k_raw/v_raw [B,Sr,Hkv,D], k_comp/v_comp [B,Sc,Hkv,D] or None, selected int [B or 1,Sq,n]."""
+    B, Sq, Hq, D = q.shape
+    Sr, Hkv = k_raw.shape[1], k_raw.shape[2]
+    G = Hq // Hkv
+    qf = q.to(compute_dtype).permute(0, 2, 1, 3) * scale                                  # [B,Hq,Sq,D]
+    kr = k_raw.to(compute_dtype).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)          # [B,Hq,Sr,D]
+    vr = v_raw.to(compute_dtype).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    s_raw = qf @ kr.transpose(-1, -2)                                                     # [B,Hq,Sq,Sr]
+    i = torch.arange(Sq).view(Sq, 1)
+    j = torch.arange(Sr).view(1, Sr)
+    hidden = torch.zeros(Sq, Sr, dtype=torch.bool)
+    if is_causal:
+        hidden |= j > i + (Sr - Sq)
+    if sliding_window > 0:
+        hidden |= j <= i + (Sr - Sq) - sliding_window
+    s_raw = s_raw.masked_fill(hidden, float("-inf"))
+    parts, values = [s_raw], None
+    Sc = 0 if k_comp is None else k_comp.shape[1]
+    if Sc > 0 and selected is not None and selected.shape[-1] > 0:
+        sel = selected.long().expand(B, Sq, selected.shape[-1])                            # [B,Sq,n]
+        ok = (sel >= 0) & (sel < Sc)
+        idx = sel.clamp(0, Sc - 1)
+        kc = k_comp.to(compute_dtype).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)      # [B,Hq,Sc,D]
+        vc = v_comp.to(compute_dtype).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+        bi = torch.arange(B).view(B, 1, 1, 1)
+        hi = torch.arange(Hq).view(1, Hq, 1, 1)
+        ksel = kc[bi, hi, idx.unsqueeze(1)]                                                # [B,Hq,Sq,n,D]
+        vsel = vc[bi, hi, idx.unsqueeze(1)]
+        s_sel = torch.einsum("bhqd,bhqnd->bhqn", qf, ksel).masked_fill(~ok.unsqueeze(1), float("-inf"))
+        parts.append(s_sel)
+        values = vsel
+    s = torch.cat(parts, dim=-1)
+    m = s.amax(dim=-1, keepdim=True)
+    if sinks is not None:
+        sk = sinks.to(compute_dtype).view(1, Hq, 1, 1)
+        m = torch.maximum(m, sk.expand_as(m))
+    m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    e = torch.exp(s - m)
+    l = e.sum(dim=-1, keepdim=True)
+    if sinks is not None:
+        l = l + torch.exp(sk - m)
+    p = e / torch.where(l > 0, l, torch.ones_like(l))
+    o = p[..., :Sr] @ vr
+    if values is not None:
+        o = o + torch.einsum("bhqn,bhqnd->bhqd", p[..., Sr:], values)
+    o = o.permute(0, 2, 1, 3).contiguous()
+    if return_lse:
+        return o, (m + torch.log(l)).squeeze(-1)
+    return o
+
+
 def instruction_count(batch, heads, head_dim, seq_a, seq_b):
     """The reference's own cost model for the op, in FMA-instructions (InstructionCount.swift:9-17)."""
     return batch * heads * (2 * head_dim + 5) * seq_a * seq_b

@@ -103,3 +103,40 @@ def test_variant_fixtures():
         assert g["index"] == w["index"], name
         assert max(abs(a - b) for a, b in zip(g["values"], w["values"])) < 1e-9, name
         assert abs(g["sum"] - w["sum"]) < 1e-6 * max(1.0, abs(w["sum"])), name
+
+
+def test_sparse_indexed_attention_closed_forms():
+    """SparseIndexedAttention (DeepSeek4.swift:521-545) restated: raw rows under the causal window and selected rows of
+    the compressed tensor in one softmax.  Checked against forms that do not use the restatement's own code path."""
+    B, Sq, Sr, Sc, Hq, Hkv, D = 2, 6, 10, 7, 4, 1, 16
+    q = so.seeded_normal((B, Sq, Hq, D), 61)
+    kr, vr = so.seeded_normal((B, Sr, Hkv, D), 62), so.seeded_normal((B, Sr, Hkv, D), 63)
+    kc, vc = so.seeded_normal((B, Sc, Hkv, D), 64), so.seeded_normal((B, Sc, Hkv, D), 65)
+    sinks = so.seeded_normal((Hq,), 66)
+    # (1) every compressed row selected by every query, no window: plain attention over [compressed; raw] keys with
+    # the causal rule on the raw part only, which an additive mask expresses
+    sel_all = torch.arange(Sc, dtype=torch.int32).view(1, 1, Sc).expand(1, Sq, Sc).contiguous()
+    got = so.sparse_indexed_explicit(q, kr, vr, kc, vc, sel_all, 0.3, sinks=sinks, compute_dtype=torch.float64)
+    mask = torch.zeros(1, 1, Sq, Sc + Sr, dtype=torch.float64)
+    i, j = torch.arange(Sq).view(Sq, 1), torch.arange(Sr).view(1, Sr)
+    mask[0, 0, :, Sc:] = torch.where(j > i + (Sr - Sq), float("-inf"), 0.0)
+    want = so.sdpa_explicit(q, torch.cat([kc, kr], 1), torch.cat([vc, vr], 1), 0.3, mask=mask, sinks=sinks,
+                            compute_dtype=torch.float64)
+    assert (got - want).abs().max() < 1e-12
+    # (2) no valid selected row: the raw sliding-window operator
+    none = torch.full((1, Sq, 3), -1, dtype=torch.int32)
+    got = so.sparse_indexed_explicit(q, kr, vr, kc, vc, none, 0.3, sinks=sinks, sliding_window=4, compute_dtype=torch.float64)
+    want = so.sdpa_explicit(q, kr, vr, 0.3, True, sinks=sinks, sliding_window=4, compute_dtype=torch.float64)
+    assert (got - want).abs().max() < 1e-12
+    # (3) a row listed twice counts twice; out-of-range entries name no row
+    sel = torch.tensor([[2, 2, 99], [0, 5, -1], [1, 1, 1], [6, -7, 3], [4, 4, 0], [7, 8, 9]], dtype=torch.int32).view(1, Sq, 3)
+    got = so.sparse_indexed_explicit(q, kr, vr, kc, vc, sel, 0.3, sliding_window=3, compute_dtype=torch.float64)
+    for b in range(B):
+        for t in range(Sq):
+            rows = [c for c in sel[0, t].tolist() if 0 <= c < Sc]
+            raw = [r for r in range(Sr) if r <= t + (Sr - Sq) and r > t + (Sr - Sq) - 3]
+            k_list = torch.cat([kr[b, raw], kc[b, rows]], 0) if rows else kr[b, raw]
+            v_list = torch.cat([vr[b, raw], vc[b, rows]], 0) if rows else vr[b, raw]
+            want_t = so.sdpa_explicit(q[b:b + 1, t:t + 1], k_list.unsqueeze(0), v_list.unsqueeze(0), 0.3,
+                                      compute_dtype=torch.float64)
+            assert (got[b, t] - want_t[0, 0]).abs().max() < 1e-12
