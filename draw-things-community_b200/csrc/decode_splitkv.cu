@@ -668,7 +668,66 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
-  // Combine.  All loads of a phase are independent so they overlap: first every (partial, row) pair's (m, l) lands in
+  // Combine.  Up to 32 partials: one warp per output row, one round trip.  Lane s fetches partial s's (m, l) of the row
+  // while every lane fetches its float4 column of all the partials' O; the weights come out of warp reductions and
+  // travel by shuffle, so nothing waits on a second dependent load or on shared memory.  (B=1, D=128: 13.4 -> 12.9 us
+  // per call; head dim 256 would need two column passes per row and measured slower this way, it keeps the form below.)
+  if (D <= 128 && a.nparts <= 32) {
+    const int np = a.nparts;
+    const int64_t base = (int64_t)pair * np;
+    constexpr int kVec = D / 4;
+    const int64_t part_stride = (int64_t)a.M * kVec;
+    for (int r = warp; r < a.M; r += kThreads / 32) {
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (lane < np) ml = __ldcg(reinterpret_cast<const float2*>(&a.part_ml[((base + lane) * a.M + r) * 2]));
+#pragma unroll 1
+      for (int c0 = 0; c0 < kVec; c0 += 32) {
+        const int d4 = c0 + lane;
+        const bool col_ok = d4 < kVec;
+        const float4* src = reinterpret_cast<const float4*>(a.part_o) + (base * a.M + r) * kVec + (col_ok ? d4 : 0);
+        float4 v[32];
+#pragma unroll
+        for (int u = 0; u < 32; ++u)
+          v[u] = (u < np && col_ok) ? __ldcg(src + u * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float mstar = ml.x;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, o2));
+        float wgt = mstar == -INFINITY ? 0.f : fast_exp2(ml.x - mstar);
+        float lt = wgt * ml.y;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o2);
+        if (a.sinks) {
+          // the sink is one more partial: weight 1 for it, every partial's weight rescaled to the common max
+          const float sl = to_float(reinterpret_cast<const T*>(a.sinks)[kvh * a.G + r % a.G]) * kLog2e;
+          const float m2 = fmaxf(mstar, sl);
+          const float down = mstar == -INFINITY ? 0.f : fast_exp2(mstar - m2);
+          wgt *= down;
+          lt = lt * down + fast_exp2(sl - m2);
+          mstar = m2;
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 32; ++u) {
+          const float wu = __shfl_sync(0xffffffffu, wgt, u);
+          acc.x = fmaf(wu, v[u].x, acc.x);
+          acc.y = fmaf(wu, v[u].y, acc.y);
+          acc.z = fmaf(wu, v[u].z, acc.z);
+          acc.w = fmaf(wu, v[u].w, acc.w);
+        }
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        const int sq = r / a.G, h = kvh * a.G + r % a.G;
+        if (col_ok) {
+          T* dst = o + b * a.o_sb + (int64_t)sq * a.o_ss + (int64_t)h * a.o_sh + d4 * 4;
+          dst[0] = from_float<T>(acc.x * inv);
+          dst[1] = from_float<T>(acc.y * inv);
+          dst[2] = from_float<T>(acc.z * inv);
+          dst[3] = from_float<T>(acc.w * inv);
+        }
+        if (a.lse && c0 == 0 && lane == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
+      }
+    }
+  } else {
+  // More partials than lanes.  All loads of a phase are independent so they overlap: first every (partial, row) pair's (m, l) lands in
   // shared memory and one warp per row turns them into weights (lanes over partials, shuffle reductions); then each
   // thread owns one float4 of one output row and streams the partial O, 32 loads in flight.
   {
@@ -742,6 +801,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       dst[3] = from_float<T>(acc.w * inv);
       if (a.lse && d4 == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + sq] = lt > 0.f ? mstar * kLn2 + logf(lt) : -INFINITY;
     }
+  }
   }
   DT_STAMP(5);
   if (threadIdx.x == 0) a.counters[pair] = 0u;  // leave the workspace ready for the next call
