@@ -110,6 +110,9 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   GroupBars* bars_all = reinterpret_cast<GroupBars*>(base_ptr + kGroups * C::kGroupBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef DT_BRINGUP
+  if (a.dbg && threadIdx.x == 0) a.dbg[((long long)blockIdx.x * kGroups * 8 + 6) * 8 + 7] = ptx::globaltimer_ns();  // CTA entry
+#endif
   // pipeline g's run of tiles: an even share of all (batch, head, query tile) triples, consecutive, so that most
   // of a run reads one head's K/V
   const long long n_runs = (long long)gridDim.x * kGroups;
@@ -358,7 +361,7 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (a.lse && row < a.Sq) a.lse[((int64_t)w.b * a.Hq + w.h) * a.Sq + row] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
       DT_SSTAMP(5);
     }
-    if (lane == 0) ptx::bulk_wait_all();
+    if (lane == 0) ptx::bulk_wait_read_all();  // the staging rows have been read; the global writes complete with the kernel
   }
 
   // =========================== teardown ===========================
@@ -368,6 +371,9 @@ crossattn_short_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_all, 512);
   }
+#ifdef DT_BRINGUP
+  if (a.dbg && threadIdx.x == 96) a.dbg[((long long)blockIdx.x * kGroups * 8 + 6) * 8 + 6] = ptx::globaltimer_ns();  // CTA exit
+#endif
 }
 
 template <typename T, int NU>

@@ -251,7 +251,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bars->acc_empty[buf]);
     }
-    if (lane == 0) ptx::bulk_wait_all();
+    if (lane == 0) ptx::bulk_wait_read_all();  // the staging rows have been read; the global writes complete with the kernel
   }
 
   // =========================== teardown ===========================

@@ -728,7 +728,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         uint64_t lsum[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
           lsum[c] = 0ull;
           if (c < nch) {
 #pragma unroll
@@ -747,9 +746,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               p1 = fast_exp2(x1);
             }
             lsum[c] = ptx::add_f32x2(lsum[c], ptx::pack_f32x2(p0, p1));
-            pk[i] = kBf16 ? ptx::cvt_pack_bf16(p0, p1) : ptx::cvt_pack_f16(p0, p1);
+            // the packed pair goes into the register score i of this chunk came in (scores 2i and 2i+1 are used up)
+            if constexpr (kBf16 != 0) ptx::cvt_pack_bf16_into(s[c][i], p0, p1);
+            else ptx::cvt_pack_f16_into(s[c][i], p0, p1);
           }
-          ptx::tmem_st16(t_s + c * 16, pk);
+          ptx::tmem_st16(t_s + c * 16, s[c]);
           }
           if (c == 1 || c == 3) {  // 64 keys of P are in TMEM: let the MMA warp start on them
             ptx::tc_wait_st();
@@ -862,7 +863,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 
   // =========================== teardown ===========================
-  if (warp >= 4 && lane == 0) ptx::bulk_wait_all();
+  if (warp >= 4 && lane == 0) ptx::bulk_wait_read_all();  // staging rows read; the global writes complete with the kernel
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 2) {

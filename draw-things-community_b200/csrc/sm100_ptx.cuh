@@ -347,6 +347,16 @@ __device__ __forceinline__ uint32_t cvt_pack_f16(float lo, float hi) {
   return d;
 }
 
+// The same conversions writing INTO a register that already holds something else ("+r": input and output are one PTX
+// register).  The softmax uses it to put the packed P words into the registers the scores came in, a block of
+// consecutive registers that tcgen05.ld filled and tcgen05.st can read again without a register move per word.
+__device__ __forceinline__ void cvt_pack_bf16_into(uint32_t& d, float lo, float hi) {
+  asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "+r"(d) : "f"(hi), "f"(lo));
+}
+__device__ __forceinline__ void cvt_pack_f16_into(uint32_t& d, float lo, float hi) {
+  asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "+r"(d) : "f"(hi), "f"(lo));
+}
+
 // 2^x for a pair of fp32 values on the FMA/ALU pipes instead of the special-function unit: round-to-nearest
 // range reduction with the 1.5*2^23 trick, degree-3 minimax polynomial on [-0.5, 0.5] (relative error
 // 7.5e-5, far below the rounding of the 16-bit P it feeds), exponent added with integer arithmetic.

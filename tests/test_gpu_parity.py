@@ -365,6 +365,10 @@ def test_host_entry_point(dtattn):
         out2 = dtattn.sdpa_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, causal,
                                    sinks=None if sinks is None else sinks.cuda()).cpu()
         assert torch.equal(out, out2), "host path and device path must agree bitwise"
+    # the UNet cross-attention shape from host tensors: the short key/value kernel behind the host entry point
+    q, k, v = inputs(2, 4096, 77, 20, 20, 64, torch.float16, 96, 0.5)
+    out = dtattn.sdpa_forward(q, k, v, 0.125)
+    check(out, c_oracle.sdpa_c(q, k, v, 0.125), torch.float16, "host path, cross-attention", strict=True)
     # sinks on the plain (single-stream) host path
     q, k, v = inputs(1, 300, 300, 4, 2, 64, torch.float16, 93)
     sinks = (so.seeded_normal((4,), 94) * 2.0).to(torch.float16)
