@@ -106,7 +106,7 @@ def sdpa_varlen_explicit(q, k, v, scale, offsets_q, offsets_k, is_causal=False, 
     out = torch.zeros(q.shape, dtype=kw.get("compute_dtype", torch.float32))
     for s in range(len(offsets_q) - 1):
         q0, q1, k0, k1 = offsets_q[s], offsets_q[s + 1], offsets_k[s], offsets_k[s + 1]
-        if q1 > q0:
+        if q1 > q0 and k1 > k0:  # queries of a sequence without keys see nothing: zeros, like a fully hidden row
             out[:, q0:q1] = sdpa_explicit(q[:, q0:q1], k[:, k0:k1], v[:, k0:k1], scale, is_causal, **kw)
     return out
 
