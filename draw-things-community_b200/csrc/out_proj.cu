@@ -13,6 +13,10 @@
 //           4-stage ring; one thread issues four tcgen05.mma (M128 N256 K16) per stage into one of two 256-column fp32
 //           accumulators in TMEM (the epilogue of tile i overlaps the main loop of tile i + 1) and commits the stage
 //           back to the producer; the ring keeps running across tiles.
+//   tail  = the tiles left over after the last full round over the SMs are cut into 2 or 4 column slices (N = 128 or
+//           64 per MMA) when that many slices still fit one round, so the last round costs a half or a quarter of a
+//           tile time instead of a whole one (SDXL's 320 tiles on 148 SMs: 2 rounds + 96 quarter tiles); a problem
+//           with fewer tiles than SMs is sliced the same way to use more of them.
 //   out   = accumulator rows -> + bias -> 16-bit -> swizzled staging rows -> one TMA store per warp and half
 //           (clipped by the tensor map at the edges of M and N).
 // Every wait is bounded and reports through the device status word (code 6).
@@ -42,6 +46,8 @@ struct ProjArgs {
   unsigned int* status;
   int S, N, K, tiles_per_batch;
   int n_tiles_n, n_tiles;  // column tiles, all tiles (column tile fastest)
+  int full_rounds;         // rounds in which CTA x works on whole tile x + round * gridDim.x
+  int tail_split, tail_units;  // then CTA x < tail_units takes slice x % tail_split of tile full_rounds * gridDim.x + x / tail_split
   // Row-parallel mode (head-sharded ranks each hold a K-slice): the fp32 partial tile goes to the rank that owns
   // its rows, into slab [this rank] of that rank's receive buffer [world][rows_per_rank][N] (ordinary stores, peer
   // memory over NVLink for other ranks); the owner sums the slabs afterwards.  slab[0] == nullptr: plain mode.
@@ -58,7 +64,7 @@ __device__ __forceinline__ uint32_t pack_pair_t(float a, float b) {
 template <typename T>
 __global__ void __launch_bounds__(kProjThreads)
 out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_c, const ProjArgs a) {
+                const __grid_constant__ CUtensorMap map_b_tail, const __grid_constant__ CUtensorMap map_c, const ProjArgs a) {
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -74,6 +80,25 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   auto tile_n0 = [&](int t) { return (t % a.n_tiles_n) * kTileN; };
   auto tile_b = [&](int t) { return (t / a.n_tiles_n) / a.tiles_per_batch; };
   auto tile_s0 = [&](int t) { return ((t / a.n_tiles_n) % a.tiles_per_batch) * kTile; };
+  // i-th unit of work of this CTA: a whole tile, or (last) one column slice of a left-over tile
+  struct Unit { int n0, b, s0, width; };
+  auto unit_at = [&](int i, Unit& u) -> bool {
+    int t;
+    if (i < a.full_rounds) {
+      t = (int)blockIdx.x + i * (int)gridDim.x;
+      u.width = kTileN;
+      u.n0 = tile_n0(t);
+    } else if (i == a.full_rounds && (int)blockIdx.x < a.tail_units) {
+      t = a.full_rounds * (int)gridDim.x + (int)blockIdx.x / a.tail_split;
+      u.width = kTileN / a.tail_split;
+      u.n0 = tile_n0(t) + ((int)blockIdx.x % a.tail_split) * u.width;
+    } else {
+      return false;
+    }
+    u.b = tile_b(t);
+    u.s0 = tile_s0(t);
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -102,10 +127,14 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
       ptx::prefetch_tensormap(&map_c);
+      if (a.tail_split > 1) ptx::prefetch_tensormap(&map_b_tail);
       int it = 0;  // ring position, continues across tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x) {
-        const int n0 = tile_n0(t), b = tile_b(t), s0 = tile_s0(t);
+      Unit u;
+      for (int i = 0; ok && unit_at(i, u); ++i) {
+        const int n0 = u.n0, b = u.b, s0 = u.s0;
+        const CUtensorMap* mb = u.width == kTileN ? &map_b : &map_b_tail;
+        const uint32_t stage_tx = (uint32_t)(kBoxBytesP + u.width * 128);
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int st = it % kStages, use = it / kStages;
           if (use > 0 && !ptx::mbar_wait(&bars->empty[st], (use - 1) & 1, abort_flag)) {
@@ -114,21 +143,22 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(&bars->full[st], (uint32_t)kStageBytesP);
+          ptx::mbar_arrive_expect_tx(&bars->full[st], stage_tx);
           uint8_t* dst = base_ptr + st * kStageBytesP;
           ptx::tma_load_4d(dst, &map_a, &bars->full[st], kb * kKStep, 0, s0, b);
-          ptx::tma_load_4d(dst + kBoxBytesP, &map_b, &bars->full[st], kb * kKStep, 0, n0, 0);
+          ptx::tma_load_4d(dst + kBoxBytesP, mb, &bars->full[st], kb * kKStep, 0, n0, 0);
         }
       }
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_f16(kBf16, kTile, kTileN, 0, 0);
       const uint64_t desc = ptx::make_smem_desc_sw128(0, 16, 1024);
       bool ok = true;
       int it = 0, n_tile = 0;
-      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x, ++n_tile) {
+      Unit u;
+      for (; ok && unit_at(n_tile, u); ++n_tile) {
+        const uint32_t idesc = ptx::make_idesc_f16(kBf16, kTile, u.width, 0, 0);
         const int buf = n_tile & 1, use = n_tile >> 1;
         // the epilogue must have drained this accumulator (two tiles ago)
         if (use > 0 && !ptx::mbar_wait(&bars->acc_empty[buf], (use - 1) & 1, abort_flag)) {
@@ -161,9 +191,10 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // =========================== epilogue ===========================
     const int ew = warp - 4;  // TMEM lanes 32*ew .. 32*ew + 31 = tile rows
     int n_tile = 0;
-    for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++n_tile) {
+    Unit u;
+    for (; unit_at(n_tile, u); ++n_tile) {
       const int buf = n_tile & 1;
-      const int n0 = tile_n0(t), b = tile_b(t), s0 = tile_s0(t);
+      const int n0 = u.n0, b = u.b, s0 = u.s0;
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->acc_full[buf], (n_tile >> 1) & 1, abort_flag))) {
         atomicCAS(a.status, 0u, 6u);
         *abort_flag = 1;
@@ -183,7 +214,7 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (owner == i) slab = a.slab[i];
         float* dst = slab + ((size_t)a.rank * a.rows_per_rank + (size_t)(row0 - owner * a.rows_per_rank)) * a.N;
 #pragma unroll 1
-        for (int c = 0; c < kTileN / 32; ++c) {
+        for (int c = 0; c < u.width / 32; ++c) {
           uint32_t acc[32];
           ptx::tmem_ld32(t_acc + c * 32, acc);
           ptx::tc_wait_ld();
@@ -208,8 +239,8 @@ out_proj_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __syncwarp();
         }
       } else {
-#pragma unroll
-      for (int hf = 0; hf < kTileN / 64; ++hf) {
+#pragma unroll 1
+      for (int hf = 0; hf < u.width / 64; ++hf) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t acc[32];
@@ -267,7 +298,7 @@ template <typename T>
 int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* weight, const void* bias, int N,
                   const dt_tensor4& out, int dtype, cudaStream_t stream, float* const* slabs = nullptr, int world = 0,
                   int rank = 0, int rows_per_rank = 0) {
-  CUtensorMap ma, mb, mc;
+  CUtensorMap ma, mb, mb_tail, mc;
   dt_tensor4 w_view{const_cast<void*>(weight), (int64_t)N * K, (int64_t)K, (int64_t)K};
   if (!make_bshd_tensor_map(&ma, a_view, B, S, 1, K, dtype, kTile)) return DT_UNSUPPORTED;
   if (!make_bshd_tensor_map(&mb, w_view, 1, N, 1, K, dtype, kTileN)) return DT_UNSUPPORTED;
@@ -290,11 +321,16 @@ int launch_proj_t(const dt_tensor4& a_view, int B, int S, int K, const void* wei
   const int64_t tiles = (int64_t)a.n_tiles_n * a.tiles_per_batch * B;
   if (tiles > (1 << 30)) return DT_UNSUPPORTED;
   a.n_tiles = (int)tiles;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  dim3 grid((unsigned)(tiles < sms ? tiles : sms));  // one persistent CTA per SM
-  kern<<<grid, kProjThreads, kProjSmem, stream>>>(ma, mb, mc, a);
+  const int sms = device_sm_count();
+  // whole rounds of one tile per SM, then the left-over tiles in column slices while the slices fit one round
+  a.full_rounds = (int)(tiles / sms);
+  const int rem = (int)(tiles % sms);
+  a.tail_split = rem == 0 ? 1 : (4 * rem <= sms ? 4 : (2 * rem <= sms ? 2 : 1));
+  a.tail_units = rem * a.tail_split;
+  mb_tail = mb;
+  if (a.tail_split > 1 && !make_bshd_tensor_map(&mb_tail, w_view, 1, N, 1, K, dtype, kTileN / a.tail_split)) return DT_UNSUPPORTED;
+  dim3 grid((unsigned)(a.full_rounds > 0 ? sms : a.tail_units));  // one persistent CTA per SM
+  kern<<<grid, kProjThreads, kProjSmem, stream>>>(ma, mb, mb_tail, mc, a);
   DT_CUDA_TRY(cudaGetLastError());
   return DT_OK;
 }

@@ -30,6 +30,9 @@ CASES = [
     (1, 130, 130, 20, 64, 1280, torch.bfloat16, True, True),    # K = 1280: twenty 64-wide K steps, ring wraps 5 times
     (3, 17, 50, 2, 128, 64, torch.float16, True, False),        # less than one tile in every dimension
     (1, 1, 2000, 32, 128, 4096, torch.float16, True, True),     # decode step followed by o_proj (Qwen3_5.swift:198-202)
+    (1, 2560, 77, 20, 64, 2048, torch.float16, True, False),    # 160 tiles on 148 SMs: one round + 12 tiles in quarter slices
+    (1, 1408, 77, 4, 64, 4608, torch.bfloat16, True, False),    # 198 tiles: one round + 50 tiles in half slices
+    (1, 1300, 77, 4, 64, 4504, torch.float16, False, False),    # the same with ragged last row and column tiles
 ]
 
 
