@@ -13,6 +13,7 @@ Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
 (the reference's own back end is not buildable: its arithmetic lives in un-vendored dependencies).
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -542,7 +543,8 @@ def run_single(args, dtattn, device, peaks):
 def run_sharded(args, dtattn, device, peaks):
     import torch.distributed as dist
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    dist.init_process_group("nccl", device_id=device)
+    # a collective that some rank never joins ends the run after five minutes instead of torch's default of ten
+    dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=300))
     name = args.workload or "wan_self"
     w = WORKLOADS[name]
     assert w["Hq"] % world == 0, "heads must divide over the ranks"
@@ -588,13 +590,16 @@ def run_sharded(args, dtattn, device, peaks):
         dist.barrier()
         torch.cuda.synchronize()
         timed_ms = e0.elapsed_time(e1)
-        if timed_ms < 1200 and not args.profile:  # keep the load on while the 200 ms clock sampler collects a few samples
-            for i in range(int(min(400, 1200 / max(timed_ms / args.steps, 1e-3)))):
+        t = torch.tensor([timed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        timed_max = float(t.item())
+        # keep the load on while the 200 ms clock sampler collects a few samples.  Every step is a collective, so the
+        # number of extra steps is derived from the time all ranks agree on (the maximum), never from a rank's own clock.
+        if timed_max < 1200 and not args.profile:
+            for i in range(int(min(400, 1200 / max(timed_max / args.steps, 1e-3)))):
                 step(i)
             torch.cuda.synchronize()
-    t = torch.tensor([timed_ms], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    ms_step = timed_max / args.steps
     status = dtattn.device_status()
     fl = flops_of(w)
     tflops = fl / (ms_step * 1e-3) / 1e12

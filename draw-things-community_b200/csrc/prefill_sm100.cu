@@ -47,20 +47,27 @@ constexpr int kRegsLow = 80, kRegsHigh = 208;
 
 template <int D, bool kMask = false>
 struct Cfg {
+  // Query tiles per work item.  TMEM (512 columns) holds S (128 columns) and O (D columns) of two tiles up to
+  // D = 128; at D = 256 it holds one tile, whose softmax is run by the first softmax warpgroup alone (the second
+  // one idles): per key block that tile has twice the tensor-core work of a D = 128 tile under the same softmax.
+  static constexpr int kTiles = D == 256 ? 1 : 2;
+  static constexpr int kSoftmaxWarps = 4 * kTiles;
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = kHalves * kHalfBytes;  // one Q tile / one K block / one V block
-  // the masked variant gives 32 KB of the K/V ring to the second mask staging buffers
-  static constexpr int kSlots = (D == 128 ? 4 : 8) - (kMask ? 32 * 1024 / kTileBytes : 0);
-  static constexpr int kMaskBytes = kMask ? 8 * 32 * 128 : 0;  // per softmax warp: 32 rows x 64 keys x 16-bit (one half block)
-  static constexpr int kStageBytes = 8 * 32 * 128;  // per softmax warp: 32 rows x 64 x 16-bit of O for the TMA store
-  static constexpr int kQBufs = D == 128 ? 1 : 2;       // Q buffers: with D = 64 there is room to load the next item's Q early
-  static constexpr int kQBytes = kQBufs * 2 * kTileBytes;
+  // the masked variant gives 32 KB of the K/V ring to the second mask staging buffers (D = 256: two 64 KB slots,
+  // one K and one V block in flight, and the mask buffers fit beside them)
+  static constexpr int kSlots = D == 256 ? 2 : (D == 128 ? 4 : 8) - (kMask ? 32 * 1024 / kTileBytes : 0);
+  static constexpr int kMaskBytes = kMask ? kSoftmaxWarps * 32 * 128 : 0;  // per softmax warp: 32 rows x 64 keys x 16-bit (one half block)
+  static constexpr int kStageBytes = kSoftmaxWarps * 32 * 128;  // per softmax warp: 32 rows x 64 x 16-bit of O for the TMA store
+  static constexpr int kQBufs = D == 64 ? 2 : 1;        // Q buffers: with D = 64 there is room to load the next item's Q early
+  static constexpr int kQBytes = kQBufs * kTiles * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarBytes = 512;
   static constexpr int kSmemBytes = kQBytes + kRingBytes + kStageBytes + kMaskBytes + kBarBytes + 1024;
   static constexpr uint32_t kTmemCols = 512;
-  static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
+  static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;  // (tile 1's columns: only with kTiles == 2)
 };
+static_assert(Cfg<256, true>::kSmemBytes <= 227 * 1024, "shared memory of the widest variant");
 
 struct PrefillArgs {
   void* o;
@@ -257,7 +264,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     it.h = bh % a.Hq;
     it.b = bh / a.Hq;
     it.kvh = it.h / G;
-    it.q0 = qt * (2 * kBM);
+    it.q0 = qt * (C::kTiles * kBM);
     it.sq = a.Sq;
     it.sk = a.Sk;
     it.qrow = it.krow = 0;
@@ -269,7 +276,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       it.b = 0;
     }
     it.off = it.sk - it.sq;
-    it.two = it.q0 + kBM < it.sq;
+    it.two = C::kTiles == 2 && it.q0 + kBM < it.sq;
     it.j0 = 0;
     if (it.q0 >= it.sq) {  // only with variable lengths: this sequence is shorter than the longest one
       it.nkv = 0;
@@ -277,7 +284,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     int nkv = max(1, (it.sk + kBN - 1) / kBN);  // a sequence without keys still runs one (fully masked) block
     if (a.is_causal) {
-      const int last_row = min(it.sq, it.q0 + 2 * kBM) - 1;
+      const int last_row = min(it.sq, it.q0 + C::kTiles * kBM) - 1;
       const long long lim = (long long)last_row + it.off + 1;  // keys [0, lim) can be visible
       const int need = (int)((max(0LL, min((long long)it.sk, lim)) + kBN - 1) / kBN);
       nkv = max(1, min(nkv, need));
@@ -377,7 +384,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int t = 0; t < (w.two ? 2 : 1); ++t)
 #pragma unroll
             for (int hf = 0; hf < C::kHalves; ++hf)
-              ptx::tma_load_4d(base_ptr + (qb * 2 + t) * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full[qb], hf * 64,
+              ptx::tma_load_4d(base_ptr + (qb * C::kTiles + t) * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full[qb], hf * 64,
                                w.h, w.qrow + w.q0 + t * kBM, w.b);
           for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
         }
@@ -414,7 +421,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           const int ntile = w.two ? 2 : 1;
           const int qb = n_item % C::kQBufs;
-          const uint64_t qd0 = qd_base + (uint64_t)(qb * 2 * (C::kTileBytes >> 4));
+          const uint64_t qd0 = qd_base + (uint64_t)(qb * C::kTiles * (C::kTileBytes >> 4));
           const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
           // ---- S_t(0) = Q_t K(0)^T ----
           stamp(a, 16 * n_item + 5);
@@ -828,7 +835,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && tma_ok) {
+          if (lane == 0 && tma_ok && hf * 64 < a.d_real) {  // (a half made of padding columns only is not stored)
             ptx::tma_store_4d(&map_o, my_stage, hf * 64, w.h, w.qrow + wrow0, w.b);
             ptx::bulk_commit_group();
           }
@@ -924,7 +931,7 @@ int launch_t(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra, i
   const bool varlen = p.seq_offsets_q != nullptr;
   a.off_q = p.seq_offsets_q;
   a.off_k = p.seq_offsets_k;
-  a.n_qpairs = ((varlen ? p.max_seq_q : p.Sq) + 2 * kBM - 1) / (2 * kBM);
+  a.n_qpairs = ((varlen ? p.max_seq_q : p.Sq) + C::kTiles * kBM - 1) / (C::kTiles * kBM);
   a.n_items = a.n_qpairs * p.Hq * (varlen ? p.n_seq : p.B);
   auto kern = prefill_tcgen05_kernel<T, D, kMask>;
   DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
@@ -944,7 +951,7 @@ bool prefill_supported(const dt_sdpa_params& p) {
   if (p.seq_offsets_q && (p.is_causal || p.sliding_window > 0 || p.n_seq > 65535)) return false;
   if (p.sliding_window > 0 && p.Sq > p.Sk) return false;  // rows that may see no key: generic kernel
   if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
-  if (p.D < 8 || p.D > 128 || p.D % 8) return false;  // head dims below 64 / 128 run zero-padded (SD1.5: 40, 80)
+  if (p.D < 8 || p.D > 256 || p.D % 8) return false;  // head dims below 64 / 128 / 256 run zero-padded (SD1.5: 40, 80, 160)
   // additive mask: each row's entries are read with 16-byte loads
   if (p.mask && (reinterpret_cast<uintptr_t>(p.mask) % 16 || p.mask_stride_b % 8 || p.mask_stride_h % 8 || p.mask_stride_q % 8))
     return false;
@@ -968,14 +975,11 @@ size_t prefill_workspace_bytes(const dt_sdpa_params& p) {
 
 int launch_prefill(const dt_sdpa_params& p, cudaStream_t stream, void* const* extra_outputs, int n_extra, void* workspace,
                    size_t workspace_bytes) {
-  const bool wide = p.D > 64;
 #define DT_PREFILL_GO(T, DD, M) launch_t<T, DD, M>(p, stream, extra_outputs, n_extra, workspace, workspace_bytes)
-  if (p.mask) {
-    if (p.dtype == DT_F16) return wide ? DT_PREFILL_GO(__half, 128, true) : DT_PREFILL_GO(__half, 64, true);
-    return wide ? DT_PREFILL_GO(__nv_bfloat16, 128, true) : DT_PREFILL_GO(__nv_bfloat16, 64, true);
-  }
-  if (p.dtype == DT_F16) return wide ? DT_PREFILL_GO(__half, 128, false) : DT_PREFILL_GO(__half, 64, false);
-  return wide ? DT_PREFILL_GO(__nv_bfloat16, 128, false) : DT_PREFILL_GO(__nv_bfloat16, 64, false);
+#define DT_PREFILL_BY_D(T, M) (p.D > 128 ? DT_PREFILL_GO(T, 256, M) : p.D > 64 ? DT_PREFILL_GO(T, 128, M) : DT_PREFILL_GO(T, 64, M))
+  if (p.mask) return p.dtype == DT_F16 ? DT_PREFILL_BY_D(__half, true) : DT_PREFILL_BY_D(__nv_bfloat16, true);
+  return p.dtype == DT_F16 ? DT_PREFILL_BY_D(__half, false) : DT_PREFILL_BY_D(__nv_bfloat16, false);
+#undef DT_PREFILL_BY_D
 #undef DT_PREFILL_GO
 }
 

@@ -123,6 +123,10 @@ def test_kernel_selection(dtattn):
     assert pick(2, 64, 77, 20, 20, 64, torch.float16, True) == "prefill_tcgen05"   # causal: the general kernel
     assert pick(2, 4096, 128, 20, 20, 64, torch.float16) == "prefill_tcgen05"      # more than 96 keys
     assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16) == "prefill_tcgen05"   # Flux joint attention
+    assert pick(1, 4352, 4352, 12, 12, 256, torch.bfloat16) == "prefill_tcgen05"   # AuraFlow joint attention: D = 256
+    assert pick(1, 2048, 2048, 16, 4, 256, torch.bfloat16, True) == "prefill_tcgen05"  # Qwen3.5 prompt prefill, D = 256
+    assert pick(1, 1, 2048, 16, 4, 256, torch.bfloat16, True) == "decode_splitkv"  # ... and its decode step
+    assert pick(2, 256, 256, 8, 8, 160, torch.float16) == "prefill_tcgen05"        # SD1.5 deepest blocks: D = 160 padded to 256
     assert pick(1, 75600, 75600, 5, 5, 128, torch.bfloat16) == "prefill_tcgen05"   # Wan, one rank's heads
     assert pick(16, 1, 8192, 32, 8, 128, torch.float16, True) == "decode_splitkv"  # GQA decode
     assert pick(1, 4608, 4608, 24, 24, 128, torch.bfloat16, flags=2) == "generic"

@@ -74,6 +74,8 @@ CASES = [
     (1, 77, 80, 2, 2, 64, torch.float16, False, 1, 1),       # one key block
     (1, 512, 1032, 2, 1, 128, torch.float16, True, 1, 1),    # nine key blocks, the last one of 8 keys
     (1, 40, 200, 2, 2, 40, torch.float16, False, 1, 2),      # SD1.5 head dim (zero-padded to 64)
+    (2, 300, 520, 8, 4, 256, torch.bfloat16, True, 2, 1),    # Gemma3 text encoder (Gemma3.swift:51,148): D = 256, causal + padding mask
+    (1, 200, 200, 2, 2, 256, torch.float16, False, 1, 2),    # D = 256, per-head bias
 ]
 
 

@@ -216,6 +216,13 @@ PREFILL = [
     (1, 200, 300, 4, 4, 80, torch.float16, False),
     (1, 130, 77, 2, 2, 96, torch.bfloat16, False),
     (1, 256, 256, 2, 1, 8, torch.float16, True),
+    # head dim 256 (AuraFlow.swift:358, Gemma3.swift:148, the shipped Qwen3.5 configs): one 128-row tile per work item
+    (1, 128, 128, 1, 1, 256, torch.bfloat16, False),   # one tile, one block
+    (1, 300, 700, 3, 3, 256, torch.bfloat16, False),   # ragged rows and keys, six blocks through the two-slot ring
+    (2, 640, 640, 4, 2, 256, torch.float16, True),     # causal, grouped KV heads, batch
+    (1, 200, 456, 2, 1, 256, torch.float16, True),     # causal, bottom-right aligned, ragged
+    (1, 260, 300, 2, 2, 160, torch.float16, False),    # SD1.5's deepest blocks: D = 160 zero-padded to 256
+    (1, 256, 256, 2, 2, 192, torch.bfloat16, True),
 ]
 
 

@@ -34,6 +34,7 @@ SINK_WINDOW = [
     (1, 20, 20, 2, 2, 40, torch.float32, True, 7, True, False),
     (1, 1500, 1500, 4, 2, 128, torch.bfloat16, True, 512, True, False),  # leading K/V blocks skipped per query tile
     (2, 700, 900, 4, 4, 64, torch.float16, True, 200, True, False),
+    (1, 700, 900, 4, 2, 256, torch.bfloat16, True, 200, True, False),   # D = 256 on the tensor-core kernel
 ]
 
 
@@ -95,7 +96,7 @@ def test_variable_length_batch(dtattn, causal):
     check(out, ref, dtype, f"varlen causal={causal}")
 
 
-@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.float16), (80, torch.float16)])
+@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.float16), (80, torch.float16), (256, torch.bfloat16)])
 def test_variable_length_batch_on_the_tensor_core_kernel(dtattn, D, dtype):
     """Packed vision-encoder style batch (Qwen3_5VL.swift:428-437, non-causal): sequences that end inside a 32-row
     store group, exactly on a tile edge, one row past it, an empty one, and one with queries but no keys."""
