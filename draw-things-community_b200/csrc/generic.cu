@@ -1,7 +1,7 @@
 // CUDA-core flash attention: the any-shape kernels (D <= 256, fp32/fp16/bf16, additive mask of any row stride,
 // causal, grouped KV heads, attention sinks, sliding window, variable-length batches).  They cover what the
-// tensor-core kernels do not (fp32 "upcastAttention" I/O, SD1.5's D = 160, masks whose rows are not 16-byte
-// aligned) and serve as an independent on-GPU second opinion in the tests.  Semantics follow the reference's
+// tensor-core kernels do not (fp32 "upcastAttention" I/O, head dims that are not a multiple of 8, masks whose
+// rows are not 16-byte aligned) and serve as an independent on-GPU second opinion in the tests.  Semantics follow the reference's
 // explicit graph (Libraries/SwiftDiffusion/Sources/Models/UNet.swift:217-265): fp32 scores, softmax over keys, P*V.
 //
 // Two mappings.  Register-tiled (D a multiple of 4, at least 32 query rows): described at generic_tiled_kernel.

@@ -3,9 +3,10 @@
 // (Libraries/SwiftDiffusion/Sources/Models/Flux1.swift:224-232 joint attention, Wan.swift:95-131 video
 // self-attention, UNetXL.swift:67-185 cross-attention) and the masked text encoders (an additive mask as 4th
 // input, alone or with isCausal: Llama.swift:70-73, CLIPTextModel.swift:46-51): fp16/bf16 I/O, fp32 accumulation,
-// head dim up to 128, grouped KV heads, optional bottom-right causal rule, BSHD strided views.
+// head dim up to 256, grouped KV heads, optional bottom-right causal rule, BSHD strided views.
 //
-// One CTA = one (batch, head, pair of 128-row query tiles).  12 warps:
+// One CTA = one (batch, head, pair of 128-row query tiles); at head dim 256 (AuraFlow.swift:358, Gemma3.swift:148,
+// Qwen3_5.swift:59-82) one tile, because TMEM holds S and O of only one.  12 warps:
 //   warp 0      TMA producer: Q tiles once, then K(j), V(j) blocks of 128 keys through a ring of slots
 //   warp 1      MMA issuer (one thread): S_t = Q_t K(j)^T  (operands in shared memory) and
 //               O_t += P_t V(j) (P read from TMEM, V from shared memory), interleaved over the two tiles so

@@ -1,9 +1,9 @@
 """The register-tiled CUDA-core kernel (64 query rows x 64 keys per step), through the C ABI, against the oracle.
 
 It serves what the tensor-core kernels do not take: fp32 tensors (the reference's upcastAttention,
-UNet.swift:217-265), head dims outside 64/128 in fp32 or beyond 128 in half precision (SD1.5's deepest blocks use
-D = 160), masks whose rows are not 16-byte aligned.  fp32 results must agree with the float64 oracle to fp32
-rounding of a few hundred accumulated terms; the 16-bit cases carry the tolerance of the other parity tests.
+UNet.swift:217-265) of any head dim, and masks whose rows are not 16-byte aligned.  fp32 results must agree with the
+float64 oracle to fp32 rounding of a few hundred accumulated terms; the 16-bit cases carry the tolerance of the other
+parity tests.
 """
 import pytest
 import torch
@@ -114,16 +114,19 @@ def test_fp32_variable_length_batch(dtattn):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_half_precision_head_dim_160_and_strided_views(dtattn, dtype):
-    """D = 160 in half precision, read through the reference's fused-projection layout (q, k, v are slices of one
-    [B, S, 3, H, D] tensor: token stride 3 H D)."""
+    """D = 160 in half precision (SD1.5's deepest blocks), read through the reference's fused-projection layout (q, k,
+    v are slices of one [B, S, 3, H, D] tensor: token stride 3 H D), on the CUDA-core kernel and on the kernel the
+    library picks by itself (the tensor-core one, zero-padded to 256)."""
     B, S, H, D = 2, 256, 8, 160
     qkv = so.seeded_normal((B, S, 3, H, D), 1231).to(dtype)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
     ref = so.sdpa_explicit(q, k, v, D ** -0.5, False, compute_dtype=torch.float64).float()
     dev = qkv.to(DEV)
-    out = dtattn.sdpa_forward(dev[:, :, 0], dev[:, :, 1], dev[:, :, 2], D ** -0.5, False)
-    torch.cuda.synchronize()
-    check(out, ref, dtype, f"d160 {dtype}")
+    for flags in (dtattn.DT_FLAG_FORCE_GENERIC, 0):
+        out = dtattn.sdpa_forward(dev[:, :, 0], dev[:, :, 1], dev[:, :, 2], D ** -0.5, False, flags=flags)
+        torch.cuda.synchronize()
+        assert dtattn.device_status() == 0
+        check(out, ref, dtype, f"d160 {dtype} flags={flags}")
 
 
 def test_unaligned_mask_rows_in_half_precision(dtattn):
