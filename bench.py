@@ -58,13 +58,22 @@ WORKLOADS = {
     "sd15_self_f16": dict(B=2, Sq=4096, Sk=4096, Hq=8, Hkv=8, D=40, dtype="f16", causal=False),
     "wan_self_5heads": dict(B=1, Sq=75600, Sk=75600, Hq=5, Hkv=5, D=128, dtype="bf16", causal=False),
     "decode_qwen35_d256": dict(B=1, Sq=1, Sk=8192, Hq=16, Hkv=4, D=256, dtype="bf16", causal=True),
+    # head dim 256 on the tensor-core kernel: AuraFlow joint attention (AuraFlow.swift:358-372: 3072 channels / 256)
+    # and prompt prefill of the shipped Qwen3.5 configs (Qwen3_5.swift:59-82)
+    "auraflow_joint_d256": dict(B=1, Sq=4352, Sk=4352, Hq=12, Hkv=12, D=256, dtype="bf16", causal=False),
+    "qwen35_prefill_d256": dict(B=1, Sq=8192, Sk=8192, Hq=16, Hkv=4, D=256, dtype="bf16", causal=True),
 }
 TDT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
 
 def flops_of(w, heads=None):
+    """4 B H Sq Sk D; under the causal rule only the visible (query, key) pairs count (row i of Sq sees
+    Sk - Sq + i + 1 keys)."""
     h = w["Hq"] if heads is None else heads
-    return 4 * w["B"] * h * w["Sq"] * w["Sk"] * w["D"]
+    full = 4 * w["B"] * h * w["Sq"] * w["Sk"] * w["D"]
+    if w.get("causal") and w["Sq"] > 1:
+        return full * (w["Sk"] - (w["Sq"] - 1) / 2.0) / w["Sk"]
+    return full
 
 
 def bytes_of(w):
@@ -214,7 +223,8 @@ def time_graph(fns, reps, warmup_reps=3):
 def side_measurements(dtattn, device, peaks):
     """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention."""
     out = {}
-    for name in ("decode_b16", "decode_b1", "decode_qwen35_d256", "sdxl_cross", "sd15_self_f16", "wan_self_5heads"):
+    for name in ("decode_b16", "decode_b1", "decode_qwen35_d256", "sdxl_cross", "sd15_self_f16", "wan_self_5heads",
+                 "auraflow_joint_d256", "qwen35_prefill_d256"):
         w = WORKLOADS[name]
         nbytes = bytes_of(w)
         n_sets = max(2, -(-3 * L2_BYTES // nbytes))  # rotate through > 3x L2 worth of distinct inputs
