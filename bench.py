@@ -220,11 +220,15 @@ def time_graph(fns, reps, warmup_reps=3):
     return e0.elapsed_time(e1) / (reps * len(fns))  # ms per launch
 
 
-def side_measurements(dtattn, device, peaks):
-    """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention."""
+SIDE_SHAPES = ("decode_b16", "decode_b1", "decode_qwen35_d256", "sdxl_cross", "sd15_self_f16", "wan_self_5heads",
+               "auraflow_joint_d256", "qwen35_prefill_d256")
+
+
+def side_measurements(dtattn, device, peaks, names=SIDE_SHAPES):
+    """The other single-GPU shapes of the metric: decode as GB/s of HBM, SDXL cross-attention, head dim 256.
+    With the default list the groups below (decode step, prologue, projection, mask) follow."""
     out = {}
-    for name in ("decode_b16", "decode_b1", "decode_qwen35_d256", "sdxl_cross", "sd15_self_f16", "wan_self_5heads",
-                 "auraflow_joint_d256", "qwen35_prefill_d256"):
+    for name in names:
         w = WORKLOADS[name]
         nbytes = bytes_of(w)
         n_sets = max(2, -(-3 * L2_BYTES // nbytes))  # rotate through > 3x L2 worth of distinct inputs
@@ -260,6 +264,8 @@ def side_measurements(dtattn, device, peaks):
             out[name]["frac_hbm_dependent_launch"] = round(nbytes / (ms_pdl * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         del sets, fns
         torch.cuda.empty_cache()
+    if names is not SIDE_SHAPES:
+        return out
     out.update(decode_step_measurements(dtattn, device))
     out.update(prologue_measurements(dtattn, device, peaks))
     out.update(out_proj_measurements(dtattn, device, peaks))
@@ -745,7 +751,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the gathered output (N > 1)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
-    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj", "masked"],
+    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj", "masked", "d256"],
                     help="run one group of side measurements alone and print it (for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
@@ -765,7 +771,8 @@ def main():
         fn = {"prologue": lambda: prologue_measurements(dtattn, device, peaks),
               "decode_step": lambda: decode_step_measurements(dtattn, device),
               "out_proj": lambda: out_proj_measurements(dtattn, device, peaks),
-              "masked": lambda: masked_measurements(dtattn, device, peaks)}[args.only]
+              "masked": lambda: masked_measurements(dtattn, device, peaks),
+              "d256": lambda: side_measurements(dtattn, device, peaks, ("auraflow_joint_d256", "qwen35_prefill_d256"))}[args.only]
         print(json.dumps({"only": args.only, "also": fn()}))
         return
     if world > 1:
