@@ -114,6 +114,7 @@ struct Barriers {
   uint64_t p_half[2][2];  // [tile][first / second 64 keys of P written]
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
+  uint64_t pv_done;  // one tile per item: completes once per P V, so that an O rescale can wait for the previous block's
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -313,6 +314,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ptx::mbar_init(&bars->kv_full[i], 1);
       ptx::mbar_init(&bars->kv_empty[i], 1);
     }
+    ptx::mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -372,7 +374,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (nx.nkv > 0) ptx::tma_prefetch_l2_4d(&map_q, hf * 64, nx.h, nx.qrow + nx.q0 + t * kBM, nx.b);
           }
           // first K/V block of this item may be fetched while the previous item still owns the Q buffers
-          ok = load_kv(w, 0, false) && load_kv(w, 0, true);
+          // (one tile per item: the MMA warp consumes K(0), K(1), V(0), K(2), V(1), ..., and the ring follows that order)
+          if constexpr (C::kTiles == 1) ok = load_kv(w, 0, false) && (w.nkv == 1 || load_kv(w, 1, false));
+          else ok = load_kv(w, 0, false) && load_kv(w, 0, true);
           if (!ok) break;
           const int qb = n_item % C::kQBufs, quse = n_item / C::kQBufs;
           if (quse > 0 && !ptx::mbar_wait(&bars->q_empty[qb], (quse - 1) & 1, abort_flag)) {
@@ -387,7 +391,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int hf = 0; hf < C::kHalves; ++hf)
               ptx::tma_load_4d(base_ptr + (qb * C::kTiles + t) * C::kTileBytes + hf * kHalfBytes, &map_q, &bars->q_full[qb], hf * 64,
                                w.h, w.qrow + w.q0 + t * kBM, w.b);
-          for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
+          if constexpr (C::kTiles == 1) {
+            for (int j = 0; j < w.nkv && ok; ++j) ok = load_kv(w, j, true) && (j + 2 >= w.nkv || load_kv(w, j + 2, false));
+          } else {
+            for (int j = 1; j < w.nkv && ok; ++j) ok = load_kv(w, j, false) && load_kv(w, j, true);
+          }
         }
       }
     } else if (warp == 1) {
@@ -424,6 +432,56 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int qb = n_item % C::kQBufs;
           const uint64_t qd0 = qd_base + (uint64_t)(qb * C::kTiles * (C::kTileBytes >> 4));
           const uint64_t qd1 = qd0 + (uint64_t)(C::kTileBytes >> 4);
+          if constexpr (C::kTiles == 1) {
+            // One tile per item (D = 256): S is double-buffered in TMEM (the columns a second tile would use), so that
+            // Q K(j+1)^T and P V(j-1) run while the softmax works on block j.  Order on the tensor pipe:
+            // QK(0) QK(1) | PV(0) QK(2) | PV(1) QK(3) | ...
+            if (!ptx::mbar_wait(&bars->q_full[qb], (n_item / C::kQBufs) & 1, abort_flag)) {
+              fail(1u);
+              break;
+            }
+            auto qk = [&](int i) -> bool {  // S[i & 1] = Q K(i)^T from the ring's next slot
+              if (!ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {
+                fail(1u);
+                return false;
+              }
+              ptx::tc_fence_after();
+              issue_qk<D>((i & 1) ? s1 : s0, qd0, ring_k + (uint64_t)(slot * (C::kTileBytes >> 4)), idesc_qk);
+              ptx::tc_commit(&bars->s_full[i & 1]);
+              ptx::tc_commit(&bars->kv_empty[slot]);
+              if (i == w.nkv - 1) ptx::tc_commit(&bars->q_empty[qb]);  // Q is no longer needed: the next item may load its own
+              advance();
+              return true;
+            };
+            if (!qk(0) || (w.nkv > 1 && !qk(1))) break;
+            for (int j = 0; j < w.nkv && ok; ++j) {
+              const int b = j & 1;
+              const uint32_t sb = b ? s1 : s0;
+              uint32_t& pph = b ? pph1 : pph0;
+              const int valid = max(16, min(kBN, w.sk - (w.j0 + j) * kBN));
+              const int ksteps = (valid + 15) >> 4;
+              const int k_mid = min(ksteps, 4);
+              if (!ptx::mbar_wait(&bars->kv_full[slot], par, abort_flag)) {  // V(j)
+                fail(1u);
+                break;
+              }
+              const int slot_v = slot;
+              const uint64_t vd = ring_v + (uint64_t)(slot_v * (C::kTileBytes >> 4));
+              advance();
+              if (!ptx::mbar_wait(&bars->p_half[b][0], pph, abort_flag)) { fail(4u); break; }
+              ptx::tc_fence_after();
+              issue_pv(o0, sb, vd, idesc_pv, j > 0 ? 1u : 0u, 0, k_mid);
+              if (!ptx::mbar_wait(&bars->p_half[b][1], pph, abort_flag)) { fail(4u); break; }
+              pph ^= 1;
+              ptx::tc_fence_after();
+              issue_pv(o0, sb, vd, idesc_pv, 1u, k_mid, ksteps);
+              ptx::tc_commit(&bars->kv_empty[slot_v]);
+              ptx::tc_commit(&bars->pv_done);
+              if (j + 2 < w.nkv && !qk(j + 2)) break;  // overwrites the S / P columns the P V above has just read
+              if (j + 1 == w.nkv) ptx::tc_commit(&bars->o_full[0]);
+            }
+            continue;
+          }
           // ---- S_t(0) = Q_t K(0)^T ----
           stamp(a, 16 * n_item + 5);
           if (!ptx::mbar_wait(&bars->q_full[qb], (n_item / C::kQBufs) & 1, abort_flag)) {
@@ -510,14 +568,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int t = (warp - 4) >> 2;  // tile
     const int row_in_tile = ((warp & 3) << 5) + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) << 5) << 16;
-    const uint32_t t_s = tmem + (t ? C::kColS1 : C::kColS0) + lane_addr;
+    uint32_t t_s = tmem + (t ? C::kColS1 : C::kColS0) + lane_addr;  // (one tile per item: S alternates between the two)
     const uint32_t t_o = tmem + (t ? C::kColO1 : C::kColO0) + lane_addr;
-    uint32_t sph = 0, oph = 0;  // phases of s_full[t] / o_full[t], continue across items
+    uint32_t sph = 0, sph_b = 0, oph = 0;  // phases of s_full[] / o_full[t], continue across items
     bool ok = true;
 #ifdef DT_BRINGUP
     bool first_dump = true;
 #endif
     int n_item = 0;
+    uint32_t n_blocks = 0;  // K/V blocks this warpgroup has handed over so far, over all items (one tile per item)
     const bool probe = (warp == 4 && lane == 0);
 
     for (int item = blockIdx.x; item < a.n_slots && ok; item += gridDim.x) {
@@ -583,13 +642,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mask_prefetch(0, 1, flags_cur);
           }
         }
-        if (!DT_OPT(16) && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[t], sph, abort_flag))) {
+        // S buffer of this block: the tile's own, or (one tile per item) the two buffers in turn
+        const int sb = C::kTiles == 1 ? (j & 1) : t;
+        if constexpr (C::kTiles == 1) t_s = tmem + (sb ? C::kColS1 : C::kColS0) + lane_addr;
+        uint32_t& sph_cur = (C::kTiles == 1 && sb) ? sph_b : sph;
+        if (!DT_OPT(16) && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars->s_full[sb], sph_cur, abort_flag))) {
           atomicCAS(a.status, 0u, 3u);
           *abort_flag = 1;
           ok = false;
           break;
         }
-        sph ^= 1;
+        sph_cur ^= 1;
         if (probe && j == 0) stamp(a, 16 * n_item + 8);
         ptx::tc_fence_after();
         uint32_t s[4][32];
@@ -716,6 +779,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           l *= alpha;
           m_used = m_new;
           if (j > 0) {
+            if constexpr (C::kTiles == 1) {
+              // With S double-buffered this block's scores arrive before the previous block's P V has run: O may only
+              // be touched once that one has retired.  (It cannot be more than one phase behind: the P V of this block
+              // waits for the P written below.)
+              if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars->pv_done, (n_blocks - 1) & 1u, abort_flag))) {
+                atomicCAS(a.status, 0u, 7u);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              ptx::tc_fence_after();
+            }
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t ov[32];
@@ -764,7 +839,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ptx::tc_wait_st();
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&bars->p_half[t][c >> 1]);
+            if (lane == 0) ptx::mbar_arrive(&bars->p_half[sb][c >> 1]);
             if (probe && j == 0) stamp(a, 16 * n_item + 14 + (c >> 1));
           }
         }
@@ -774,6 +849,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ptx::unpack_f32x2(ptx::add_f32x2(lsum[2], lsum[3]), b0, b1);
           l += (a0 + a1) + (b0 + b1);
         }
+        ++n_blocks;
       }
       if (!ok) break;
       if (probe) stamp(a, 16 * n_item + 9);

@@ -250,6 +250,19 @@ def test_prefill_large_magnitude_scores(dtattn):
     check(out, oracle(q, k, v, 1.0), torch.bfloat16, "large scores")
 
 
+def test_prefill_large_magnitude_scores_head_dim_256(dtattn):
+    """The same at head dim 256, where S is double-buffered and a block's scores arrive before the previous block's
+    P*V has run: the O rescale has to wait for that P*V.  Many rows, several heads and a causal variant, so that the
+    rescale happens in most blocks of most tiles."""
+    B, S, H, D = 1, 1280, 4, 256
+    q, k, v = inputs(B, S, S, H, H, D, torch.bfloat16, 63)
+    ramp = torch.linspace(0.1, 2.0, S).view(1, S, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    for causal in (False, True):
+        out = run(dtattn, q, k, v, 0.5, causal)     # scores of magnitude up to ~ 250: the row max rises block after block
+        check(out, oracle(q, k, v, 0.5, causal), torch.bfloat16, f"large scores d256 causal={causal}")
+
+
 def test_prefill_strided_views(dtattn):
     """Row-offset and batch-strided views are honoured without a copy (Flux1.swift:236-243, UNet.swift:334-344)."""
     B, S, H, D, dtype = 2, 300, 2, 128, torch.bfloat16
