@@ -50,7 +50,9 @@ template <int D, bool kMask = false>
 struct Cfg {
   // Query tiles per work item.  TMEM (512 columns) holds S (128 columns) and O (D columns) of two tiles up to
   // D = 128; at D = 256 it holds one tile, whose softmax is run by the first softmax warpgroup alone (the second
-  // one idles): per key block that tile has twice the tensor-core work of a D = 128 tile under the same softmax.
+  // one idles), and the columns of the second tile's S hold a second S buffer of the same tile: the tensor pipe runs
+  // P V(j-1) and Q K(j+1)^T while the softmax works on block j (per key block that tile has twice the tensor-core
+  // work of a D = 128 tile under the same softmax, so one warpgroup keeps up).
   static constexpr int kTiles = D == 256 ? 1 : 2;
   static constexpr int kSoftmaxWarps = 4 * kTiles;
   static constexpr int kHalves = D / 64;
