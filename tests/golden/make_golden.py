@@ -23,6 +23,9 @@ CASES = [
     dict(B=2, Sq=1, Sk=515, Hq=8, Hkv=2, D=128, causal=True, seed=130),     # GQA decode
     dict(B=1, Sq=4, Sk=130, Hq=8, Hkv=2, D=128, causal=True, seed=140),     # multi-token verify over a cache
     dict(B=1, Sq=96, Sk=96, Hq=2, Hkv=1, D=64, causal=True, seed=150),      # causal prefill
+    dict(B=1, Sq=200, Sk=200, Hq=3, Hkv=3, D=256, causal=False, seed=160),  # AuraFlow joint attention head dim, shrunk
+    dict(B=1, Sq=150, Sk=280, Hq=4, Hkv=1, D=256, causal=True, seed=170),   # Qwen3.5 prompt continuation: D = 256, grouped heads
+    dict(B=2, Sq=70, Sk=70, Hq=2, Hkv=2, D=160, causal=False, seed=180),    # SD1.5 deepest blocks' head dim
 ]
 
 
