@@ -13,7 +13,7 @@
 // shared-memory tile (fp32, odd row pitch): lane j owns key j of the tile for Q.K^T, then head dims {lane, lane + 32,
 // ...} for P.V.  No tensor cores yet: the decode step of the reference's model (one token, 128 + 512 keys) is a few
 // microseconds of work, long prefills are not tuned.
-#include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace dt {
 namespace {
@@ -166,6 +166,343 @@ sparse_indexed_kernel(const SparseArgs a) {
   if (a.lse && lane == 0) a.lse[((int64_t)b * a.Hq + h) * a.Sq + i] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core variant (mma.sync m16n8k16, fp32 accumulate) for 16-bit tensors whose head dim is a multiple of 64 and
+// whose rows are 16-byte aligned: the reference's shape (64 heads over one KV head, dim 512) is a [heads x keys x dim]
+// matrix product per token, and the decode step needs the token's keys spread over several CTAs.
+//
+// One CTA = one token x 16 query heads of one KV head x one share of the token's keys; 4 warps.  Keys are gathered 32 at
+// a time into shared memory (16-byte pieces, 16-bit, row pitch D + 8 so that ldmatrix rows fall on distinct banks).
+// S = Q K^T: warp w takes keys 8 w .. 8 w + 7 of the tile over the whole head dim (one n-tile, D / 16 k-steps; Q and K
+// fragments by ldmatrix).  The row maxima of the four warps meet in shared memory, every warp then holds the tile's
+// maximum, exponentiates its 8 keys and writes them as 16-bit P into a [16 x 32] exchange tile.  O += P V: warp w owns
+// head dims [w D / 4, (w + 1) D / 4) (D / 32 n-tiles of fp32 accumulators), P by ldmatrix, V by ldmatrix.trans.
+// With more than one share per token the CTAs of a token form a thread-block cluster: each leaves (m, l, O) in its
+// shared memory and CTA r of the cluster combines and stores columns [r D / n, (r + 1) D / n) of the 16 rows from all
+// of them through distributed shared memory (ordinary ld.shared::cluster loads).
+constexpr int kMmaThreads = 128;
+constexpr int kMmaKeys = 32;
+constexpr int kMmaMaxSplit = 8;
+
+struct SparseMmaExtra {
+  int n_split;   // CTAs (= cluster size) per token and head group
+  int same_kv;   // values are the keys (one gathered tile serves both)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kMmaThreads)
+sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = a.D, P = D + 8;  // row pitch in elements
+  uint16_t* Qs = reinterpret_cast<uint16_t*>(smem_raw);   // [16][P]
+  uint16_t* Ks = Qs + 16 * P;                              // [32][P]
+  uint16_t* Vs = x.same_kv ? Ks : Ks + kMmaKeys * P;       // [32][P]
+  uint16_t* Pex = Ks + (x.same_kv ? 1 : 2) * kMmaKeys * P;  // [16][40]
+  float* mxs = reinterpret_cast<float*>(Pex + 16 * 40);    // [4][16] row maxima, one set per warp
+  float* ls = mxs + 64;                                    // [4][16] row sums
+  int* codes = reinterpret_cast<int*>(ls + 64);            // [32]
+  // after the key loop the K tile's storage holds this CTA's partial result: O [16][D] fp32, then m [16], l [16]
+  float* Opart = reinterpret_cast<float*>(Ks);
+  float* mpart = ls + 64 + 32;                             // behind codes
+  float* lpart = mpart + 16;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+  const int i = blockIdx.x / x.n_split, split = blockIdx.x % x.n_split, b = blockIdx.z;
+  const int G = a.Hq / a.Hkv;
+  const int ng = (G + 15) / 16;
+  const int kvh = blockIdx.y / ng, hg = blockIdx.y - kvh * ng;
+  const int h0 = kvh * G + hg * 16;
+  const int nh = min(16, G - hg * 16);  // query heads in this group (rows beyond them hold zeros)
+  const int chunks = D / 8;             // 16-byte pieces per row
+
+  {
+    const T* q = reinterpret_cast<const T*>(a.q) + b * a.q_sb + (int64_t)i * a.q_ss;
+    for (int c = tid; c < 16 * chunks; c += kMmaThreads) {
+      const int r = c / chunks, ch = c - r * chunks;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < nh) v = *reinterpret_cast<const uint4*>(q + (int64_t)(h0 + r) * a.q_sh + ch * 8);
+      *reinterpret_cast<uint4*>(Qs + r * P + ch * 8) = v;
+    }
+  }
+
+  const long long last = a.is_causal ? (long long)i + (a.Sr - a.Sq) : (long long)a.Sr - 1;
+  long long first = a.window > 0 ? (long long)i + (a.Sr - a.Sq) - a.window + 1 : 0;
+  if (first < 0) first = 0;
+  const long long last_c = last < (long long)a.Sr - 1 ? last : (long long)a.Sr - 1;
+  const int n_raw = last_c >= first ? (int)(last_c - first + 1) : 0;
+  const int n_keys = n_raw + (a.Sc > 0 ? a.n_sel : 0);
+  const int32_t* sel = a.selected ? a.selected + b * a.sel_sb + (int64_t)i * a.sel_sq : nullptr;
+  const int n_tiles = (n_keys + kMmaKeys - 1) / kMmaKeys;
+  const int per = (n_tiles + x.n_split - 1) / x.n_split;
+  const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
+
+  const T* kr = reinterpret_cast<const T*>(a.k_raw) + b * a.kr_sb + kvh * a.kr_sh;
+  const T* vr = reinterpret_cast<const T*>(a.v_raw) + b * a.vr_sb + kvh * a.vr_sh;
+  const T* kc = reinterpret_cast<const T*>(a.k_comp) + b * a.kc_sb + kvh * a.kc_sh;
+  const T* vc = reinterpret_cast<const T*>(a.v_comp) + b * a.vc_sb + kvh * a.vc_sh;
+
+  const int Dq = D / 4, ntl = Dq / 8;  // this warp's head dims and its n-tiles of 8 (D = 512: 16)
+  const int dim0 = warp * Dq;
+  float acc[16][4];
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+  float m_row[2] = {-INFINITY, -INFINITY};  // rows g and g + 8: the same in all four warps
+  float l_lane[2] = {0.f, 0.f};             // this lane's share of the row sums (its two keys of every tile)
+
+  const uint32_t qs_addr = ptx::smem_u32(Qs) + (uint32_t)(((lane & 15) * P + (lane >> 4) * 8) * 2);
+  const uint32_t ks_addr = ptx::smem_u32(Ks) + (uint32_t)(((8 * warp + (lane & 7)) * P + (lane >> 3) * 8) * 2);
+  const uint32_t pex_addr = ptx::smem_u32(Pex) + (uint32_t)(((lane & 15) * 40 + (lane >> 4) * 8) * 2);
+  const uint32_t vs_addr = ptx::smem_u32(Vs) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * P + dim0 + (lane >> 4) * 8) * 2);
+
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    __syncthreads();  // the previous tile is used up (and Q is in place)
+    if (tid < kMmaKeys) {
+      const int vkey = tile * kMmaKeys + tid;
+      int code = -1;  // -1: no key; >= 0: raw row; <= -2: compressed row -(code + 2)
+      if (vkey < n_raw) {
+        code = (int)(first + vkey);
+      } else if (vkey < n_keys) {
+        const int idx = sel[vkey - n_raw];
+        if (idx >= 0 && idx < a.Sc) code = -(idx + 2);
+      }
+      codes[tid] = code;
+    }
+    __syncthreads();
+    for (int c = tid; c < kMmaKeys * chunks; c += kMmaThreads) {
+      const int r = c / chunks, ch = c - r * chunks;
+      const int code = codes[r];
+      uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = kv;
+      if (code >= 0) {
+        kv = *reinterpret_cast<const uint4*>(kr + (int64_t)code * a.kr_ss + ch * 8);
+        if (!x.same_kv) vv = *reinterpret_cast<const uint4*>(vr + (int64_t)code * a.vr_ss + ch * 8);
+      } else if (code <= -2) {
+        const int row = -(code + 2);
+        kv = *reinterpret_cast<const uint4*>(kc + (int64_t)row * a.kc_ss + ch * 8);
+        if (!x.same_kv) vv = *reinterpret_cast<const uint4*>(vc + (int64_t)row * a.vc_ss + ch * 8);
+      }
+      *reinterpret_cast<uint4*>(Ks + r * P + ch * 8) = kv;
+      if (!x.same_kv) *reinterpret_cast<uint4*>(Vs + r * P + ch * 8) = vv;
+    }
+    __syncthreads();
+
+    // ---- scores of this warp's 8 keys, all 16 heads, the whole head dim ----
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      uint32_t a0[4], a1[4], b0, b1, b2, b3;
+      ptx::ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], qs_addr + (uint32_t)(ks * 32));
+      ptx::ldmatrix_x4(a1[0], a1[1], a1[2], a1[3], qs_addr + (uint32_t)(ks * 32 + 32));
+      ptx::ldmatrix_x4(b0, b1, b2, b3, ks_addr + (uint32_t)(ks * 32));
+      ptx::mma_m16n8k16<kBf16>(sc, a0, b0, b1);
+      ptx::mma_m16n8k16<kBf16>(sc, a1, b2, b3);
+    }
+    const bool v0 = codes[8 * warp + 2 * tg] != -1, v1 = codes[8 * warp + 2 * tg + 1] != -1;
+    float s00 = v0 ? sc[0] * a.scale_log2 : -INFINITY, s01 = v1 ? sc[1] * a.scale_log2 : -INFINITY;  // row g
+    float s10 = v0 ? sc[2] * a.scale_log2 : -INFINITY, s11 = v1 ? sc[3] * a.scale_log2 : -INFINITY;  // row g + 8
+    float mx0 = fmaxf(s00, s01), mx1 = fmaxf(s10, s11);
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (tg == 0) {
+      mxs[warp * 16 + g] = mx0;
+      mxs[warp * 16 + g + 8] = mx1;
+    }
+    __syncthreads();
+    const float mt0 = fmaxf(fmaxf(mxs[g], mxs[16 + g]), fmaxf(mxs[32 + g], mxs[48 + g]));
+    const float mt1 = fmaxf(fmaxf(mxs[g + 8], mxs[24 + g]), fmaxf(mxs[40 + g], mxs[56 + g]));
+    const float mn0 = fmaxf(m_row[0], mt0), mn1 = fmaxf(m_row[1], mt1);
+    const float al0 = mn0 == -INFINITY ? 1.f : exp2f(m_row[0] - mn0), al1 = mn1 == -INFINITY ? 1.f : exp2f(m_row[1] - mn1);
+    const float p00 = mn0 == -INFINITY ? 0.f : exp2f(s00 - mn0), p01 = mn0 == -INFINITY ? 0.f : exp2f(s01 - mn0);
+    const float p10 = mn1 == -INFINITY ? 0.f : exp2f(s10 - mn1), p11 = mn1 == -INFINITY ? 0.f : exp2f(s11 - mn1);
+    l_lane[0] = l_lane[0] * al0 + (p00 + p01);
+    l_lane[1] = l_lane[1] * al1 + (p10 + p11);
+    m_row[0] = mn0;
+    m_row[1] = mn1;
+    {
+      uint32_t w0, w1;
+      if constexpr (kBf16) {
+        w0 = ptx::cvt_pack_bf16(p00, p01);
+        w1 = ptx::cvt_pack_bf16(p10, p11);
+      } else {
+        w0 = ptx::cvt_pack_f16(p00, p01);
+        w1 = ptx::cvt_pack_f16(p10, p11);
+      }
+      *reinterpret_cast<uint32_t*>(Pex + g * 40 + 8 * warp + 2 * tg) = w0;
+      *reinterpret_cast<uint32_t*>(Pex + (g + 8) * 40 + 8 * warp + 2 * tg) = w1;
+    }
+    __syncthreads();
+
+    // ---- O += P V over this warp's head dims ----
+    uint32_t pa0[4], pa1[4];
+    ptx::ldmatrix_x4(pa0[0], pa0[1], pa0[2], pa0[3], pex_addr);
+    ptx::ldmatrix_x4(pa1[0], pa1[1], pa1[2], pa1[3], pex_addr + 32);
+#pragma unroll
+    for (int nt = 0; nt < 16; nt += 2) {
+      if (nt < ntl) {
+        acc[nt][0] *= al0; acc[nt][1] *= al0; acc[nt][2] *= al1; acc[nt][3] *= al1;
+        acc[nt + 1][0] *= al0; acc[nt + 1][1] *= al0; acc[nt + 1][2] *= al1; acc[nt + 1][3] *= al1;
+        uint32_t b0, b1, b2, b3;
+        ptx::ldmatrix_x4_trans(b0, b1, b2, b3, vs_addr + (uint32_t)(nt * 16));
+        ptx::mma_m16n8k16<kBf16>(acc[nt], pa0, b0, b1);
+        ptx::mma_m16n8k16<kBf16>(acc[nt + 1], pa0, b2, b3);
+        ptx::ldmatrix_x4_trans(b0, b1, b2, b3, vs_addr + (uint32_t)(nt * 16 + 16 * P * 2));
+        ptx::mma_m16n8k16<kBf16>(acc[nt], pa1, b0, b1);
+        ptx::mma_m16n8k16<kBf16>(acc[nt + 1], pa1, b2, b3);
+      }
+    }
+  }
+
+  // ---- row sums over the four warps' keys ----
+  float l0 = l_lane[0], l1 = l_lane[1];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();  // the last tile is used up: Ks may be overwritten below
+  if (tg == 0) {
+    ls[warp * 16 + g] = l0;
+    ls[warp * 16 + g + 8] = l1;
+  }
+  __syncthreads();
+  l0 = (ls[g] + ls[16 + g]) + (ls[32 + g] + ls[48 + g]);
+  l1 = (ls[g + 8] + ls[24 + g]) + (ls[40 + g] + ls[56 + g]);
+
+  const T* sinks = reinterpret_cast<const T*>(a.sinks);
+  T* obase = reinterpret_cast<T*>(a.o) + b * a.o_sb + (int64_t)i * a.o_ss;
+  if (x.n_split == 1) {
+    float inv[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      float m = m_row[r], l = r ? l1 : l0, alpha = 1.f;
+      if (sinks && row < nh) {  // one more score column without a value row
+        const float sl = to_float(sinks[h0 + row]) * kLog2e;
+        const float m_f = fmaxf(m, sl);
+        alpha = exp2f(m - m_f);
+        l = l * alpha + exp2f(sl - m_f);
+        m = m_f;
+      }
+      inv[r] = l > 0.f ? alpha / l : 0.f;
+      if (a.lse && warp == 0 && tg == 0 && row < nh)
+        a.lse[((int64_t)b * a.Hq + h0 + row) * a.Sq + i] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      if (nt < ntl) {
+        const int col = dim0 + nt * 8 + 2 * tg;
+        uint32_t w0, w1;
+        if constexpr (kBf16) {
+          w0 = ptx::cvt_pack_bf16(acc[nt][0] * inv[0], acc[nt][1] * inv[0]);
+          w1 = ptx::cvt_pack_bf16(acc[nt][2] * inv[1], acc[nt][3] * inv[1]);
+        } else {
+          w0 = ptx::cvt_pack_f16(acc[nt][0] * inv[0], acc[nt][1] * inv[0]);
+          w1 = ptx::cvt_pack_f16(acc[nt][2] * inv[1], acc[nt][3] * inv[1]);
+        }
+        if (g < nh) *reinterpret_cast<uint32_t*>(obase + (int64_t)(h0 + g) * a.o_sh + col) = w0;
+        if (g + 8 < nh) *reinterpret_cast<uint32_t*>(obase + (int64_t)(h0 + g + 8) * a.o_sh + col) = w1;
+      }
+    }
+    return;
+  }
+
+  // ---- several CTAs per token: partial results to shared memory, combined over the cluster ----
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) {
+    if (nt < ntl) {
+      const int col = dim0 + nt * 8 + 2 * tg;
+      *reinterpret_cast<float2*>(Opart + g * D + col) = make_float2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<float2*>(Opart + (g + 8) * D + col) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+  }
+  if (warp == 0 && tg == 0) {
+    mpart[g] = m_row[0];
+    mpart[g + 8] = m_row[1];
+    lpart[g] = l0;
+    lpart[g + 8] = l1;
+  }
+  ptx::cluster_sync();  // every CTA of the token has written its partial result
+  {
+    const uint32_t rank = ptx::cluster_ctarank();
+    const int cols = D / x.n_split;  // this CTA's share of the columns (D is a multiple of 64, n_split <= 8)
+    const uint32_t o_loc = ptx::smem_u32(Opart), m_loc = ptx::smem_u32(mpart), l_loc = ptx::smem_u32(lpart);
+    for (int e = tid; e < 16 * cols; e += kMmaThreads) {
+      const int row = e / cols, col = (int)rank * cols + (e - row * cols);
+      float ms[kMmaMaxSplit];
+      float m = -INFINITY;
+      for (int sIdx = 0; sIdx < x.n_split; ++sIdx) {
+        ms[sIdx] = ptx::ld_cluster_f32(ptx::map_to_cta(m_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
+        m = fmaxf(m, ms[sIdx]);
+      }
+      float sl = -INFINITY;
+      if (sinks && row < nh) sl = to_float(sinks[h0 + row]) * kLog2e;
+      const float m_f = fmaxf(m, sl);
+      float l = (sl == -INFINITY) ? 0.f : exp2f(sl - m_f);  // the sink: a score without a value row
+      float o = 0.f;
+      for (int sIdx = 0; sIdx < x.n_split; ++sIdx) {
+        const float wgt = ms[sIdx] == -INFINITY ? 0.f : exp2f(ms[sIdx] - m_f);
+        l += wgt * ptx::ld_cluster_f32(ptx::map_to_cta(l_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
+        o += wgt * ptx::ld_cluster_f32(ptx::map_to_cta(o_loc + (uint32_t)(row * D + col) * 4u, (uint32_t)sIdx));
+      }
+      if (row < nh) {
+        obase[(int64_t)(h0 + row) * a.o_sh + col] = from_float<T>(l > 0.f ? o / l : 0.f);
+        if (a.lse && col == 0) a.lse[((int64_t)b * a.Hq + h0 + row) * a.Sq + i] = l > 0.f ? m_f * kLn2 + logf(l) : -INFINITY;
+      }
+    }
+  }
+  ptx::cluster_sync();  // nobody leaves while its shared memory is still being read
+}
+
+// What the tensor-core variant needs: 16-bit tensors, head dim a multiple of 64, every row it gathers 16-byte aligned.
+bool sparse_mma_supported(const dt_sparse_indexed_params& p) {
+  if (p.dtype != DT_F16 && p.dtype != DT_BF16) return false;
+  if (p.D % 64 || p.D > 512) return false;
+  auto ok = [](const dt_tensor4& t) {
+    return t.ptr == nullptr || (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0 && t.stride_b % 8 == 0 && t.stride_s % 8 == 0 &&
+                                t.stride_h % 8 == 0);
+  };
+  return ok(p.q) && ok(p.o) && ok(p.k_raw) && ok(p.v_raw) && ok(p.k_comp) && ok(p.v_comp);
+}
+
+template <typename T>
+int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, cudaStream_t stream) {
+  auto same = [](const dt_tensor4& u, const dt_tensor4& v) {
+    return u.ptr == v.ptr && u.stride_b == v.stride_b && u.stride_s == v.stride_s && u.stride_h == v.stride_h;
+  };
+  SparseMmaExtra x{};
+  x.same_kv = same(p.k_raw, p.v_raw) && (p.Sc == 0 || p.n_selected == 0 || same(p.k_comp, p.v_comp));
+  const int G = p.Hq / p.Hkv, ng = (G + 15) / 16;
+  const long long ctas = (long long)p.Sq * ng * p.Hkv * p.B;
+  // few tokens (the decode step): a token's keys are shared out over a cluster of CTAs, as long as every CTA still gets
+  // a few tiles and the grid stays within about two rounds over the SMs
+  const int keys = (p.sliding_window > 0 ? (p.sliding_window < p.Sr ? p.sliding_window : p.Sr) : p.Sr) + (p.Sc > 0 ? p.n_selected : 0);
+  const int tiles = (keys + kMmaKeys - 1) / kMmaKeys;
+  int split = 1;
+  const int sms = device_sm_count();
+  while (split < kMmaMaxSplit && ctas * (split * 2) <= 2LL * sms && tiles >= 2 * (split * 2)) split *= 2;
+  x.n_split = split;
+  const int P = p.D + 8;
+  const size_t smem = 2 * ((size_t)16 * P + (size_t)(x.same_kv ? 1 : 2) * kMmaKeys * P + 16 * 40) + 4 * (64 + 64 + 32 + 16 + 16);
+  auto kern = sparse_mma_kernel<T>;
+  if (smem > 48 * 1024) DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.Sq * split), (unsigned)(p.Hkv * ng), (unsigned)p.B);
+  cfg.blockDim = dim3(kMmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = split > 1 ? 1 : 0;
+  DT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, x));
+  return DT_OK;
+}
+
 template <typename T>
 int launch_sparse_t(const dt_sparse_indexed_params& p, cudaStream_t stream) {
   SparseArgs a{};
@@ -187,6 +524,9 @@ int launch_sparse_t(const dt_sparse_indexed_params& p, cudaStream_t stream) {
   a.scale_log2 = p.scale * kLog2e;
   a.is_causal = p.is_causal;
   a.window = p.sliding_window;
+  if constexpr (!std::is_same<T, float>::value) {
+    if (sparse_mma_supported(p) && !(p.flags & DT_FLAG_FORCE_GENERIC)) return launch_sparse_mma_t<T>(p, a, stream);
+  }
   const size_t smem = sizeof(float) * ((size_t)hpc * p.D + (size_t)kTileKeys * (p.D | 1) + (size_t)kTileKeys * p.D);
   auto kern = sparse_indexed_kernel<T>;
   if (smem > 48 * 1024) DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -80,7 +80,7 @@ class SparseIndexedParams(ctypes.Structure):
                 ("sliding_window", ctypes.c_int32),
                 ("q", Tensor4), ("o", Tensor4), ("k_raw", Tensor4), ("v_raw", Tensor4), ("k_comp", Tensor4), ("v_comp", Tensor4),
                 ("selected", ctypes.c_void_p), ("selected_stride_b", ctypes.c_int64), ("selected_stride_q", ctypes.c_int64),
-                ("sinks", ctypes.c_void_p), ("lse", ctypes.c_void_p)]
+                ("sinks", ctypes.c_void_p), ("lse", ctypes.c_void_p), ("flags", ctypes.c_uint32)]
 
 
 class DtError(RuntimeError):
@@ -376,7 +376,7 @@ def sdpa_forward_projected(q, k, v, scale, weight, bias=None, is_causal=False, o
 
 
 def sparse_indexed_attention(q, k_raw, v_raw, k_comp, v_comp, selected, scale, sinks=None, sliding_window=0,
-                             is_causal=True, out=None, lse=None, stream=None):
+                             is_causal=True, out=None, lse=None, stream=None, flags=0):
     """SparseIndexedAttention (DeepSeek4.swift:521-545): q [B,Sq,Hq,D] over its sliding causal window of the raw rows
     k_raw / v_raw [B,Sr,Hkv,D] and over the rows of k_comp / v_comp [B,Sc,Hkv,D] (None when there are none) that
     `selected` (int32 [B or 1, Sq, n_selected]; entries outside [0, Sc) mean "no row") names, in one softmax with the
@@ -393,6 +393,7 @@ def sparse_indexed_attention(q, k_raw, v_raw, k_comp, v_comp, selected, scale, s
     p.scale = float(scale)
     p.is_causal = int(bool(is_causal))
     p.sliding_window = int(sliding_window)
+    p.flags = int(flags)
     p.q, p.o, p.k_raw, p.v_raw = _view4(q), _view4(out), _view4(k_raw), _view4(v_raw)
     if k_comp is not None and p.Sc > 0:
         p.k_comp, p.v_comp = _view4(k_comp), _view4(v_comp)

@@ -231,8 +231,11 @@ int dt_qk_prologue(const dt_qk_prologue_params* q, const dt_qk_prologue_params* 
  * whole batch): an entry outside [0, Sc) means "no row", a row listed twice counts twice; sinks: [Hq] in the tensors'
  * dtype or NULL; lse: optional fp32 [B, Hq, Sq].  The reference's model uses one shared KV head for 64 query heads of
  * dim 512 with the same tensor as keys and values; here keys and values are separate views (pass the same pointer
- * twice for that layout), D <= 512, fp16 / bf16 / fp32.  The arithmetic of the reference's operator is in its absent
- * back end: "no row" for out-of-range entries and duplicates counting twice are this library's definition.
+ * twice for that layout: the gathered rows then serve as both), D <= 512, fp16 / bf16 / fp32.  16-bit tensors with D a
+ * multiple of 64 and 16-byte aligned rows run on the tensor cores (a token's keys are shared out over a cluster of CTAs
+ * when there are few tokens, i.e. in the decode step); everything else on a CUDA-core kernel.  The arithmetic of the
+ * reference's operator is in its absent back end: "no row" for out-of-range entries and duplicates counting twice are
+ * this library's definition.
  */
 typedef struct {
   int32_t B, Sq, Hq, Hkv, D;
@@ -246,6 +249,7 @@ typedef struct {
   int64_t selected_stride_b, selected_stride_q;
   const void* sinks;
   float* lse;
+  uint32_t flags; /* DT_FLAG_FORCE_GENERIC: the CUDA-core kernel instead of the tensor-core one */
 } dt_sparse_indexed_params;
 int dt_sparse_indexed_attention(const dt_sparse_indexed_params* p, void* cuda_stream);
 
