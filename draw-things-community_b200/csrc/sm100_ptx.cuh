@@ -100,6 +100,14 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t cluster_addr) {  // 16-byte aligned
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 
 // ---- TMA ----------------------------------------------------------------------------------------
 

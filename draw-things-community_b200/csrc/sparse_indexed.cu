@@ -180,50 +180,58 @@ sparse_indexed_kernel(const SparseArgs a) {
 // With more than one share per token the CTAs of a token form a thread-block cluster: each leaves (m, l, O) in its
 // shared memory and CTA r of the cluster combines and stores columns [r D / n, (r + 1) D / n) of the 16 rows from all
 // of them through distributed shared memory (ordinary ld.shared::cluster loads).
-constexpr int kMmaThreads = 128;
 constexpr int kMmaKeys = 32;
 constexpr int kMmaMaxSplit = 8;
+constexpr int kMmaMaxGroups = 4;  // head groups of 16 per CTA
 
 struct SparseMmaExtra {
-  int n_split;   // CTAs (= cluster size) per token and head group
+  int n_split;   // CTAs (= cluster size) per token and head group; > 1 only with one head group per CTA
   int same_kv;   // values are the keys (one gathered tile serves both)
+  int gpc;       // head groups of 16 per CTA (4 warps each); they share the gathered tiles
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kMmaThreads)
+__global__ void __launch_bounds__(128 * kMmaMaxGroups)
 sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = a.D, P = D + 8;  // row pitch in elements
-  uint16_t* Qs = reinterpret_cast<uint16_t*>(smem_raw);   // [16][P]
-  uint16_t* Ks = Qs + 16 * P;                              // [32][P]
-  uint16_t* Vs = x.same_kv ? Ks : Ks + kMmaKeys * P;       // [32][P]
-  uint16_t* Pex = Ks + (x.same_kv ? 1 : 2) * kMmaKeys * P;  // [16][40]
-  float* mxs = reinterpret_cast<float*>(Pex + 16 * 40);    // [4][16] row maxima, one set per warp
-  float* ls = mxs + 64;                                    // [4][16] row sums
-  int* codes = reinterpret_cast<int*>(ls + 64);            // [32]
-  // after the key loop the K tile's storage holds this CTA's partial result: O [16][D] fp32, then m [16], l [16]
-  float* Opart = reinterpret_cast<float*>(Ks);
-  float* mpart = ls + 64 + 32;                             // behind codes
-  float* lpart = mpart + 16;
+  const int gpc = x.gpc, nthreads = 128 * gpc;
+  uint16_t* Qs = reinterpret_cast<uint16_t*>(smem_raw);                 // [gpc * 16][P]
+  uint16_t* Kb = Qs + gpc * 16 * P;                                      // [2][32][P]
+  uint16_t* Vb = x.same_kv ? Kb : Kb + 2 * kMmaKeys * P;                 // [2][32][P]
+  uint16_t* Pex = Kb + (x.same_kv ? 2 : 4) * kMmaKeys * P;               // [gpc][16][40]
+  float* mxs = reinterpret_cast<float*>(Pex + gpc * 16 * 40);            // [gpc][4][16] row maxima, one set per warp
+  float* ls = mxs + gpc * 64;                                            // [gpc][4][16] row sums
+  int* codes = reinterpret_cast<int*>(ls + gpc * 64);                    // [2][32]
+  // cluster path (one head group per CTA): after the key loop the first K buffer holds this CTA's partial result
+  float* Opart = reinterpret_cast<float*>(Kb);                           // [16][D] fp32
+  float* mpart = reinterpret_cast<float*>(codes + 64);                   // [16]
+  float* lpart = mpart + 16;                                             // [16]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+  const int gi = warp >> 2, w = warp & 3;  // head group within the CTA, warp within the group
   const int i = blockIdx.x / x.n_split, split = blockIdx.x % x.n_split, b = blockIdx.z;
   const int G = a.Hq / a.Hkv;
-  const int ng = (G + 15) / 16;
-  const int kvh = blockIdx.y / ng, hg = blockIdx.y - kvh * ng;
+  const int ng = (G + 15) / 16, gy = (ng + gpc - 1) / gpc;
+  const int kvh = blockIdx.y / gy;
+  const int hg0 = (blockIdx.y - kvh * gy) * gpc;         // first head group of this CTA
+  const int hg = hg0 + gi;
   const int h0 = kvh * G + hg * 16;
-  const int nh = min(16, G - hg * 16);  // query heads in this group (rows beyond them hold zeros)
-  const int chunks = D / 8;             // 16-byte pieces per row
+  const int nh = hg < ng ? min(16, G - hg * 16) : 0;     // query heads of this warp's group (rows beyond them hold zeros)
+  const int chunks = D / 8;                              // 16-byte pieces per row
 
   {
     const T* q = reinterpret_cast<const T*>(a.q) + b * a.q_sb + (int64_t)i * a.q_ss;
-    for (int c = tid; c < 16 * chunks; c += kMmaThreads) {
+    for (int c = tid; c < gpc * 16 * chunks; c += nthreads) {
       const int r = c / chunks, ch = c - r * chunks;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < nh) v = *reinterpret_cast<const uint4*>(q + (int64_t)(h0 + r) * a.q_sh + ch * 8);
-      *reinterpret_cast<uint4*>(Qs + r * P + ch * 8) = v;
+      const int head = kvh * G + hg0 * 16 + r;  // rows of all groups of the CTA are consecutive heads
+      // asynchronous like the key rows below (the first wait covers both); rows beyond the heads are zero-filled
+      const bool on = hg0 * 16 + r < G;
+      ptx::cp_async_16(ptx::smem_u32(Qs + r * P + ch * 8), on ? (const void*)(q + (int64_t)head * a.q_sh + ch * 8) : (const void*)q,
+                       on ? 16 : 0);
     }
+    ptx::cp_async_commit();
   }
 
   const long long last = a.is_causal ? (long long)i + (a.Sr - a.Sq) : (long long)a.Sr - 1;
@@ -242,53 +250,80 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   const T* kc = reinterpret_cast<const T*>(a.k_comp) + b * a.kc_sb + kvh * a.kc_sh;
   const T* vc = reinterpret_cast<const T*>(a.v_comp) + b * a.vc_sb + kvh * a.vc_sh;
 
-  const int Dq = D / 4, ntl = Dq / 8;  // this warp's head dims and its n-tiles of 8 (D = 512: 16)
-  const int dim0 = warp * Dq;
-  float acc[16][4];
-#pragma unroll
-  for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-  float m_row[2] = {-INFINITY, -INFINITY};  // rows g and g + 8: the same in all four warps
-  float l_lane[2] = {0.f, 0.f};             // this lane's share of the row sums (its two keys of every tile)
-
-  const uint32_t qs_addr = ptx::smem_u32(Qs) + (uint32_t)(((lane & 15) * P + (lane >> 4) * 8) * 2);
-  const uint32_t ks_addr = ptx::smem_u32(Ks) + (uint32_t)(((8 * warp + (lane & 7)) * P + (lane >> 3) * 8) * 2);
-  const uint32_t pex_addr = ptx::smem_u32(Pex) + (uint32_t)(((lane & 15) * 40 + (lane >> 4) * 8) * 2);
-  const uint32_t vs_addr = ptx::smem_u32(Vs) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * P + dim0 + (lane >> 4) * 8) * 2);
-
-  for (int tile = t_begin; tile < t_end; ++tile) {
-    __syncthreads();  // the previous tile is used up (and Q is in place)
+  // which row each of a tile's 32 keys is: -1 no key, >= 0 raw row, <= -2 compressed row -(code + 2)
+  auto set_codes = [&](int tile, int buf) {
     if (tid < kMmaKeys) {
       const int vkey = tile * kMmaKeys + tid;
-      int code = -1;  // -1: no key; >= 0: raw row; <= -2: compressed row -(code + 2)
+      int code = -1;
       if (vkey < n_raw) {
         code = (int)(first + vkey);
       } else if (vkey < n_keys) {
         const int idx = sel[vkey - n_raw];
         if (idx >= 0 && idx < a.Sc) code = -(idx + 2);
       }
-      codes[tid] = code;
+      codes[buf * kMmaKeys + tid] = code;
     }
-    __syncthreads();
-    for (int c = tid; c < kMmaKeys * chunks; c += kMmaThreads) {
+  };
+  // the tile's rows into buffer `buf`: asynchronous 16-byte copies, zero fill where there is no key
+  auto gather = [&](int buf) {
+    const uint32_t kdst = ptx::smem_u32(Kb + buf * kMmaKeys * P), vdst = ptx::smem_u32(Vb + buf * kMmaKeys * P);
+    for (int c = tid; c < kMmaKeys * chunks; c += nthreads) {
       const int r = c / chunks, ch = c - r * chunks;
-      const int code = codes[r];
-      uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = kv;
+      const int code = codes[buf * kMmaKeys + r];
+      const T* ksrc = kr;  // any valid address when nothing is copied
+      const T* vsrc = vr;
+      int nbytes = 0;
       if (code >= 0) {
-        kv = *reinterpret_cast<const uint4*>(kr + (int64_t)code * a.kr_ss + ch * 8);
-        if (!x.same_kv) vv = *reinterpret_cast<const uint4*>(vr + (int64_t)code * a.vr_ss + ch * 8);
+        ksrc = kr + (int64_t)code * a.kr_ss + ch * 8;
+        vsrc = vr + (int64_t)code * a.vr_ss + ch * 8;
+        nbytes = 16;
       } else if (code <= -2) {
         const int row = -(code + 2);
-        kv = *reinterpret_cast<const uint4*>(kc + (int64_t)row * a.kc_ss + ch * 8);
-        if (!x.same_kv) vv = *reinterpret_cast<const uint4*>(vc + (int64_t)row * a.vc_ss + ch * 8);
+        ksrc = kc + (int64_t)row * a.kc_ss + ch * 8;
+        vsrc = vc + (int64_t)row * a.vc_ss + ch * 8;
+        nbytes = 16;
       }
-      *reinterpret_cast<uint4*>(Ks + r * P + ch * 8) = kv;
-      if (!x.same_kv) *reinterpret_cast<uint4*>(Vs + r * P + ch * 8) = vv;
+      const uint32_t off = (uint32_t)((r * P + ch * 8) * 2);
+      ptx::cp_async_16(kdst + off, ksrc, nbytes);
+      if (!x.same_kv) ptx::cp_async_16(vdst + off, vsrc, nbytes);
     }
-    __syncthreads();
+    ptx::cp_async_commit();
+  };
 
-    // ---- scores of this warp's 8 keys, all 16 heads, the whole head dim ----
+  const int Dq = D / 4, ntl = Dq / 8;  // this warp's head dims and its n-tiles of 8 (D = 512: 16)
+  const int dim0 = w * Dq;
+  float acc[16][4];
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+  float m_row[2] = {-INFINITY, -INFINITY};  // rows g and g + 8: the same in the four warps of a group
+  float l_lane[2] = {0.f, 0.f};             // this lane's share of the row sums (its two keys of every tile)
+
+  const uint32_t qs_addr = ptx::smem_u32(Qs) + (uint32_t)(((gi * 16 + (lane & 15)) * P + (lane >> 4) * 8) * 2);
+  const uint32_t ks_off = (uint32_t)(((8 * w + (lane & 7)) * P + (lane >> 3) * 8) * 2);
+  const uint32_t vs_off = (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * P + dim0 + (lane >> 4) * 8) * 2);
+  uint16_t* pex = Pex + gi * 16 * 40;
+  const uint32_t pex_addr = ptx::smem_u32(pex) + (uint32_t)(((lane & 15) * 40 + (lane >> 4) * 8) * 2);
+  float* mx_g = mxs + gi * 64;
+
+  if (t_begin < t_end) {
+    set_codes(t_begin, 0);
+    __syncthreads();
+    gather(0);
+  }
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int cur = (tile - t_begin) & 1;
+    const bool more = tile + 1 < t_end;
+    if (more) set_codes(tile + 1, cur ^ 1);
+    ptx::cp_async_wait<0>();
+    __syncthreads();  // this tile has landed for everybody, the previous tile is used up, the next codes are visible
+    if (more) gather(cur ^ 1);  // travels while this tile is worked on
+    const uint32_t ks_addr = ptx::smem_u32(Kb + cur * kMmaKeys * P) + ks_off;
+    const uint32_t vs_addr = ptx::smem_u32(Vb + cur * kMmaKeys * P) + vs_off;
+    const int* code_cur = codes + cur * kMmaKeys;
+
+    // ---- scores of this warp's 8 keys, the group's 16 heads, the whole head dim ----
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ks = 0; ks < D / 16; ks += 2) {
       uint32_t a0[4], a1[4], b0, b1, b2, b3;
@@ -298,21 +333,21 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
       ptx::mma_m16n8k16<kBf16>(sc, a0, b0, b1);
       ptx::mma_m16n8k16<kBf16>(sc, a1, b2, b3);
     }
-    const bool v0 = codes[8 * warp + 2 * tg] != -1, v1 = codes[8 * warp + 2 * tg + 1] != -1;
-    float s00 = v0 ? sc[0] * a.scale_log2 : -INFINITY, s01 = v1 ? sc[1] * a.scale_log2 : -INFINITY;  // row g
-    float s10 = v0 ? sc[2] * a.scale_log2 : -INFINITY, s11 = v1 ? sc[3] * a.scale_log2 : -INFINITY;  // row g + 8
+    const bool v0 = code_cur[8 * w + 2 * tg] != -1, v1 = code_cur[8 * w + 2 * tg + 1] != -1;
+    const float s00 = v0 ? sc[0] * a.scale_log2 : -INFINITY, s01 = v1 ? sc[1] * a.scale_log2 : -INFINITY;  // row g
+    const float s10 = v0 ? sc[2] * a.scale_log2 : -INFINITY, s11 = v1 ? sc[3] * a.scale_log2 : -INFINITY;  // row g + 8
     float mx0 = fmaxf(s00, s01), mx1 = fmaxf(s10, s11);
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     if (tg == 0) {
-      mxs[warp * 16 + g] = mx0;
-      mxs[warp * 16 + g + 8] = mx1;
+      mx_g[w * 16 + g] = mx0;
+      mx_g[w * 16 + g + 8] = mx1;
     }
     __syncthreads();
-    const float mt0 = fmaxf(fmaxf(mxs[g], mxs[16 + g]), fmaxf(mxs[32 + g], mxs[48 + g]));
-    const float mt1 = fmaxf(fmaxf(mxs[g + 8], mxs[24 + g]), fmaxf(mxs[40 + g], mxs[56 + g]));
+    const float mt0 = fmaxf(fmaxf(mx_g[g], mx_g[16 + g]), fmaxf(mx_g[32 + g], mx_g[48 + g]));
+    const float mt1 = fmaxf(fmaxf(mx_g[g + 8], mx_g[24 + g]), fmaxf(mx_g[40 + g], mx_g[56 + g]));
     const float mn0 = fmaxf(m_row[0], mt0), mn1 = fmaxf(m_row[1], mt1);
     const float al0 = mn0 == -INFINITY ? 1.f : exp2f(m_row[0] - mn0), al1 = mn1 == -INFINITY ? 1.f : exp2f(m_row[1] - mn1);
     const float p00 = mn0 == -INFINITY ? 0.f : exp2f(s00 - mn0), p01 = mn0 == -INFINITY ? 0.f : exp2f(s01 - mn0);
@@ -330,8 +365,8 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
         w0 = ptx::cvt_pack_f16(p00, p01);
         w1 = ptx::cvt_pack_f16(p10, p11);
       }
-      *reinterpret_cast<uint32_t*>(Pex + g * 40 + 8 * warp + 2 * tg) = w0;
-      *reinterpret_cast<uint32_t*>(Pex + (g + 8) * 40 + 8 * warp + 2 * tg) = w1;
+      *reinterpret_cast<uint32_t*>(pex + g * 40 + 8 * w + 2 * tg) = w0;
+      *reinterpret_cast<uint32_t*>(pex + (g + 8) * 40 + 8 * w + 2 * tg) = w1;
     }
     __syncthreads();
 
@@ -361,14 +396,16 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  __syncthreads();  // the last tile is used up: Ks may be overwritten below
+  float* ls_g = ls + gi * 64;
+  ptx::cp_async_wait<0>();  // (a CTA without tiles still has its Q copies in flight)
+  __syncthreads();  // the last tile is used up: the K buffers may be overwritten below
   if (tg == 0) {
-    ls[warp * 16 + g] = l0;
-    ls[warp * 16 + g + 8] = l1;
+    ls_g[w * 16 + g] = l0;
+    ls_g[w * 16 + g + 8] = l1;
   }
   __syncthreads();
-  l0 = (ls[g] + ls[16 + g]) + (ls[32 + g] + ls[48 + g]);
-  l1 = (ls[g + 8] + ls[24 + g]) + (ls[40 + g] + ls[56 + g]);
+  l0 = (ls_g[g] + ls_g[16 + g]) + (ls_g[32 + g] + ls_g[48 + g]);
+  l1 = (ls_g[g + 8] + ls_g[24 + g]) + (ls_g[40 + g] + ls_g[56 + g]);
 
   const T* sinks = reinterpret_cast<const T*>(a.sinks);
   T* obase = reinterpret_cast<T*>(a.o) + b * a.o_sb + (int64_t)i * a.o_ss;
@@ -386,7 +423,7 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
         m = m_f;
       }
       inv[r] = l > 0.f ? alpha / l : 0.f;
-      if (a.lse && warp == 0 && tg == 0 && row < nh)
+      if (a.lse && w == 0 && tg == 0 && row < nh)
         a.lse[((int64_t)b * a.Hq + h0 + row) * a.Sq + i] = l > 0.f ? m * kLn2 + logf(l) : -INFINITY;
     }
 #pragma unroll
@@ -408,7 +445,7 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
     return;
   }
 
-  // ---- several CTAs per token: partial results to shared memory, combined over the cluster ----
+  // ---- several CTAs per token (one head group each): partial results to shared memory, combined over the cluster ----
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) {
     if (nt < ntl) {
@@ -417,7 +454,7 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
       *reinterpret_cast<float2*>(Opart + (g + 8) * D + col) = make_float2(acc[nt][2], acc[nt][3]);
     }
   }
-  if (warp == 0 && tg == 0) {
+  if (w == 0 && tg == 0) {
     mpart[g] = m_row[0];
     mpart[g + 8] = m_row[1];
     lpart[g] = l0;
@@ -426,28 +463,51 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   ptx::cluster_sync();  // every CTA of the token has written its partial result
   {
     const uint32_t rank = ptx::cluster_ctarank();
-    const int cols = D / x.n_split;  // this CTA's share of the columns (D is a multiple of 64, n_split <= 8)
+    const int cols = D / x.n_split;  // this CTA's share of the columns (D is a multiple of 64, n_split <= 8: at least 8)
+    const int vecs = cols / 4;
     const uint32_t o_loc = ptx::smem_u32(Opart), m_loc = ptx::smem_u32(mpart), l_loc = ptx::smem_u32(lpart);
-    for (int e = tid; e < 16 * cols; e += kMmaThreads) {
-      const int row = e / cols, col = (int)rank * cols + (e - row * cols);
-      float ms[kMmaMaxSplit];
-      float m = -INFINITY;
-      for (int sIdx = 0; sIdx < x.n_split; ++sIdx) {
-        ms[sIdx] = ptx::ld_cluster_f32(ptx::map_to_cta(m_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
-        m = fmaxf(m, ms[sIdx]);
+    for (int e = tid; e < 16 * vecs; e += nthreads) {  // four columns of one row per step
+      const int row = e / vecs, col = (int)rank * cols + (e - row * vecs) * 4;
+      float ms[kMmaMaxSplit], lp[kMmaMaxSplit];
+      float4 op[kMmaMaxSplit];
+#pragma unroll
+      for (int sIdx = 0; sIdx < kMmaMaxSplit; ++sIdx) {  // all loads first: they are independent of each other
+        if (sIdx < x.n_split) {
+          ms[sIdx] = ptx::ld_cluster_f32(ptx::map_to_cta(m_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
+          lp[sIdx] = ptx::ld_cluster_f32(ptx::map_to_cta(l_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
+          op[sIdx] = ptx::ld_cluster_f32x4(ptx::map_to_cta(o_loc + (uint32_t)(row * D + col) * 4u, (uint32_t)sIdx));
+        } else {
+          ms[sIdx] = -INFINITY;
+          lp[sIdx] = 0.f;
+          op[sIdx] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
+      float m = -INFINITY;
+#pragma unroll
+      for (int sIdx = 0; sIdx < kMmaMaxSplit; ++sIdx) m = fmaxf(m, ms[sIdx]);
       float sl = -INFINITY;
       if (sinks && row < nh) sl = to_float(sinks[h0 + row]) * kLog2e;
       const float m_f = fmaxf(m, sl);
       float l = (sl == -INFINITY) ? 0.f : exp2f(sl - m_f);  // the sink: a score without a value row
-      float o = 0.f;
-      for (int sIdx = 0; sIdx < x.n_split; ++sIdx) {
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int sIdx = 0; sIdx < kMmaMaxSplit; ++sIdx) {
         const float wgt = ms[sIdx] == -INFINITY ? 0.f : exp2f(ms[sIdx] - m_f);
-        l += wgt * ptx::ld_cluster_f32(ptx::map_to_cta(l_loc + (uint32_t)row * 4u, (uint32_t)sIdx));
-        o += wgt * ptx::ld_cluster_f32(ptx::map_to_cta(o_loc + (uint32_t)(row * D + col) * 4u, (uint32_t)sIdx));
+        l += wgt * lp[sIdx];
+        o.x += wgt * op[sIdx].x; o.y += wgt * op[sIdx].y; o.z += wgt * op[sIdx].z; o.w += wgt * op[sIdx].w;
       }
       if (row < nh) {
-        obase[(int64_t)(h0 + row) * a.o_sh + col] = from_float<T>(l > 0.f ? o / l : 0.f);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* dst = obase + (int64_t)(h0 + row) * a.o_sh + col;
+        uint2 pk;
+        if constexpr (kBf16) {
+          pk.x = ptx::cvt_pack_bf16(o.x * inv, o.y * inv);
+          pk.y = ptx::cvt_pack_bf16(o.z * inv, o.w * inv);
+        } else {
+          pk.x = ptx::cvt_pack_f16(o.x * inv, o.y * inv);
+          pk.y = ptx::cvt_pack_f16(o.z * inv, o.w * inv);
+        }
+        *reinterpret_cast<uint2*>(dst) = pk;
         if (a.lse && col == 0) a.lse[((int64_t)b * a.Hq + h0 + row) * a.Sq + i] = l > 0.f ? m_f * kLn2 + logf(l) : -INFINITY;
       }
     }
@@ -483,13 +543,18 @@ int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, 
   const int sms = device_sm_count();
   while (split < kMmaMaxSplit && ctas * (split * 2) <= 2LL * sms && tiles >= 2 * (split * 2)) split *= 2;
   x.n_split = split;
+  // many tokens: all head groups of a KV head (up to four: 64 heads) in one CTA, so that a gathered row is fetched
+  // from L2 once for all of them; with a cluster one group per CTA (more CTAs is what the decode step wants)
+  x.gpc = split > 1 ? 1 : (ng < kMmaMaxGroups ? ng : kMmaMaxGroups);
+  const int gy = (ng + x.gpc - 1) / x.gpc;
   const int P = p.D + 8;
-  const size_t smem = 2 * ((size_t)16 * P + (size_t)(x.same_kv ? 1 : 2) * kMmaKeys * P + 16 * 40) + 4 * (64 + 64 + 32 + 16 + 16);
+  const size_t smem = 2 * ((size_t)x.gpc * 16 * P + (size_t)(x.same_kv ? 2 : 4) * kMmaKeys * P + (size_t)x.gpc * 16 * 40) +
+                      4 * ((size_t)x.gpc * 128 + 64 + 32);
   auto kern = sparse_mma_kernel<T>;
   if (smem > 48 * 1024) DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.Sq * split), (unsigned)(p.Hkv * ng), (unsigned)p.B);
-  cfg.blockDim = dim3(kMmaThreads);
+  cfg.gridDim = dim3((unsigned)(p.Sq * split), (unsigned)(p.Hkv * gy), (unsigned)p.B);
+  cfg.blockDim = dim3(128 * x.gpc);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
