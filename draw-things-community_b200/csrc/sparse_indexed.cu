@@ -7,12 +7,12 @@
 // arithmetic is in the absent back end; the definition restated here: an entry of the list outside [0, compressed rows)
 // means "no row", a row listed twice counts twice, the sink is an extra unscaled score without a value row.
 //
-// CUDA-core kernel, any head dim up to 512, fp16 / bf16 / fp32.  One CTA = one query token x up to 16 query heads that
-// share a KV head (the whole point of the layout: a gathered key row is read once for all of them); one warp per head.
-// The token's keys -- first its window of raw rows, then its selected rows -- are visited 32 at a time from a
-// shared-memory tile (fp32, odd row pitch): lane j owns key j of the tile for Q.K^T, then head dims {lane, lane + 32,
-// ...} for P.V.  No tensor cores yet: the decode step of the reference's model (one token, 128 + 512 keys) is a few
-// microseconds of work, long prefills are not tuned.
+// Two kernels: a tensor-core one (described at sparse_mma_kernel) for 16-bit tensors with a head dim that is a multiple
+// of 64 and 16-byte aligned rows, and a CUDA-core one for everything else (any head dim up to 512, fp16 / bf16 / fp32):
+// one CTA = one query token x up to 16 query heads that share a KV head (a gathered key row is read once for all of
+// them); one warp per head.  The token's keys -- first its window of raw rows, then its selected rows -- are visited
+// 32 at a time from a shared-memory tile (fp32, odd row pitch): lane j owns key j of the tile for Q.K^T, then head
+// dims {lane, lane + 32, ...} for P.V.
 #include "sm100_ptx.cuh"
 
 namespace dt {
