@@ -270,6 +270,7 @@ def side_measurements(dtattn, device, peaks, names=SIDE_SHAPES):
     out.update(prologue_measurements(dtattn, device, peaks))
     out.update(out_proj_measurements(dtattn, device, peaks))
     out.update(masked_measurements(dtattn, device, peaks))
+    out.update(sparse_measurements(dtattn, device, peaks))
     return out
 
 
@@ -298,6 +299,28 @@ def masked_measurements(dtattn, device, peaks):
     del sets
     torch.cuda.empty_cache()
     return {"llm_text_encoder_masked": res}
+
+
+def sparse_measurements(dtattn, device, peaks):
+    """Sparse indexed attention in the reference's configuration (DeepSeek4.swift:120-140: 64 query heads over one KV
+    head, head dim 512, raw window 128, 512 selected compressed rows, the same tensor as keys and values): a prompt of
+    4096 tokens, and the decode step over 8192 cached raw rows (CUDA-graph replay).  FLOPs = 4 * heads * keys * D per token."""
+    H, D, W, TOPK, dt = 64, 512, 128, 512, torch.bfloat16
+    out = {}
+    for name, (Sq, Sr, Sc) in {"sparse_indexed_prefill_4096": (4096, 4096, 1024), "sparse_indexed_decode_8192": (1, 8192, 2048)}.items():
+        g = torch.Generator(device=device).manual_seed(31)
+        rnd = lambda *shape: torch.randn(*shape, generator=g, device=device, dtype=torch.float32).to(dt)
+        q, kr, kc, sinks = rnd(1, Sq, H, D), rnd(1, Sr, 1, D), rnd(1, Sc, 1, D), rnd(H)
+        n = min(TOPK, Sc)
+        lists = torch.stack([torch.randperm(Sc, generator=g, device=device)[:n] for _ in range(min(Sq, 64))]).to(torch.int32)
+        sel = lists.repeat((Sq + lists.shape[0] - 1) // lists.shape[0], 1)[:Sq].unsqueeze(0).contiguous()
+        o = torch.empty_like(q)
+        fn = lambda: dtattn.sparse_indexed_attention(q, kr, kr, kc, kc, sel, D ** -0.5, sinks=sinks, sliding_window=W, out=o)
+        ms = time_graph([fn], reps=20 if Sq == 1 else 3)
+        fl = 4.0 * Sq * H * (min(W, Sr) + n) * D
+        out[name] = {"us_per_call_graph": round(ms * 1e3, 1), "tflops": round(fl / (ms * 1e-3) / 1e12, 2),
+                     "keys_per_token": min(W, Sr) + n, "heads": H, "D": D}
+    return out
 
 
 def out_proj_measurements(dtattn, device, peaks):
@@ -751,7 +774,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the gathered output (N > 1)")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no side measurements, no CPU baseline, one end-to-end step")
-    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj", "masked", "d256"],
+    ap.add_argument("--only", default=None, choices=["prologue", "decode_step", "out_proj", "masked", "d256", "sparse"],
                     help="run one group of side measurements alone and print it (for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "dtattn" else args.warmup
@@ -772,6 +795,7 @@ def main():
               "decode_step": lambda: decode_step_measurements(dtattn, device),
               "out_proj": lambda: out_proj_measurements(dtattn, device, peaks),
               "masked": lambda: masked_measurements(dtattn, device, peaks),
+              "sparse": lambda: sparse_measurements(dtattn, device, peaks),
               "d256": lambda: side_measurements(dtattn, device, peaks, ("auraflow_joint_d256", "qwen35_prefill_d256"))}[args.only]
         print(json.dumps({"only": args.only, "also": fn()}))
         return
