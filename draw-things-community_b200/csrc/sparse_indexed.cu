@@ -172,7 +172,8 @@ sparse_indexed_kernel(const SparseArgs a) {
 // matrix product per token, and the decode step needs the token's keys spread over several CTAs.
 //
 // One CTA = one token x 16 query heads of one KV head x one share of the token's keys; 4 warps.  Keys are gathered 32 at
-// a time into shared memory (16-byte pieces, 16-bit, row pitch D + 8 so that ldmatrix rows fall on distinct banks).
+// a time into shared memory (16-byte pieces, 16-bit, row pitch D + 8 so that ldmatrix rows fall on distinct banks);
+// 64 at a time where two buffers of that size fit (keys and values in one tensor): a warp then takes 16 keys.
 // S = Q K^T: warp w takes keys 8 w .. 8 w + 7 of the tile over the whole head dim (one n-tile, D / 16 k-steps; Q and K
 // fragments by ldmatrix).  The row maxima of the four warps meet in shared memory, every warp then holds the tile's
 // maximum, exponentiates its 8 keys and writes them as 16-bit P into a [16 x 32] exchange tile.  O += P V: warp w owns
@@ -180,7 +181,6 @@ sparse_indexed_kernel(const SparseArgs a) {
 // With more than one share per token the CTAs of a token form a thread-block cluster: each leaves (m, l, O) in its
 // shared memory and CTA r of the cluster combines and stores columns [r D / n, (r + 1) D / n) of the 16 rows from all
 // of them through distributed shared memory (ordinary ld.shared::cluster loads).
-constexpr int kMmaKeys = 32;
 constexpr int kMmaMaxSplit = 8;
 constexpr int kMmaMaxGroups = 4;  // head groups of 16 per CTA
 
@@ -190,23 +190,25 @@ struct SparseMmaExtra {
   int gpc;       // head groups of 16 per CTA (4 warps each); they share the gathered tiles
 };
 
-template <typename T>
+template <typename T, int TK>  // TK keys per tile: 32, or 64 (every Q fragment then feeds two score MMAs)
 __global__ void __launch_bounds__(128 * kMmaMaxGroups)
 sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  constexpr int NT = TK / 32;        // n-tiles of 8 keys per warp in Q K^T
+  constexpr int PP = TK + 8;         // row pitch of the P exchange tile
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = a.D, P = D + 8;  // row pitch in elements
   const int gpc = x.gpc, nthreads = 128 * gpc;
   uint16_t* Qs = reinterpret_cast<uint16_t*>(smem_raw);                 // [gpc * 16][P]
   uint16_t* Kb = Qs + gpc * 16 * P;                                      // [2][32][P]
-  uint16_t* Vb = x.same_kv ? Kb : Kb + 2 * kMmaKeys * P;                 // [2][32][P]
-  uint16_t* Pex = Kb + (x.same_kv ? 2 : 4) * kMmaKeys * P;               // [gpc][16][40]
-  float* mxs = reinterpret_cast<float*>(Pex + gpc * 16 * 40);            // [gpc][4][16] row maxima, one set per warp
+  uint16_t* Vb = x.same_kv ? Kb : Kb + 2 * TK * P;                 // [2][32][P]
+  uint16_t* Pex = Kb + (x.same_kv ? 2 : 4) * TK * P;               // [gpc][16][40]
+  float* mxs = reinterpret_cast<float*>(Pex + gpc * 16 * PP);            // [gpc][4][16] row maxima, one set per warp
   float* ls = mxs + gpc * 64;                                            // [gpc][4][16] row sums
   int* codes = reinterpret_cast<int*>(ls + gpc * 64);                    // [2][32]
   // cluster path (one head group per CTA): after the key loop the first K buffer holds this CTA's partial result
   float* Opart = reinterpret_cast<float*>(Kb);                           // [16][D] fp32
-  float* mpart = reinterpret_cast<float*>(codes + 64);                   // [16]
+  float* mpart = reinterpret_cast<float*>(codes + 2 * TK);               // [16]
   float* lpart = mpart + 16;                                             // [16]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
@@ -241,7 +243,7 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   const int n_raw = last_c >= first ? (int)(last_c - first + 1) : 0;
   const int n_keys = n_raw + (a.Sc > 0 ? a.n_sel : 0);
   const int32_t* sel = a.selected ? a.selected + b * a.sel_sb + (int64_t)i * a.sel_sq : nullptr;
-  const int n_tiles = (n_keys + kMmaKeys - 1) / kMmaKeys;
+  const int n_tiles = (n_keys + TK - 1) / TK;
   const int per = (n_tiles + x.n_split - 1) / x.n_split;
   const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
 
@@ -252,8 +254,8 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
 
   // which row each of a tile's 32 keys is: -1 no key, >= 0 raw row, <= -2 compressed row -(code + 2)
   auto set_codes = [&](int tile, int buf) {
-    if (tid < kMmaKeys) {
-      const int vkey = tile * kMmaKeys + tid;
+    if (tid < TK) {
+      const int vkey = tile * TK + tid;
       int code = -1;
       if (vkey < n_raw) {
         code = (int)(first + vkey);
@@ -261,15 +263,15 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
         const int idx = sel[vkey - n_raw];
         if (idx >= 0 && idx < a.Sc) code = -(idx + 2);
       }
-      codes[buf * kMmaKeys + tid] = code;
+      codes[buf * TK + tid] = code;
     }
   };
   // the tile's rows into buffer `buf`: asynchronous 16-byte copies, zero fill where there is no key
   auto gather = [&](int buf) {
-    const uint32_t kdst = ptx::smem_u32(Kb + buf * kMmaKeys * P), vdst = ptx::smem_u32(Vb + buf * kMmaKeys * P);
-    for (int c = tid; c < kMmaKeys * chunks; c += nthreads) {
+    const uint32_t kdst = ptx::smem_u32(Kb + buf * TK * P), vdst = ptx::smem_u32(Vb + buf * TK * P);
+    for (int c = tid; c < TK * chunks; c += nthreads) {
       const int r = c / chunks, ch = c - r * chunks;
-      const int code = codes[buf * kMmaKeys + r];
+      const int code = codes[buf * TK + r];
       const T* ksrc = kr;  // any valid address when nothing is copied
       const T* vsrc = vr;
       int nbytes = 0;
@@ -301,10 +303,10 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   float l_lane[2] = {0.f, 0.f};             // this lane's share of the row sums (its two keys of every tile)
 
   const uint32_t qs_addr = ptx::smem_u32(Qs) + (uint32_t)(((gi * 16 + (lane & 15)) * P + (lane >> 4) * 8) * 2);
-  const uint32_t ks_off = (uint32_t)(((8 * w + (lane & 7)) * P + (lane >> 3) * 8) * 2);
+  const uint32_t ks_off = (uint32_t)(((8 * NT * w + (lane & 7)) * P + (lane >> 3) * 8) * 2);
   const uint32_t vs_off = (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * P + dim0 + (lane >> 4) * 8) * 2);
-  uint16_t* pex = Pex + gi * 16 * 40;
-  const uint32_t pex_addr = ptx::smem_u32(pex) + (uint32_t)(((lane & 15) * 40 + (lane >> 4) * 8) * 2);
+  uint16_t* pex = Pex + gi * 16 * PP;
+  const uint32_t pex_addr = ptx::smem_u32(pex) + (uint32_t)(((lane & 15) * PP + (lane >> 4) * 8) * 2);
   float* mx_g = mxs + gi * 64;
 
   if (t_begin < t_end) {
@@ -319,24 +321,41 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
     ptx::cp_async_wait<0>();
     __syncthreads();  // this tile has landed for everybody, the previous tile is used up, the next codes are visible
     if (more) gather(cur ^ 1);  // travels while this tile is worked on
-    const uint32_t ks_addr = ptx::smem_u32(Kb + cur * kMmaKeys * P) + ks_off;
-    const uint32_t vs_addr = ptx::smem_u32(Vb + cur * kMmaKeys * P) + vs_off;
-    const int* code_cur = codes + cur * kMmaKeys;
+    const uint32_t ks_addr = ptx::smem_u32(Kb + cur * TK * P) + ks_off;
+    const uint32_t vs_addr = ptx::smem_u32(Vb + cur * TK * P) + vs_off;
+    const int* code_cur = codes + cur * TK;
 
-    // ---- scores of this warp's 8 keys, the group's 16 heads, the whole head dim ----
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- scores of this warp's 8 NT keys, the group's 16 heads, the whole head dim ----
+    float sc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
     for (int ks = 0; ks < D / 16; ks += 2) {
-      uint32_t a0[4], a1[4], b0, b1, b2, b3;
+      uint32_t a0[4], a1[4];
       ptx::ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], qs_addr + (uint32_t)(ks * 32));
       ptx::ldmatrix_x4(a1[0], a1[1], a1[2], a1[3], qs_addr + (uint32_t)(ks * 32 + 32));
-      ptx::ldmatrix_x4(b0, b1, b2, b3, ks_addr + (uint32_t)(ks * 32));
-      ptx::mma_m16n8k16<kBf16>(sc, a0, b0, b1);
-      ptx::mma_m16n8k16<kBf16>(sc, a1, b2, b3);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        uint32_t b0, b1, b2, b3;
+        ptx::ldmatrix_x4(b0, b1, b2, b3, ks_addr + (uint32_t)(ks * 32 + j * 8 * P * 2));
+        ptx::mma_m16n8k16<kBf16>(sc[j], a0, b0, b1);
+        ptx::mma_m16n8k16<kBf16>(sc[j], a1, b2, b3);
+      }
     }
-    const bool v0 = code_cur[8 * w + 2 * tg] != -1, v1 = code_cur[8 * w + 2 * tg + 1] != -1;
-    const float s00 = v0 ? sc[0] * a.scale_log2 : -INFINITY, s01 = v1 ? sc[1] * a.scale_log2 : -INFINITY;  // row g
-    const float s10 = v0 ? sc[2] * a.scale_log2 : -INFINITY, s11 = v1 ? sc[3] * a.scale_log2 : -INFINITY;  // row g + 8
-    float mx0 = fmaxf(s00, s01), mx1 = fmaxf(s10, s11);
+    // this lane's scores: rows g (s[j][0], s[j][1]) and g + 8 (s[j][2], s[j][3]) of keys 8 NT w + 8 j + 2 tg + {0, 1}
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int key = 8 * NT * w + 8 * j + 2 * tg;
+      const bool v0 = code_cur[key] != -1, v1 = code_cur[key + 1] != -1;
+      sc[j][0] = v0 ? sc[j][0] * a.scale_log2 : -INFINITY;
+      sc[j][1] = v1 ? sc[j][1] * a.scale_log2 : -INFINITY;
+      sc[j][2] = v0 ? sc[j][2] * a.scale_log2 : -INFINITY;
+      sc[j][3] = v1 ? sc[j][3] * a.scale_log2 : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+      mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+    }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -350,13 +369,13 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
     const float mt1 = fmaxf(fmaxf(mx_g[g + 8], mx_g[24 + g]), fmaxf(mx_g[40 + g], mx_g[56 + g]));
     const float mn0 = fmaxf(m_row[0], mt0), mn1 = fmaxf(m_row[1], mt1);
     const float al0 = mn0 == -INFINITY ? 1.f : exp2f(m_row[0] - mn0), al1 = mn1 == -INFINITY ? 1.f : exp2f(m_row[1] - mn1);
-    const float p00 = mn0 == -INFINITY ? 0.f : exp2f(s00 - mn0), p01 = mn0 == -INFINITY ? 0.f : exp2f(s01 - mn0);
-    const float p10 = mn1 == -INFINITY ? 0.f : exp2f(s10 - mn1), p11 = mn1 == -INFINITY ? 0.f : exp2f(s11 - mn1);
-    l_lane[0] = l_lane[0] * al0 + (p00 + p01);
-    l_lane[1] = l_lane[1] * al1 + (p10 + p11);
-    m_row[0] = mn0;
-    m_row[1] = mn1;
-    {
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const float p00 = mn0 == -INFINITY ? 0.f : exp2f(sc[j][0] - mn0), p01 = mn0 == -INFINITY ? 0.f : exp2f(sc[j][1] - mn0);
+      const float p10 = mn1 == -INFINITY ? 0.f : exp2f(sc[j][2] - mn1), p11 = mn1 == -INFINITY ? 0.f : exp2f(sc[j][3] - mn1);
+      sum0 += p00 + p01;
+      sum1 += p10 + p11;
       uint32_t w0, w1;
       if constexpr (kBf16) {
         w0 = ptx::cvt_pack_bf16(p00, p01);
@@ -365,27 +384,32 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
         w0 = ptx::cvt_pack_f16(p00, p01);
         w1 = ptx::cvt_pack_f16(p10, p11);
       }
-      *reinterpret_cast<uint32_t*>(pex + g * 40 + 8 * w + 2 * tg) = w0;
-      *reinterpret_cast<uint32_t*>(pex + (g + 8) * 40 + 8 * w + 2 * tg) = w1;
+      const int key = 8 * NT * w + 8 * j + 2 * tg;
+      *reinterpret_cast<uint32_t*>(pex + g * PP + key) = w0;
+      *reinterpret_cast<uint32_t*>(pex + (g + 8) * PP + key) = w1;
     }
+    l_lane[0] = l_lane[0] * al0 + sum0;
+    l_lane[1] = l_lane[1] * al1 + sum1;
+    m_row[0] = mn0;
+    m_row[1] = mn1;
     __syncthreads();
 
     // ---- O += P V over this warp's head dims ----
-    uint32_t pa0[4], pa1[4];
-    ptx::ldmatrix_x4(pa0[0], pa0[1], pa0[2], pa0[3], pex_addr);
-    ptx::ldmatrix_x4(pa1[0], pa1[1], pa1[2], pa1[3], pex_addr + 32);
+    uint32_t pa[TK / 16][4];
+#pragma unroll
+    for (int k2 = 0; k2 < TK / 16; ++k2) ptx::ldmatrix_x4(pa[k2][0], pa[k2][1], pa[k2][2], pa[k2][3], pex_addr + (uint32_t)(k2 * 32));
 #pragma unroll
     for (int nt = 0; nt < 16; nt += 2) {
       if (nt < ntl) {
         acc[nt][0] *= al0; acc[nt][1] *= al0; acc[nt][2] *= al1; acc[nt][3] *= al1;
         acc[nt + 1][0] *= al0; acc[nt + 1][1] *= al0; acc[nt + 1][2] *= al1; acc[nt + 1][3] *= al1;
-        uint32_t b0, b1, b2, b3;
-        ptx::ldmatrix_x4_trans(b0, b1, b2, b3, vs_addr + (uint32_t)(nt * 16));
-        ptx::mma_m16n8k16<kBf16>(acc[nt], pa0, b0, b1);
-        ptx::mma_m16n8k16<kBf16>(acc[nt + 1], pa0, b2, b3);
-        ptx::ldmatrix_x4_trans(b0, b1, b2, b3, vs_addr + (uint32_t)(nt * 16 + 16 * P * 2));
-        ptx::mma_m16n8k16<kBf16>(acc[nt], pa1, b0, b1);
-        ptx::mma_m16n8k16<kBf16>(acc[nt + 1], pa1, b2, b3);
+#pragma unroll
+        for (int k2 = 0; k2 < TK / 16; ++k2) {
+          uint32_t b0, b1, b2, b3;
+          ptx::ldmatrix_x4_trans(b0, b1, b2, b3, vs_addr + (uint32_t)(nt * 16 + k2 * 16 * P * 2));
+          ptx::mma_m16n8k16<kBf16>(acc[nt], pa[k2], b0, b1);
+          ptx::mma_m16n8k16<kBf16>(acc[nt + 1], pa[k2], b2, b3);
+        }
       }
     }
   }
@@ -526,8 +550,8 @@ bool sparse_mma_supported(const dt_sparse_indexed_params& p) {
   return ok(p.q) && ok(p.o) && ok(p.k_raw) && ok(p.v_raw) && ok(p.k_comp) && ok(p.v_comp);
 }
 
-template <typename T>
-int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, cudaStream_t stream) {
+template <typename T, int TK>
+int launch_sparse_mma_tk(const dt_sparse_indexed_params& p, const SparseArgs& a, cudaStream_t stream) {
   auto same = [](const dt_tensor4& u, const dt_tensor4& v) {
     return u.ptr == v.ptr && u.stride_b == v.stride_b && u.stride_s == v.stride_s && u.stride_h == v.stride_h;
   };
@@ -538,7 +562,7 @@ int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, 
   // few tokens (the decode step): a token's keys are shared out over a cluster of CTAs, as long as every CTA still gets
   // a few tiles and the grid stays within about two rounds over the SMs
   const int keys = (p.sliding_window > 0 ? (p.sliding_window < p.Sr ? p.sliding_window : p.Sr) : p.Sr) + (p.Sc > 0 ? p.n_selected : 0);
-  const int tiles = (keys + kMmaKeys - 1) / kMmaKeys;
+  const int tiles = (keys + TK - 1) / TK;
   int split = 1;
   const int sms = device_sm_count();
   while (split < kMmaMaxSplit && ctas * (split * 2) <= 2LL * sms && tiles >= 2 * (split * 2)) split *= 2;
@@ -548,9 +572,9 @@ int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, 
   x.gpc = split > 1 ? 1 : (ng < kMmaMaxGroups ? ng : kMmaMaxGroups);
   const int gy = (ng + x.gpc - 1) / x.gpc;
   const int P = p.D + 8;
-  const size_t smem = 2 * ((size_t)x.gpc * 16 * P + (size_t)(x.same_kv ? 2 : 4) * kMmaKeys * P + (size_t)x.gpc * 16 * 40) +
-                      4 * ((size_t)x.gpc * 128 + 64 + 32);
-  auto kern = sparse_mma_kernel<T>;
+  const size_t smem = 2 * ((size_t)x.gpc * 16 * P + (size_t)(x.same_kv ? 2 : 4) * TK * P + (size_t)x.gpc * 16 * (TK + 8)) +
+                      4 * ((size_t)x.gpc * 128 + 2 * TK + 32);
+  auto kern = sparse_mma_kernel<T, TK>;
   if (smem > 48 * 1024) DT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.Sq * split), (unsigned)(p.Hkv * gy), (unsigned)p.B);
@@ -566,6 +590,18 @@ int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, 
   cfg.numAttrs = split > 1 ? 1 : 0;
   DT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, x));
   return DT_OK;
+}
+
+// 64 keys per tile when the two K buffers of that size fit beside Q (keys and values in one tensor; otherwise 32)
+template <typename T>
+int launch_sparse_mma_t(const dt_sparse_indexed_params& p, const SparseArgs& a, cudaStream_t stream) {
+  auto same = [](const dt_tensor4& u, const dt_tensor4& v) {
+    return u.ptr == v.ptr && u.stride_b == v.stride_b && u.stride_s == v.stride_s && u.stride_h == v.stride_h;
+  };
+  const bool same_kv = same(p.k_raw, p.v_raw) && (p.Sc == 0 || p.n_selected == 0 || same(p.k_comp, p.v_comp));
+  const int keys = (p.sliding_window > 0 ? (p.sliding_window < p.Sr ? p.sliding_window : p.Sr) : p.Sr) + (p.Sc > 0 ? p.n_selected : 0);
+  if (same_kv && keys >= 256 && (long long)p.Sq * p.B >= 64) return launch_sparse_mma_tk<T, 64>(p, a, stream);
+  return launch_sparse_mma_tk<T, 32>(p, a, stream);
 }
 
 template <typename T>

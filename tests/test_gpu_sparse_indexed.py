@@ -79,10 +79,14 @@ def test_operator_mirror_and_equivalence_with_the_window_operator(dtattn):
     assert (a.float() - b.float()).abs().max() <= 2e-3
 
 
-def test_keys_that_are_also_the_values(dtattn):
+@pytest.mark.parametrize("shape", [(9, 200, 64, 40), (70, 400, 200, 150), (130, 130, 33, 200)])
+def test_keys_that_are_also_the_values(dtattn, shape):
     """The reference's layout (DeepSeek4.swift:489-491): one tensor serves as keys and values; the tensor-core kernel
-    then gathers each row once.  Also without sinks, and with a strided (row-padded) view."""
-    B, Sq, Sr, Sc, n_sel, Hq, D, dtype = 1, 9, 200, 64, 40, 64, 512, torch.bfloat16
+    then gathers each row once, and with enough tokens and keys works on 64 keys per step instead of 32 (the second
+    and third shape; the third has a last tile of 6 keys and lists longer than the compressed tensor).  Also without
+    sinks, and with a strided (row-padded) view."""
+    Sq, Sr, Sc, n_sel = shape
+    B, Hq, D, dtype = 1, 64, 512, torch.bfloat16
     q, kr, _, kc, _, sel, sinks = make_case(B, Sq, Sr, Sc, n_sel, Hq, 1, D, dtype, 821)
     big_r = torch.zeros(B, Sr, 1, D + 64, dtype=dtype)
     big_r[..., :D] = kr
