@@ -272,8 +272,8 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
     for (int c = tid; c < TK * chunks; c += nthreads) {
       const int r = c / chunks, ch = c - r * chunks;
       const int code = codes[buf * TK + r];
-      const T* ksrc = kr;  // any valid address when nothing is copied
-      const T* vsrc = vr;
+      const T* ksrc = reinterpret_cast<const T*>(a.q);  // any valid address when nothing is copied (the raw tensors may be absent)
+      const T* vsrc = ksrc;
       int nbytes = 0;
       if (code >= 0) {
         ksrc = kr + (int64_t)code * a.kr_ss + ch * 8;
