@@ -579,6 +579,19 @@ def run_single(args, dtattn, device, peaks):
     print(json.dumps(line))
 
 
+def agreed_extra_steps(dist, device, timed_ms, steps, profile=False):
+    """(max over ranks of the timed region in ms, number of further steps every rank runs to keep the load on for the
+    clock sampler).  Every step is a collective, so the count must be the same on all ranks: it is derived from the
+    all-reduced maximum, never from a rank's own clock (ranks that disagreed by one step left the odd one waiting in
+    a rendezvous nobody else joined)."""
+    t = torch.tensor([timed_ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    timed_max = float(t.item())
+    if profile or timed_max >= 1200:
+        return timed_max, 0
+    return timed_max, int(min(400, 1200 / max(timed_max / steps, 1e-3)))
+
+
 def run_sharded(args, dtattn, device, peaks):
     import torch.distributed as dist
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -628,16 +641,10 @@ def run_sharded(args, dtattn, device, peaks):
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        timed_ms = e0.elapsed_time(e1)
-        t = torch.tensor([timed_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        timed_max = float(t.item())
-        # keep the load on while the 200 ms clock sampler collects a few samples.  Every step is a collective, so the
-        # number of extra steps is derived from the time all ranks agree on (the maximum), never from a rank's own clock.
-        if timed_max < 1200 and not args.profile:
-            for i in range(int(min(400, 1200 / max(timed_max / args.steps, 1e-3)))):
-                step(i)
-            torch.cuda.synchronize()
+        timed_max, n_more = agreed_extra_steps(dist, device, e0.elapsed_time(e1), args.steps, args.profile)
+        for i in range(n_more):  # keep the load on while the 200 ms clock sampler collects a few samples
+            step(i)
+        torch.cuda.synchronize()
     ms_step = timed_max / args.steps
     status = dtattn.device_status()
     fl = flops_of(w)

@@ -112,3 +112,38 @@ def test_head_range_rules():
     assert sharding.chunk_rows(75600, 4, items_per_row_block=10) == [(0, 18944), (18944, 37888), (37888, 56832), (56832, 75600)]
     assert sharding.chunk_rows(75600, 4, items_per_row_block=5) == [(0, 37888), (37888, 75600)]   # Wan on 8 GPUs
     assert sharding.chunk_rows(100, 1) == [(0, 100)]
+
+
+def _steps_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import bench
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # the ranks measured slightly different times for the same five steps: their own clocks would give 21 and 22
+        # extra steps (1200 / 54.6 and 1200 / 54.4), i.e. one rank would enter a collective step the other never joins
+        own_ms = 5 * (54.6 if rank == 0 else 54.4)
+        own_count = int(min(400, 1200 / (own_ms / 5)))
+        agreed_ms, n = bench.agreed_extra_steps(dist, torch.device("cpu"), own_ms, 5)
+        q.put((rank, own_count, agreed_ms, n, bench.agreed_extra_steps(dist, torch.device("cpu"), 5000.0 + rank, 5)[1]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_every_rank_runs_the_same_number_of_extra_steps():
+    """bench.py keeps the GPUs loaded for the clock sampler with extra steps, and every step is a collective: the
+    count comes from the all-reduced maximum so that all ranks agree on it."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_steps_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert res[0][1] != res[1][1], "the scenario must be one where the ranks' own clocks disagree"
+    assert res[0][2] == res[1][2] == pytest.approx(5 * 54.6)
+    assert res[0][3] == res[1][3] == 21
+    assert res[0][4] == res[1][4] == 0  # long enough already: no extra steps
