@@ -252,6 +252,7 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   const T* kc = reinterpret_cast<const T*>(a.k_comp) + b * a.kc_sb + kvh * a.kc_sh;
   const T* vc = reinterpret_cast<const T*>(a.v_comp) + b * a.vc_sb + kvh * a.vc_sh;
 
+  const int g_r0 = tid / chunks, g_ch0 = tid - g_r0 * chunks, g_dr = nthreads / chunks, g_dch = nthreads - g_dr * chunks;
   // which row each of a tile's 32 keys is: -1 no key, >= 0 raw row, <= -2 compressed row -(code + 2)
   auto set_codes = [&](int tile, int buf) {
     if (tid < TK) {
@@ -269,8 +270,12 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
   // the tile's rows into buffer `buf`: asynchronous 16-byte copies, zero fill where there is no key
   auto gather = [&](int buf) {
     const uint32_t kdst = ptx::smem_u32(Kb + buf * TK * P), vdst = ptx::smem_u32(Vb + buf * TK * P);
-    for (int c = tid; c < TK * chunks; c += nthreads) {
-      const int r = c / chunks, ch = c - r * chunks;
+    int r = g_r0, ch = g_ch0;  // (row, 16-byte piece) of this thread's first copy; they advance without dividing
+    for (int c = tid; c < TK * chunks; c += nthreads, r += g_dr, ch += g_dch) {
+      if (ch >= chunks) {
+        ch -= chunks;
+        ++r;
+      }
       const int code = codes[buf * TK + r];
       const T* ksrc = reinterpret_cast<const T*>(a.q);  // any valid address when nothing is copied (the raw tensors may be absent)
       const T* vsrc = ksrc;
@@ -398,11 +403,17 @@ sparse_mma_kernel(const SparseArgs a, const SparseMmaExtra x) {
     uint32_t pa[TK / 16][4];
 #pragma unroll
     for (int k2 = 0; k2 < TK / 16; ++k2) ptx::ldmatrix_x4(pa[k2][0], pa[k2][1], pa[k2][2], pa[k2][3], pex_addr + (uint32_t)(k2 * 32));
+    if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {  // some row's maximum moved (rare once it has settled)
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        if (nt < ntl) {
+          acc[nt][0] *= al0; acc[nt][1] *= al0; acc[nt][2] *= al1; acc[nt][3] *= al1;
+        }
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < 16; nt += 2) {
       if (nt < ntl) {
-        acc[nt][0] *= al0; acc[nt][1] *= al0; acc[nt][2] *= al1; acc[nt][3] *= al1;
-        acc[nt + 1][0] *= al0; acc[nt + 1][1] *= al0; acc[nt + 1][2] *= al1; acc[nt + 1][3] *= al1;
 #pragma unroll
         for (int k2 = 0; k2 < TK / 16; ++k2) {
           uint32_t b0, b1, b2, b3;
