@@ -432,7 +432,7 @@ def decode_step_measurements(dtattn, device):
 
 def cpu_baseline(w, max_seconds=25.0):
     """The CPU restatement (oracle/sdpa_oracle.c) timed on this machine's host cores on the same shape.
-    Query rows are sampled evenly when the whole shape would take longer than the budget."""
+    Query rows are sampled evenly when the whole shape would take longer than `max_seconds`."""
     from oracle import c_oracle
     cores = c_oracle.host_cores()
     dt = torch.float32
