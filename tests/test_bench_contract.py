@@ -24,3 +24,20 @@ def test_reference_arm_prints_one_contract_line():
     assert cb["kind"] in ("port", "reference") and cb["cores"] >= 1 and cb["sample"] and cb["value"] == d["value"]
     e2e = d["e2e"]
     assert e2e["value"] == d["value"] and e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
+
+
+def test_flop_counts():
+    """4 B H Sq Sk D for the plain operator; under the causal rule only the visible (query, key) pairs count, and a
+    single new token over a cache sees every key."""
+    sys.path.insert(0, ROOT)
+    import bench
+    w = bench.WORKLOADS["flux_joint"]
+    assert bench.flops_of(w) == 4 * 1 * 24 * 4608 * 4608 * 128
+    assert bench.flops_of(w, heads=3) == 4 * 1 * 3 * 4608 * 4608 * 128
+    d = bench.WORKLOADS["decode_b16"]
+    assert d["causal"] and bench.flops_of(d) == 4 * 16 * 32 * 1 * 8192 * 128
+    c = dict(B=1, Sq=4, Sk=6, Hq=1, Hkv=1, D=2, causal=True)
+    visible = sum(6 - 4 + i + 1 for i in range(4))  # rows see 3, 4, 5, 6 keys
+    assert abs(bench.flops_of(c) - 4 * visible * 2) < 1e-9
+    for name in ("auraflow_joint_d256", "qwen35_prefill_d256"):
+        assert bench.WORKLOADS[name]["D"] == 256 and name in bench.SIDE_SHAPES
